@@ -1,0 +1,125 @@
+/*
+ * fa2_b200 — C ABI of the B200 (sm_100a) FlashAttention-2 kernels.
+ *
+ * This is the boundary an XLA FFI custom call (or any other host runtime) binds. It replaces
+ * the two Triton launch sites of erfanzar/jax-flash-attn2:
+ *   - forward : jax_flash_attn2/flash_attention_triton/_forward_triton.py:462-592
+ *               (_fwd_attention_kernel_call -> triton_call(_attn_fwd))
+ *   - backward: jax_flash_attn2/flash_attention_triton/_backward_triton.py:948-1173
+ *               (_bwd_attention_kernel_call -> triton_call(_attn_bwd_preprocess), triton_call(_attn_bwd))
+ *
+ * Conventions
+ *   - Every pointer is a device pointer owned by the caller. The library allocates nothing,
+ *     frees nothing and keeps no pointer after a call returns.
+ *   - Work is launched on the CUDA stream passed in (a cudaStream_t cast to void*); no call
+ *     synchronises the host with the device.
+ *   - Tensors are addressed by element strides, so [B,S,H,D] and [B,H,S,D] storage (and
+ *     broadcast bias / mask dimensions, stride 0) need no copy. The head-dim stride must be 1.
+ *   - Return value: 0 on success, a negative fa2_status otherwise. fa2_last_error() returns a
+ *     thread-local message for the last failing call. Validation happens before any launch.
+ */
+#ifndef FA2_B200_H_
+#define FA2_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  FA2_OK = 0,
+  FA2_ERR_INVALID_ARG = -1,   /* null pointer, bad shape, bad stride, bad dropout ...        */
+  FA2_ERR_UNSUPPORTED = -2,   /* head dim / dtype / alignment outside what the kernels take  */
+  FA2_ERR_CUDA = -3,          /* a CUDA runtime or driver call failed                        */
+  FA2_ERR_WORKSPACE = -4      /* workspace pointer missing or too small                      */
+} fa2_status;
+
+typedef enum {
+  FA2_FP16 = 0,               /* same numbering as dtype_index(), _utils.py:75-82            */
+  FA2_BF16 = 1,
+  FA2_FP32 = 2                /* accepted for bias / mask only                               */
+} fa2_dtype;
+
+/* Element strides of a 4-D operand, indexed as (batch, sequence, head, 1). */
+typedef struct {
+  int64_t b, s, h;
+} fa2_strides;
+
+/* Additive score term (bias or mask): x[b, h, i, j]; stride 0 broadcasts a dimension, the j
+ * stride is 1. Same broadcasting rules as calc_bias_strides(), _utils.py:151-193. */
+typedef struct {
+  const void* ptr;            /* NULL = absent                                               */
+  int32_t dtype;              /* fa2_dtype: the q/k/v dtype or FA2_FP32                      */
+  int64_t stride_b, stride_h, stride_q;
+} fa2_score_term;
+
+typedef struct {
+  int32_t batch, seqlen_q, seqlen_k, heads_q, heads_kv, head_dim;
+  int32_t dtype;              /* fa2_dtype of q, k, v, o, do, dq, dk, dv                     */
+  int32_t causal;             /* bottom-right aligned when seqlen_q != seqlen_k              */
+  float softmax_scale;        /* multiplies q.k ; callers default it to 1/sqrt(head_dim)     */
+  float dropout_p;            /* probability of dropping an attention weight, [0, 1)         */
+  uint64_t dropout_seed;
+  /* A sharded caller passes the global position of its slice so that every shard draws the
+   * dropout bits the unsharded call would draw. */
+  int32_t batch_offset, head_offset, heads_q_global;
+} fa2_problem;
+
+typedef struct {
+  fa2_problem p;
+  const void* q; fa2_strides q_strides;       /* [B, Sq, Hq,  D] */
+  const void* k; fa2_strides k_strides;       /* [B, Sk, Hkv, D] */
+  const void* v; fa2_strides v_strides;       /* [B, Sk, Hkv, D] */
+  void* o;       fa2_strides o_strides;       /* [B, Sq, Hq,  D] */
+  float* lse;                                  /* [B, Hq, lse_stride_h >= Sq], natural log    */
+  int64_t lse_stride_b, lse_stride_h;
+  fa2_score_term bias;                         /* added to scale * q.k                        */
+  fa2_score_term mask;                         /* added as well; 0 keeps, -inf / finfo.min drops */
+} fa2_fwd_params;
+
+typedef struct {
+  fa2_problem p;
+  const void* q;  fa2_strides q_strides;
+  const void* k;  fa2_strides k_strides;
+  const void* v;  fa2_strides v_strides;
+  const void* o;  fa2_strides o_strides;
+  const void* d_o; fa2_strides do_strides;    /* cotangent of o, [B, Sq, Hq, D]               */
+  const float* lse; int64_t lse_stride_b, lse_stride_h;
+  fa2_score_term bias;
+  fa2_score_term mask;
+  void* dq; fa2_strides dq_strides;           /* [B, Sq, Hq,  D] in the q dtype               */
+  void* dk; fa2_strides dk_strides;           /* [B, Sk, Hkv, D], already summed over a group */
+  void* dv; fa2_strides dv_strides;
+  void* workspace;                             /* fa2_bwd_workspace_bytes() bytes, 256-aligned */
+  size_t workspace_bytes;
+} fa2_bwd_params;
+
+/* Forward: o = softmax(scale q k^T + bias + mask [causal]) v with dropout on the weights, and
+ * lse = log sum exp of the (pre-dropout) scores. Replaces _fwd_attention_kernel_call
+ * (_forward_triton.py:462-592) and the kernel _attn_fwd (_forward_triton.py:213-459). */
+int fa2_fwd(const fa2_fwd_params* params, void* cuda_stream);
+
+/* Backward: dq, dk, dv from d_o, the saved o and lse. Replaces _bwd_attention_kernel_call
+ * (_backward_triton.py:948-1173): the rowsum(o * d_o) pre-pass (_attn_bwd_preprocess, :79-147),
+ * the main kernel (_attn_bwd, :712-945) and the per-group reduction of dk / dv (:1156-1161). */
+int fa2_bwd(const fa2_bwd_params* params, void* cuda_stream);
+
+/* Bytes of scratch the backward needs for this problem (fp32 dq accumulator and the row sums). */
+size_t fa2_bwd_workspace_bytes(const fa2_problem* problem);
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* fa2_last_error(void);
+
+/* ABI version of this header: major * 1000 + minor. */
+int fa2_version(void);
+
+/* Reads and clears the device status word written by a kernel whose bounded wait ran out
+ * (0 = no time-out seen). Synchronises the stream; meant for tests and debugging. */
+int fa2_debug_device_status(void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA2_B200_H_ */

@@ -1,0 +1,304 @@
+// C ABI of the library: argument validation, tensor-map construction, kernel dispatch.
+// Host half of the reference's launchers _fwd_attention_kernel_call
+// (jax_flash_attn2/flash_attention_triton/_forward_triton.py:462-592) and
+// _bwd_attention_kernel_call (_backward_triton.py:948-1173); the shape and broadcast rules
+// follow calc_bias_strides (flash_attention_triton/_utils.py:151-193).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/fa2_b200.h"
+#include "bwd_launch.cuh"
+#include "fwd_launch.cuh"
+
+namespace fa2 {
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+__device__ int g_status_word;   // set by kernels whose bounded wait ran out
+
+int* status_ptr() {
+  // Looked up per call: the address differs per device and the caller chooses the device.
+  int* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word) != cudaSuccess) return nullptr;
+  return p;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// Tensor map of a [B, S, H, D] operand (any strides, unit head-dim stride) viewed as the 5-D
+// tensor (64, S, D/64, H, B); one box is (64, rows, D/64, 1, 1) and lands in shared memory as
+// D/64 consecutive [rows][64] blocks with the 128-byte swizzle the MMA descriptors expect.
+int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, int D,
+              const fa2_strides& st, int box_rows, const char* what) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(FA2_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0)
+    return fail(FA2_ERR_UNSUPPORTED, "%s: pointer must be 16-byte aligned", what);
+  if ((st.b % 8) || (st.s % 8) || (st.h % 8))
+    return fail(FA2_ERR_UNSUPPORTED, "%s: strides must be multiples of 8 elements", what);
+  if (st.s <= 0 || (H > 1 && st.h <= 0) || (B > 1 && st.b <= 0))
+    return fail(FA2_ERR_INVALID_ARG, "%s: strides must be positive", what);
+  const cuuint64_t dims[5] = {64, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(D / 64),
+                              static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+  // A dimension of extent 1 still needs a legal (multiple of 16 bytes) stride.
+  const cuuint64_t sh = static_cast<cuuint64_t>(st.h > 0 ? st.h : D) * 2;
+  const cuuint64_t sb = static_cast<cuuint64_t>(st.b > 0 ? st.b : static_cast<int64_t>(D)) * 2;
+  const cuuint64_t strides[4] = {static_cast<cuuint64_t>(st.s) * 2, 128, sh, sb};
+  const cuuint32_t box[5] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(D / 64),
+                             1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUresult r =
+      enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+          const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(FA2_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what,
+                static_cast<int>(r));
+  return FA2_OK;
+}
+
+int check_problem(const fa2_problem& p) {
+  if (p.batch <= 0 || p.seqlen_q <= 0 || p.seqlen_k <= 0 || p.heads_q <= 0 || p.heads_kv <= 0)
+    return fail(FA2_ERR_INVALID_ARG, "batch, sequence lengths and head counts must be positive");
+  if (p.heads_q % p.heads_kv != 0)
+    return fail(FA2_ERR_INVALID_ARG, "query heads (%d) must be divisible by key/value heads (%d)",
+                p.heads_q, p.heads_kv);
+  if (p.dtype != FA2_FP16 && p.dtype != FA2_BF16)
+    return fail(FA2_ERR_UNSUPPORTED, "only fp16 and bf16 inputs are supported");
+  if (p.head_dim != 64 && p.head_dim != 128)
+    return fail(FA2_ERR_UNSUPPORTED, "head_dim %d is not supported (64 and 128 are)", p.head_dim);
+  if (!(p.dropout_p >= 0.f) || !(p.dropout_p < 1.f))
+    return fail(FA2_ERR_INVALID_ARG, "dropout_p must be in [0, 1)");
+  if (!std::isfinite(p.softmax_scale))
+    return fail(FA2_ERR_INVALID_ARG, "softmax_scale must be finite");
+  if (p.dropout_p > 0.f && (p.heads_q_global < p.head_offset + p.heads_q || p.batch_offset < 0 ||
+                            p.head_offset < 0))
+    return fail(FA2_ERR_INVALID_ARG, "dropout offsets: head_offset + heads_q exceeds heads_q_global");
+  return FA2_OK;
+}
+
+int make_score_term(ScoreTermDev* out, const fa2_score_term& t, const fa2_problem& p,
+                    const char* what) {
+  std::memset(out, 0, sizeof(*out));
+  if (!t.ptr) return FA2_OK;
+  if (t.dtype != p.dtype && t.dtype != FA2_FP32)
+    return fail(FA2_ERR_UNSUPPORTED, "%s: dtype must be the q dtype or fp32", what);
+  if (t.stride_b < 0 || t.stride_h < 0 || t.stride_q < 0)
+    return fail(FA2_ERR_INVALID_ARG, "%s: strides must be non-negative", what);
+  out->ptr = t.ptr;
+  out->sb = t.stride_b;
+  out->sh = t.stride_h;
+  out->sq = t.stride_q;
+  out->is_f32 = (t.dtype == FA2_FP32);
+  const int vec = out->is_f32 ? 4 : 8;
+  out->vec_ok = ((reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0) && (t.stride_b % vec == 0) &&
+                (t.stride_h % vec == 0) && (t.stride_q % vec == 0);
+  return FA2_OK;
+}
+
+void make_dropout(DropoutDev* d, const fa2_problem& p) {
+  std::memset(d, 0, sizeof(*d));
+  d->enabled = p.dropout_p > 0.f;
+  d->inv_keep = 1.f;
+  if (!d->enabled) return;
+  const double thr = std::floor(static_cast<double>(p.dropout_p) * 4294967296.0 + 0.5);
+  d->threshold = thr >= 4294967295.0 ? 0xffffffffu : static_cast<uint32_t>(thr);
+  d->inv_keep = static_cast<float>(1.0 / (1.0 - static_cast<double>(p.dropout_p)));
+  d->seed_lo = static_cast<uint32_t>(p.dropout_seed & 0xffffffffu);
+  d->seed_hi = static_cast<uint32_t>(p.dropout_seed >> 32);
+  d->b_off = p.batch_offset;
+  d->h_off = p.head_offset;
+  d->hq_global = p.heads_q_global;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct BwdWorkspace {
+  size_t delta_off, dq_off, total;
+  int sq_pad;
+};
+BwdWorkspace bwd_workspace(const fa2_problem& p) {
+  BwdWorkspace w;
+  w.sq_pad = (p.seqlen_q + 127) / 128 * 128;
+  const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * w.sq_pad;
+  w.delta_off = 0;
+  w.dq_off = align_up(rows * sizeof(float), 256);
+  w.total = w.dq_off + align_up(rows * p.head_dim * sizeof(float), 256);
+  return w;
+}
+
+}  // namespace
+}  // namespace fa2
+
+using namespace fa2;
+
+extern "C" {
+
+int fa2_version(void) { return 1000; }
+
+const char* fa2_last_error(void) { return g_err; }
+
+int fa2_debug_device_status(void* cuda_stream) {
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  int* dptr = status_ptr();
+  if (!dptr) return fail(FA2_ERR_CUDA, "status word is not addressable");
+  int v = 0;
+  if (cudaStreamSynchronize(stream) != cudaSuccess ||
+      cudaMemcpy(&v, dptr, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return fail(FA2_ERR_CUDA, "reading the status word failed: %s",
+                cudaGetErrorString(cudaGetLastError()));
+  if (v != 0) cudaMemset(dptr, 0, sizeof(int));
+  return v;
+}
+
+int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
+  if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
+  const fa2_problem& p = a->p;
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (!a->q || !a->k || !a->v || !a->o || !a->lse)
+    return fail(FA2_ERR_INVALID_ARG, "q, k, v, o and lse must be non-null");
+  if (a->lse_stride_h < p.seqlen_q || a->lse_stride_b < 0)
+    return fail(FA2_ERR_INVALID_ARG, "lse_stride_h must be at least seqlen_q");
+
+  FwdLaunch L;
+  std::memset(&L, 0, sizeof(L));
+  const bool bf16 = p.dtype == FA2_BF16;
+  const int D = p.head_dim;
+  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->q_strides, 128, "q")) ||
+      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->k_strides, 128, "k")) ||
+      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->v_strides, 128, "v")) ||
+      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->o_strides, 128, "o")))
+    return rc;
+
+  FwdKernelParams& kp = L.kp;
+  kp.B = p.batch; kp.Sq = p.seqlen_q; kp.Sk = p.seqlen_k;
+  kp.Hq = p.heads_q; kp.Hkv = p.heads_kv; kp.G = p.heads_q / p.heads_kv;
+  kp.causal_off = p.seqlen_k - p.seqlen_q;
+  kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
+  kp.lse = a->lse; kp.lse_sb = a->lse_stride_b; kp.lse_sh = a->lse_stride_h;
+  if ((rc = make_score_term(&kp.bias, a->bias, p, "bias")) ||
+      (rc = make_score_term(&kp.mask, a->mask, p, "mask")))
+    return rc;
+  make_dropout(&kp.drop, p);
+  kp.n_qblk = (p.seqlen_q + 255) / 256;
+  kp.status = status_ptr();
+  if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
+
+  L.head_dim = D;
+  L.bf16 = bf16;
+  L.causal = p.causal != 0;
+  // The plain path assumes a positive scale (it takes the row maximum before scaling).
+  L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled || !(p.softmax_scale > 0.f);
+
+  const cudaError_t e = launch_fwd(L, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess)
+    return fail(FA2_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
+  return FA2_OK;
+}
+
+size_t fa2_bwd_workspace_bytes(const fa2_problem* problem) {
+  if (!problem || check_problem(*problem)) return 0;
+  return bwd_workspace(*problem).total;
+}
+
+int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
+  if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
+  const fa2_problem& p = a->p;
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (!a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->dq || !a->dk || !a->dv)
+    return fail(FA2_ERR_INVALID_ARG, "q, k, v, o, d_o, lse, dq, dk and dv must be non-null");
+  if (a->lse_stride_h < p.seqlen_q || a->lse_stride_b < 0)
+    return fail(FA2_ERR_INVALID_ARG, "lse_stride_h must be at least seqlen_q");
+  const BwdWorkspace w = bwd_workspace(p);
+  if (!a->workspace || a->workspace_bytes < w.total)
+    return fail(FA2_ERR_WORKSPACE, "workspace must hold %zu bytes", w.total);
+  if (reinterpret_cast<uintptr_t>(a->workspace) & 255)
+    return fail(FA2_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+
+  BwdLaunch L;
+  std::memset(&L, 0, sizeof(L));
+  const bool bf16 = p.dtype == FA2_BF16;
+  const int D = p.head_dim;
+  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->q_strides, 128, "q")) ||
+      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->k_strides, 128, "k")) ||
+      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->v_strides, 128, "v")) ||
+      (rc = make_tmap(&L.tmdO, a->d_o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->do_strides, 128, "d_o")) ||
+      (rc = make_tmap(&L.tmdK, a->dk, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dk_strides, 128, "dk")) ||
+      (rc = make_tmap(&L.tmdV, a->dv, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dv_strides, 128, "dv")))
+    return rc;
+  if ((a->o_strides.b % 8) || (a->o_strides.s % 8) || (a->o_strides.h % 8) ||
+      (a->dq_strides.b % 8) || (a->dq_strides.s % 8) || (a->dq_strides.h % 8) ||
+      (reinterpret_cast<uintptr_t>(a->o) & 15) || (reinterpret_cast<uintptr_t>(a->dq) & 15))
+    return fail(FA2_ERR_UNSUPPORTED, "o / dq: 16-byte aligned pointers and strides in multiples of 8 are required");
+
+  BwdKernelParams& kp = L.kp;
+  kp.B = p.batch; kp.Sq = p.seqlen_q; kp.Sk = p.seqlen_k;
+  kp.Hq = p.heads_q; kp.Hkv = p.heads_kv; kp.G = p.heads_q / p.heads_kv;
+  kp.causal_off = p.seqlen_k - p.seqlen_q;
+  kp.scale = p.softmax_scale;
+  kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
+  kp.lse = a->lse; kp.lse_sb = a->lse_stride_b; kp.lse_sh = a->lse_stride_h;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  kp.delta = reinterpret_cast<float*>(ws + w.delta_off);
+  kp.dq_acc = reinterpret_cast<float*>(ws + w.dq_off);
+  kp.Sq_pad = w.sq_pad;
+  if ((rc = make_score_term(&kp.bias, a->bias, p, "bias")) ||
+      (rc = make_score_term(&kp.mask, a->mask, p, "mask")))
+    return rc;
+  make_dropout(&kp.drop, p);
+  kp.n_kvblk = (p.seqlen_k + 127) / 128;
+  kp.status = status_ptr();
+  if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
+
+  L.head_dim = D;
+  L.bf16 = bf16;
+  L.causal = p.causal != 0;
+  L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled;
+  L.o = a->o; L.o_strides[0] = a->o_strides.b; L.o_strides[1] = a->o_strides.s; L.o_strides[2] = a->o_strides.h;
+  L.d_o = a->d_o; L.do_strides[0] = a->do_strides.b; L.do_strides[1] = a->do_strides.s; L.do_strides[2] = a->do_strides.h;
+  L.dq = a->dq; L.dq_strides[0] = a->dq_strides.b; L.dq_strides[1] = a->dq_strides.s; L.dq_strides[2] = a->dq_strides.h;
+  L.delta = reinterpret_cast<float*>(ws + w.delta_off);
+  L.dq_acc_bytes = w.total - w.dq_off;
+
+  const cudaError_t e = launch_bwd(L, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess)
+    return fail(FA2_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
+  return FA2_OK;
+}
+
+}  // extern "C"

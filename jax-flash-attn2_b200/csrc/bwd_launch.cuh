@@ -1,0 +1,25 @@
+// Host-side launch record of the backward pass (pre-pass, main kernel, dq conversion).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "kernel_params.cuh"
+
+namespace fa2 {
+
+struct BwdLaunch {
+  CUtensorMap tmQ, tmK, tmV, tmdO, tmdK, tmdV;
+  BwdKernelParams kp;
+  int head_dim;
+  bool bf16, causal, feat;
+  const void* o;   long long o_strides[3];    // (batch, sequence, head) element strides
+  const void* d_o; long long do_strides[3];
+  void* dq;        long long dq_strides[3];
+  float* delta;    // start of the row-statistics area of the workspace
+  size_t dq_acc_bytes;
+};
+
+// Runs the three kernels of the backward pass on `stream`.
+cudaError_t launch_bwd(const BwdLaunch& a, cudaStream_t stream);
+
+}  // namespace fa2

@@ -1,0 +1,20 @@
+// Host-side launch records handed from the C-ABI layer to the kernel translation units.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "kernel_params.cuh"
+
+namespace fa2 {
+
+struct FwdLaunch {
+  CUtensorMap tmQ, tmK, tmV, tmO;
+  FwdKernelParams kp;
+  int head_dim;
+  bool bf16, causal, feat;
+};
+
+// Launches the forward kernel specialised for (head_dim, dtype, causal, score terms/dropout).
+cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream);
+
+}  // namespace fa2

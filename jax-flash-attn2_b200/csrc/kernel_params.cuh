@@ -1,0 +1,51 @@
+// Device-side parameter blocks shared by the host launcher and the kernels.
+#pragma once
+#include <cstdint>
+
+namespace fa2 {
+
+// Additive score term (bias or mask) as the kernels see it: element strides, j stride 1.
+struct ScoreTermDev {
+  const void* ptr;      // nullptr = absent
+  long long sb, sh, sq;
+  int is_f32;           // 1: float32 elements, 0: the 16-bit dtype of q
+  int vec_ok;           // 1: rows can be read with 16-byte loads (pointer and strides aligned)
+};
+
+struct DropoutDev {
+  uint32_t threshold;   // keep an element iff its 32-bit draw >= threshold
+  float inv_keep;       // 1 / (1 - p)
+  uint32_t seed_lo, seed_hi;
+  int b_off, h_off, hq_global;
+  int enabled;
+};
+
+struct FwdKernelParams {
+  int B, Sq, Sk, Hq, Hkv, G;
+  int causal_off;       // Sk - Sq: query row i may see key j iff j <= i + causal_off
+  float scale_log2;     // softmax_scale * log2(e)
+  float* lse;
+  long long lse_sb, lse_sh;
+  ScoreTermDev bias, mask;
+  DropoutDev drop;
+  int n_qblk;           // number of 256-row query blocks
+  int* status;          // device status word (bounded-wait time-outs)
+};
+
+struct BwdKernelParams {
+  int B, Sq, Sk, Hq, Hkv, G;
+  int causal_off;
+  float scale;          // softmax_scale
+  float scale_log2;     // softmax_scale * log2(e)
+  const float* lse;     // natural log, [B, Hq, >= Sq]
+  long long lse_sb, lse_sh;
+  const float* delta;   // rowsum(o * do), [B, Hq, Sq_pad]
+  float* dq_acc;        // fp32 [B, Hq, Sq_pad, D]
+  int Sq_pad;           // Sq rounded up to 128
+  ScoreTermDev bias, mask;
+  DropoutDev drop;
+  int n_kvblk;          // number of 128-row key blocks
+  int* status;
+};
+
+}  // namespace fa2

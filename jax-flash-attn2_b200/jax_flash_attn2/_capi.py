@@ -1,0 +1,135 @@
+"""ctypes binding of libfa2_b200.so (declared in include/fa2_b200.h).
+
+The structures mirror the C header field by field. Nothing here computes anything: if the
+library is missing the import of the kernels fails loudly, there is no fallback path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG_ROOT, "libfa2_b200.so")
+
+FA2_FP16, FA2_BF16, FA2_FP32 = 0, 1, 2
+FA2_OK = 0
+FA2_ERR_INVALID_ARG, FA2_ERR_UNSUPPORTED, FA2_ERR_CUDA, FA2_ERR_WORKSPACE = -1, -2, -3, -4
+
+EXPORTED_SYMBOLS = (
+    "fa2_fwd",
+    "fa2_bwd",
+    "fa2_bwd_workspace_bytes",
+    "fa2_last_error",
+    "fa2_version",
+    "fa2_debug_device_status",
+)
+
+
+class Strides(C.Structure):
+    _fields_ = [("b", C.c_int64), ("s", C.c_int64), ("h", C.c_int64)]
+
+
+class ScoreTerm(C.Structure):
+    _fields_ = [
+        ("ptr", C.c_void_p),
+        ("dtype", C.c_int32),
+        ("stride_b", C.c_int64),
+        ("stride_h", C.c_int64),
+        ("stride_q", C.c_int64),
+    ]
+
+
+class Problem(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32),
+        ("seqlen_q", C.c_int32),
+        ("seqlen_k", C.c_int32),
+        ("heads_q", C.c_int32),
+        ("heads_kv", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("dtype", C.c_int32),
+        ("causal", C.c_int32),
+        ("softmax_scale", C.c_float),
+        ("dropout_p", C.c_float),
+        ("dropout_seed", C.c_uint64),
+        ("batch_offset", C.c_int32),
+        ("head_offset", C.c_int32),
+        ("heads_q_global", C.c_int32),
+    ]
+
+
+class FwdParams(C.Structure):
+    _fields_ = [
+        ("p", Problem),
+        ("q", C.c_void_p), ("q_strides", Strides),
+        ("k", C.c_void_p), ("k_strides", Strides),
+        ("v", C.c_void_p), ("v_strides", Strides),
+        ("o", C.c_void_p), ("o_strides", Strides),
+        ("lse", C.c_void_p),
+        ("lse_stride_b", C.c_int64), ("lse_stride_h", C.c_int64),
+        ("bias", ScoreTerm),
+        ("mask", ScoreTerm),
+    ]
+
+
+class BwdParams(C.Structure):
+    _fields_ = [
+        ("p", Problem),
+        ("q", C.c_void_p), ("q_strides", Strides),
+        ("k", C.c_void_p), ("k_strides", Strides),
+        ("v", C.c_void_p), ("v_strides", Strides),
+        ("o", C.c_void_p), ("o_strides", Strides),
+        ("d_o", C.c_void_p), ("do_strides", Strides),
+        ("lse", C.c_void_p),
+        ("lse_stride_b", C.c_int64), ("lse_stride_h", C.c_int64),
+        ("bias", ScoreTerm),
+        ("mask", ScoreTerm),
+        ("dq", C.c_void_p), ("dq_strides", Strides),
+        ("dk", C.c_void_p), ("dk_strides", Strides),
+        ("dv", C.c_void_p), ("dv_strides", Strides),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class Fa2Error(RuntimeError):
+    """A call into libfa2_b200.so returned a non-zero status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"fa2_b200 error {code}: {message}")
+        self.code = code
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library once and declares the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python {os.path.join(_PKG_ROOT, 'build.py')}`. "
+            "There is no fallback implementation."
+        )
+    lib = C.CDLL(LIB_PATH)
+    lib.fa2_fwd.argtypes = [C.POINTER(FwdParams), C.c_void_p]
+    lib.fa2_fwd.restype = C.c_int
+    lib.fa2_bwd.argtypes = [C.POINTER(BwdParams), C.c_void_p]
+    lib.fa2_bwd.restype = C.c_int
+    lib.fa2_bwd_workspace_bytes.argtypes = [C.POINTER(Problem)]
+    lib.fa2_bwd_workspace_bytes.restype = C.c_size_t
+    lib.fa2_last_error.argtypes = []
+    lib.fa2_last_error.restype = C.c_char_p
+    lib.fa2_version.argtypes = []
+    lib.fa2_version.restype = C.c_int
+    lib.fa2_debug_device_status.argtypes = [C.c_void_p]
+    lib.fa2_debug_device_status.restype = C.c_int
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    if code != FA2_OK:
+        raise Fa2Error(code, load().fa2_last_error().decode("utf-8", "replace"))

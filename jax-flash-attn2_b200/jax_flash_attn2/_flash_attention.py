@@ -1,0 +1,72 @@
+"""Differentiable attention op over the CUDA kernels.
+
+Mirrors the structure of the reference's `flash_attention_call` custom_vjp
+(jax_flash_attn2/flash_attention_triton/_flash_attention.py:27-157): the forward saves
+(q, k, v, bias, attention_mask, out, lse, dropout_seed); the backward returns gradients for
+q, k and v only (bias, mask and seed get none). torch.autograd.Function plays the part of
+jax.custom_vjp because JAX is not available where this library is built and tested.
+"""
+from __future__ import annotations
+
+import typing as tp
+
+import torch
+
+from ._kernel_calls import (
+    bwd_attention_kernel_call,
+    fwd_attention_kernel_call,
+    normalise_attention_mask,
+)
+
+
+class _FlashAttentionCall(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard):
+        out, lse = fwd_attention_kernel_call(
+            q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, **shard
+        )
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.extras = (attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard)
+        return out
+
+    @staticmethod
+    def backward(ctx, dO):
+        q, k, v, out, lse = ctx.saved_tensors
+        attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard = ctx.extras
+        dq, dk, dv = bwd_attention_kernel_call(
+            dO, q, k, v, bias, attention_mask, out, lse, dropout_prob, causal, softmax_scale, dropout_seed, **shard
+        )
+        return dq, dk, dv, None, None, None, None, None, None, None
+
+
+def flash_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    attention_mask: tp.Optional[torch.Tensor] = None,
+    bias: tp.Optional[torch.Tensor] = None,
+    softmax_scale: tp.Optional[float] = None,
+    dropout_prob: float = 0.0,
+    causal: bool = False,
+    dropout_seed: tp.Optional[int] = None,
+    varlen_mode: bool = True,
+    *,
+    batch_offset: int = 0,
+    head_offset: int = 0,
+    heads_q_global: tp.Optional[int] = None,
+) -> torch.Tensor:
+    """Same signature as the reference's `triton_flash_attention`
+    (flash_attention_triton/_flash_attention.py:125-157). `varlen_mode` is accepted for
+    compatibility: a 2-D padding mask is always honoured (keys masked, padded rows zeroed).
+    The three keyword-only arguments place a shard inside the unsharded problem so that dropout
+    draws the same bits on every partitioning."""
+    del varlen_mode
+    sq, sk = q.shape[1], k.shape[1]
+    add_mask, row_keep = normalise_attention_mask(attention_mask, q.dtype, sq, sk)
+    shard = dict(batch_offset=batch_offset, head_offset=head_offset, heads_q_global=heads_q_global)
+    out = _FlashAttentionCall.apply(
+        q, k, v, add_mask, bias, softmax_scale, float(dropout_prob), bool(causal), dropout_seed, shard
+    )
+    if row_keep is not None:
+        out = out * row_keep[:, :, None, None].to(out.dtype)
+    return out

@@ -1,0 +1,220 @@
+"""Host launchers of the CUDA kernels, on torch CUDA tensors.
+
+These two functions stand where the reference has `_fwd_attention_kernel_call`
+(jax_flash_attn2/flash_attention_triton/_forward_triton.py:462-592) and
+`_bwd_attention_kernel_call` (jax_flash_attn2/flash_attention_triton/_backward_triton.py:948-1173):
+same argument meaning, same checks, same error behaviour (assertion / ValueError before any
+launch). torch is used for device memory and streams only; all arithmetic happens in
+libfa2_b200.so. There is no fallback: without the library or without a GPU these raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import typing as tp
+
+import torch
+
+from . import _capi
+
+_DTYPE_CODE = {torch.float16: _capi.FA2_FP16, torch.bfloat16: _capi.FA2_BF16, torch.float32: _capi.FA2_FP32}
+
+
+def _strides(x: torch.Tensor) -> _capi.Strides:
+    """(batch, sequence, head) element strides of a [B, S, H, D] tensor."""
+    return _capi.Strides(x.stride(0), x.stride(1), x.stride(2))
+
+
+def _unit_last(x: torch.Tensor) -> torch.Tensor:
+    return x if x.stride(-1) == 1 else x.contiguous()
+
+
+def _score_term(x: tp.Optional[torch.Tensor], batch: int, heads: int, sq: int, sk: int, name: str):
+    """Broadcast rules of calc_bias_strides (flash_attention_triton/_utils.py:151-193): batch in
+    {1, B}, heads in {1, Hq}, the two sequence dims equal to (Sq, Sk); additionally the query dim
+    may be 1 (a key-padding term). Returns (ScoreTerm, tensor kept alive)."""
+    term = _capi.ScoreTerm()
+    if x is None:
+        return term, None
+    if x.dim() != 4:
+        raise ValueError(f"{name} must have four dimensions, got shape {tuple(x.shape)}")
+    if x.dtype not in _DTYPE_CODE:
+        raise ValueError(f"{name} has unsupported dtype {x.dtype}")
+    bb, bh, bq, bk = x.shape
+    if bb not in (1, batch):
+        raise ValueError(f"{name} batch size must be {batch} or 1, got {bb}")
+    if bh not in (1, heads):
+        raise ValueError(f"{name} heads must be {heads} or 1, got {bh}")
+    if bq not in (1, sq) or bk != sk:
+        raise ValueError(f"{name} sequence dims must be ({sq}, {sk}), got ({bq}, {bk})")
+    x = _unit_last(x)
+    term.ptr = x.data_ptr()
+    term.dtype = _DTYPE_CODE[x.dtype]
+    term.stride_b = 0 if bb == 1 else x.stride(0)
+    term.stride_h = 0 if bh == 1 else x.stride(1)
+    term.stride_q = 0 if bq == 1 else x.stride(2)
+    return term, x
+
+
+def normalise_attention_mask(
+    attention_mask: tp.Optional[torch.Tensor], dtype: torch.dtype, sq: int, sk: int
+) -> tp.Tuple[tp.Optional[torch.Tensor], tp.Optional[torch.Tensor]]:
+    """Turns the accepted mask forms into an additive term.
+
+    * 4-D floating mask [B, 1|Hq, Sq, Sk] (0 keeps, finfo.min / -inf drops): used as is.
+    * 4-D bool / integer mask (non-zero keeps): converted to 0 / -inf.
+    * 2-D [B, S] padding mask (non-zero = real token): the reference's meaning of
+      `attention_mask` (_forward_triton.py:474-479). Becomes a key-padding term [B,1,1,Sk];
+      the second return value is the [B, Sq] row mask with which the caller zeroes the padded
+      query rows, as the reference's unpacking does.
+    """
+    if attention_mask is None:
+        return None, None
+    m = attention_mask
+    if m.dim() == 2:
+        if sq != sk:
+            raise AssertionError("Attention mask is not supported with QSeq != KSeq")
+        keep = m != 0
+        add = torch.zeros(m.shape, dtype=torch.float32, device=m.device)
+        add.masked_fill_(~keep, float("-inf"))
+        return add[:, None, None, :].contiguous(), keep
+    if m.dim() != 4:
+        raise ValueError(f"attention_mask must be 2-D or 4-D, got shape {tuple(m.shape)}")
+    if m.is_floating_point():
+        return m, None
+    add = torch.zeros(m.shape, dtype=dtype, device=m.device)
+    add.masked_fill_(m == 0, float("-inf"))
+    return add, None
+
+
+def _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offset, head_offset, heads_q_global):
+    batch, sq, hq, d = q.shape
+    _, sk, hkv, _ = k.shape
+    p = _capi.Problem()
+    p.batch, p.seqlen_q, p.seqlen_k = batch, sq, sk
+    p.heads_q, p.heads_kv, p.head_dim = hq, hkv, d
+    p.dtype = _DTYPE_CODE[q.dtype]
+    p.causal = int(bool(causal))
+    p.softmax_scale = float(1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale)
+    p.dropout_p = float(dropout_prob)
+    p.dropout_seed = int(0 if dropout_seed is None else dropout_seed) & 0xFFFFFFFFFFFFFFFF
+    p.batch_offset = int(batch_offset)
+    p.head_offset = int(head_offset)
+    p.heads_q_global = int(hq if heads_q_global is None else heads_q_global)
+    return p
+
+
+def _check_qkv(q, k, v):
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("fa2_b200 runs on CUDA tensors only; there is no CPU path")
+    batch, sq, hq, d = q.shape
+    _, sk, hkv, _ = k.shape
+    expected = (batch, sk, hkv, d)
+    assert tuple(k.shape) == expected, f"key shape is {tuple(k.shape)} and we excepted it to be like {expected}"
+    assert tuple(v.shape) == expected, f"value shape is {tuple(v.shape)} and we excepted it to be like {expected}"
+    assert hq % hkv == 0, f"nheads_q = {hq} is not divisible by nheads_kv = {hkv}"
+    assert q.dtype == k.dtype == v.dtype, "All tensors must have the same type"
+    assert q.dtype in (torch.float16, torch.bfloat16), "Only support fp16 and bf16"
+
+
+def fwd_attention_kernel_call(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    attention_mask: tp.Optional[torch.Tensor] = None,
+    bias: tp.Optional[torch.Tensor] = None,
+    softmax_scale: tp.Optional[float] = None,
+    dropout_prob: float = 0.0,
+    causal: bool = False,
+    dropout_seed: tp.Optional[int] = None,
+    *,
+    batch_offset: int = 0,
+    head_offset: int = 0,
+    heads_q_global: tp.Optional[int] = None,
+) -> tp.Tuple[torch.Tensor, torch.Tensor]:
+    """Forward launch. q [B,Sq,Hq,D]; k, v [B,Sk,Hkv,D]; `attention_mask` here is already an
+    additive 4-D term (see normalise_attention_mask). Returns (out [B,Sq,Hq,D] in q.dtype,
+    lse [B,Hq,ceil(Sq/128)*128] float32, natural log; columns >= Sq are not written)."""
+    _check_qkv(q, k, v)
+    lib = _capi.load()
+    q, k, v = _unit_last(q), _unit_last(k), _unit_last(v)
+    batch, sq, hq, d = q.shape
+    sk = k.shape[1]
+    out = torch.empty((batch, sq, hq, d), dtype=q.dtype, device=q.device)
+    sq_rounded = (sq + 127) // 128 * 128
+    lse = torch.empty((batch, hq, sq_rounded), dtype=torch.float32, device=q.device)
+
+    a = _capi.FwdParams()
+    a.p = _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offset, head_offset, heads_q_global)
+    a.q, a.q_strides = q.data_ptr(), _strides(q)
+    a.k, a.k_strides = k.data_ptr(), _strides(k)
+    a.v, a.v_strides = v.data_ptr(), _strides(v)
+    a.o, a.o_strides = out.data_ptr(), _strides(out)
+    a.lse, a.lse_stride_b, a.lse_stride_h = lse.data_ptr(), lse.stride(0), lse.stride(1)
+    a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias")
+    a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _capi.check(lib.fa2_fwd(C.byref(a), C.c_void_p(stream)))
+    return out, lse
+
+
+def bwd_attention_kernel_call(
+    dO: torch.Tensor,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    bias: tp.Optional[torch.Tensor],
+    attention_mask: tp.Optional[torch.Tensor],
+    o: torch.Tensor,
+    M: torch.Tensor,
+    dropout_prob: float,
+    causal: bool,
+    softmax_scale: tp.Optional[float],
+    dropout_seed: tp.Optional[int],
+    *,
+    batch_offset: int = 0,
+    head_offset: int = 0,
+    heads_q_global: tp.Optional[int] = None,
+) -> tp.Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward launch; `M` is the lse returned by the forward. Returns (dq, dk, dv) in the input
+    dtype; dk and dv are already reduced over the query heads of each key/value head."""
+    _check_qkv(q, k, v)
+    lib = _capi.load()
+    q, k, v, o, dO = map(_unit_last, (q, k, v, o, dO))
+    batch, sq, hq, d = q.shape
+    sk = k.shape[1]
+    assert tuple(dO.shape) == tuple(q.shape) and tuple(o.shape) == tuple(q.shape)
+    assert dO.dtype == q.dtype and o.dtype == q.dtype
+    dq = torch.empty_like(q, memory_format=torch.contiguous_format)
+    dk = torch.empty_like(k, memory_format=torch.contiguous_format)
+    dv = torch.empty_like(v, memory_format=torch.contiguous_format)
+
+    a = _capi.BwdParams()
+    a.p = _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offset, head_offset, heads_q_global)
+    nbytes = lib.fa2_bwd_workspace_bytes(C.byref(a.p))
+    if nbytes == 0:
+        _capi.check(_capi.FA2_ERR_INVALID_ARG)
+    workspace = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
+    a.q, a.q_strides = q.data_ptr(), _strides(q)
+    a.k, a.k_strides = k.data_ptr(), _strides(k)
+    a.v, a.v_strides = v.data_ptr(), _strides(v)
+    a.o, a.o_strides = o.data_ptr(), _strides(o)
+    a.d_o, a.do_strides = dO.data_ptr(), _strides(dO)
+    a.lse, a.lse_stride_b, a.lse_stride_h = M.data_ptr(), M.stride(0), M.stride(1)
+    a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias")
+    a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
+    a.dq, a.dq_strides = dq.data_ptr(), _strides(dq)
+    a.dk, a.dk_strides = dk.data_ptr(), _strides(dk)
+    a.dv, a.dv_strides = dv.data_ptr(), _strides(dv)
+    a.workspace, a.workspace_bytes = workspace.data_ptr(), nbytes
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        _capi.check(lib.fa2_bwd(C.byref(a), C.c_void_p(stream)))
+    return dq, dk, dv
+
+
+def device_status() -> int:
+    """Reads (and clears) the status word a kernel sets when one of its bounded waits ran out."""
+    lib = _capi.load()
+    return int(lib.fa2_debug_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream)))
