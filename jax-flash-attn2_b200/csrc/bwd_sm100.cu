@@ -1,4 +1,619 @@
+// Backward attention kernels for sm_100a.
+//
+// Replace the reference's _attn_bwd_preprocess (jax_flash_attn2/flash_attention_triton/
+// _backward_triton.py:79-147), _attn_bwd with its dk/dv and dq halves (:150-945) and the
+// per-group reduction of dk / dv done afterwards in XLA (:1156-1161).
+//
+// Three launches:
+//   1. bwd_pre_kernel   : delta = rowsum(o * do), lse converted to base 2, both padded to 128
+//                         rows per tile; zeroes the fp32 dq accumulator. HBM-bound.
+//   2. bwd_main_kernel  : one CTA per (batch, kv head, 128-key tile). It keeps K and V in shared
+//                         memory, walks over the query heads of the group and their query tiles,
+//                         and runs five tcgen05 GEMMs per step, in the transposed form where the
+//                         TMEM lane is the key row:
+//                           S^T  = K Q^T          dP^T = V dO^T
+//                           dV  += P^T dO         (P^T read from tensor memory)
+//                           dK  += dS^T Q         (dS^T staged in shared memory)
+//                           dQ_i = dS K           (fresh per step, reduced into fp32 global)
+//                         dK / dV accumulate in tensor memory over the whole group, so there is
+//                         no per-query-head temporary and no second reduction.
+//   3. bwd_dq_convert   : fp32 dq accumulator (tiled layout) * scale -> dq in the input dtype.
 #include "bwd_launch.cuh"
+#include "ptx_sm100.cuh"
+
 namespace fa2 {
-cudaError_t launch_bwd(const BwdLaunch&, cudaStream_t) { return cudaErrorNotSupported; }
+
+namespace {
+
+constexpr int kBM = 128;   // query rows per step
+constexpr int kBN = 128;   // keys per CTA
+constexpr int kThreads = 448;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kMaxDynSmem = 232448;
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kTileBytes = 128 * D * 2;
+  static constexpr int kBlockBytes = 128 * 128;   // one [128 rows][64 elements] block
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kKOff + kTileBytes;
+  static constexpr int kQOff = kVOff + kTileBytes;         // 2 stages
+  static constexpr int kdOOff = kQOff + 2 * kTileBytes;    // 2 stages
+  static constexpr int kdSOff = kdOOff + 2 * kTileBytes;   // [128 keys][128 queries] 16 bit
+  static constexpr int kStatsOff = kdSOff + 128 * 128 * 2; // 2 stages x (lse2[128], delta[128])
+  static constexpr int kBarOff = kStatsOff + 2 * 1024;
+  static constexpr int kNumBars = 16;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kDynamicBytes = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
+  static_assert(kTotal <= kMaxDynSmem, "shared memory budget exceeded");
+};
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
 }
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+template <bool kBf16>
+__device__ __forceinline__ float load_term(const ScoreTermDev& t, long long idx) {
+  if (t.is_f32) return __ldg(static_cast<const float*>(t.ptr) + idx);
+  return to_float16bit<kBf16>(__ldg(static_cast<const uint16_t*>(t.ptr) + idx));
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// 1. pre-pass
+// ---------------------------------------------------------------------------------------------
+// stats layout: [B, Hq, nQ, 2, 128] float: (lse * log2e | +inf for rows that take no gradient,
+// delta). dq_acc layout: [B, Hq, nQ, D/4, 128, 4] float.
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(128)
+bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
+               long long o_sb, long long o_ss, long long o_sh, long long do_sb, long long do_ss,
+               long long do_sh, const float* __restrict__ lse, long long lse_sb, long long lse_sh,
+               float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ) {
+  const int i = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / Hq, h = bh - b * Hq;
+  const int tid = threadIdx.x;
+  constexpr int kLanesPerRow = D / 8;            // 16-byte loads
+  constexpr int kRowsPerPass = 128 / kLanesPerRow;
+  const int sub = tid % kLanesPerRow;
+  const long long tile = (static_cast<long long>(bh) * nQ + i);
+  float* st = stats + tile * 256;
+  for (int r0 = 0; r0 < kBM; r0 += kRowsPerPass) {
+    const int r = r0 + tid / kLanesPerRow;
+    const int row = i * kBM + r;
+    float acc = 0.f;
+    if (row < Sq) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + b * o_sb + row * o_ss + h * o_sh) + sub);
+      const uint4 g = __ldg(reinterpret_cast<const uint4*>(d_o + b * do_sb + row * do_ss + h * do_sh) + sub);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        acc = fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(aw[k] & 0xffff)),
+                   to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] & 0xffff)), acc);
+        acc = fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(aw[k] >> 16)),
+                   to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] >> 16)), acc);
+      }
+    }
+#pragma unroll
+    for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
+      acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (sub == 0) {
+      float l2 = INFINITY;
+      if (row < Sq) {
+        const float l = lse[b * lse_sb + h * lse_sh + row];
+        if (l > -INFINITY && l < INFINITY) l2 = l * kLog2e;
+      }
+      st[r] = l2;
+      st[128 + r] = (row < Sq) ? acc : 0.f;
+    }
+  }
+  float4* acc4 = reinterpret_cast<float4*>(dq_acc + tile * (kBM * D));
+  for (int k = tid; k < kBM * D / 4; k += 128) acc4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+// ---------------------------------------------------------------------------------------------
+// 3. dq conversion
+// ---------------------------------------------------------------------------------------------
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(128)
+bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long long sb,
+               long long ss, long long sh, int Sq, int Hq, int nQ, float scale) {
+  const int i = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / Hq, h = bh - b * Hq;
+  const int r = threadIdx.x;
+  const int row = i * kBM + r;
+  if (row >= Sq) return;
+  const float4* src = reinterpret_cast<const float4*>(dq_acc) +
+                      (static_cast<long long>(bh) * nQ + i) * (kBM * D / 4) + r;
+  uint4* dst = reinterpret_cast<uint4*>(dq + b * sb + row * ss + h * sh);
+#pragma unroll
+  for (int c8 = 0; c8 < D / 8; ++c8) {
+    const float4 x = src[(2 * c8) * 128];
+    const float4 y = src[(2 * c8 + 1) * 128];
+    uint4 v;
+    v.x = pack2<kBf16>(x.x * scale, x.y * scale);
+    v.y = pack2<kBf16>(x.z * scale, x.w * scale);
+    v.z = pack2<kBf16>(y.x * scale, y.y * scale);
+    v.w = pack2<kBf16>(y.z * scale, y.w * scale);
+    dst[c8] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2. main kernel
+// ---------------------------------------------------------------------------------------------
+template <int D, bool kBf16, bool kCausal, bool kFeat>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
+                const float* __restrict__ stats, const BwdKernelParams p) {
+  using L = BwdSmem<D>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t pad = smem_base - smem_u32(smem_raw);
+  if (pad + L::kTotal > static_cast<uint32_t>(L::kDynamicBytes)) {
+    if (threadIdx.x == 0) atomicOr(p.status, 64);
+    return;
+  }
+  uint8_t* smem_gen = smem_raw + pad;
+
+  const uint32_t sK = smem_base + L::kKOff, sV = smem_base + L::kVOff;
+  const uint32_t sQ = smem_base + L::kQOff, sdO = smem_base + L::kdOOff;
+  const uint32_t sdS = smem_base + L::kdSOff, sStats = smem_base + L::kStatsOff;
+  const uint32_t bars = smem_base + L::kBarOff;
+  const uint32_t bar_kv_full = bars;
+  auto bar_q_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto bar_do_full = [&](int s) { return bars + 8u * (3 + s); };
+  auto bar_q_empty = [&](int s) { return bars + 8u * (5 + s); };
+  auto bar_do_empty = [&](int s) { return bars + 8u * (7 + s); };
+  const uint32_t bar_s_full = bars + 8u * 9, bar_p_full = bars + 8u * 10;
+  const uint32_t bar_dp_full = bars + 8u * 11, bar_ds_full = bars + 8u * 12;
+  const uint32_t bar_dq_full = bars + 8u * 13, bar_dq_drained = bars + 8u * 14;
+  const uint32_t bar_dkv_full = bars + 8u * 15;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- work item: (batch, kv head, key tile); later key tiles (fewest steps when causal) last
+  const int n = blockIdx.x % p.n_kvblk;
+  const int bhk = blockIdx.x / p.n_kvblk;
+  const int b = bhk / p.Hkv;
+  const int hk = bhk - b * p.Hkv;
+  const int nQ = (p.Sq + kBM - 1) / kBM;
+  int i_start = 0;
+  if (kCausal) {
+    const int first_row = n * kBN - p.causal_off;   // first query row that sees key n*128
+    i_start = first_row > 0 ? first_row / kBM : 0;
+    if (i_start > nQ) i_start = nQ;
+  }
+  const int nI = nQ - i_start;          // query tiles per head
+  const int T = nI * p.G;               // steps of this CTA
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_q_full(s), 1);
+      mbar_init(bar_do_full(s), 1);
+      mbar_init(bar_q_empty(s), 1);
+      mbar_init(bar_do_empty(s), 1);
+    }
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, 256);
+    mbar_init(bar_dp_full, 1);
+    mbar_init(bar_ds_full, 256);
+    mbar_init(bar_dq_full, 1);
+    mbar_init(bar_dq_drained, 128);
+    mbar_init(bar_dkv_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 13 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColS = 0, kColdP = 128, kColdK = 256, kColdV = 256 + D;
+  constexpr uint32_t kColdQ = (D == 128) ? 128 : 384;
+
+  auto step_coords = [&](int it, int& h, int& i) {
+    const int g = it / nI;
+    i = i_start + (it - g * nI);
+    h = hk * p.G + g;
+  };
+
+  if (warp == 13) {
+    // =========================== TMA producer ================================================
+    if (lane == 0 && T > 0) {
+      mbar_arrive_expect_tx(bar_kv_full, 2 * L::kTileBytes);
+      tma_load_5d(sK, &tmK, bar_kv_full, 0, n * kBN, 0, hk, b);
+      tma_load_5d(sV, &tmV, bar_kv_full, 0, n * kBN, 0, hk, b);
+      bool ok = true;
+      for (int it = 0; it < T && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t par = ((it >> 1) & 1) ^ 1;
+        int h, i;
+        step_coords(it, h, i);
+        ok = mbar_wait(bar_q_empty(st), par, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_q_full(st), L::kTileBytes + 1024);
+        tma_load_5d(sQ + st * L::kTileBytes, &tmQ, bar_q_full(st), 0, i * kBM, 0, h, b);
+        bulk_load_1d(sStats + st * 1024,
+                     stats + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * 256, 1024,
+                     bar_q_full(st));
+        ok = mbar_wait(bar_do_empty(st), par, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_do_full(st), L::kTileBytes);
+        tma_load_5d(sdO + st * L::kTileBytes, &tmdO, bar_do_full(st), 0, i * kBM, 0, h, b);
+      }
+      if (!ok) atomicOr(p.status, 8);
+    }
+    __syncwarp();
+  } else if (warp == 12) {
+    // =========================== MMA issuer ==================================================
+    if (lane == 0 && T > 0) {
+      constexpr uint32_t idesc_s = make_idesc(kBf16, 128, 128, false, false);
+      constexpr uint32_t idesc_dv = make_idesc(kBf16, 128, D, false, true);
+      constexpr uint32_t idesc_dk = make_idesc(kBf16, 128, D, false, true);
+      constexpr uint32_t idesc_dq = make_idesc(kBf16, 128, D, true, true);
+      bool ok = true;
+
+      // D[kv, q] = A[kv, d] * B[q, d]^T, both operands K-major over the head dim
+      auto issue_kd = [&](uint32_t d_col, uint32_t a0, uint32_t b0) {
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
+          mma_ss(tmem_base + d_col, make_sdesc(a0 + off, 16, 1024), make_sdesc(b0 + off, 16, 1024),
+                 idesc_s, k > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_dv = [&](uint32_t do_tile, bool first) {
+#pragma unroll
+        for (int k = 0; k < kBM / 16; ++k) {
+          // P^T for queries [16k, 16k+16): 8 packed columns; the two 64-query halves were written
+          // by different warpgroups at columns 0 and 64 of the S region.
+          const uint32_t a_col = kColS + (k < 4 ? 8 * k : 64 + 8 * (k - 4));
+          mma_ts(tmem_base + kColdV, tmem_base + a_col,
+                 make_sdesc(do_tile + k * 2048, L::kBlockBytes, 1024), idesc_dv,
+                 (first && k == 0) ? 0u : 1u);
+        }
+      };
+      auto issue_dk = [&](uint32_t q_tile, bool first) {
+#pragma unroll
+        for (int k = 0; k < kBM / 16; ++k) {
+          const uint32_t a_off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
+          mma_ss(tmem_base + kColdK, make_sdesc(sdS + a_off, 16, 1024),
+                 make_sdesc(q_tile + k * 2048, L::kBlockBytes, 1024), idesc_dk,
+                 (first && k == 0) ? 0u : 1u);
+        }
+      };
+      auto issue_dq = [&]() {
+#pragma unroll
+        for (int k = 0; k < kBN / 16; ++k) {
+          // A = dS (M = query, contiguous in the dS^T rows; K = key rows), B = K tile, both MN-major
+          mma_ss(tmem_base + kColdQ, make_sdesc(sdS + k * 2048, L::kBlockBytes, 1024),
+                 make_sdesc(sK + k * 2048, L::kBlockBytes, 1024), idesc_dq, k > 0 ? 1u : 0u);
+        }
+      };
+
+      ok = mbar_wait(bar_kv_full, 0, abort_flag);
+      if (ok) ok = mbar_wait(bar_q_full(0), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_kd(kColS, sK, sQ);
+        mma_commit(bar_s_full);
+        ok = mbar_wait(bar_do_full(0), 0, abort_flag);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_kd(kColdP, sV, sdO);
+        mma_commit(bar_dp_full);
+      }
+      for (int it = 0; it < T && ok; ++it) {
+        const int st = it & 1, nx = st ^ 1;
+        const uint32_t par = it & 1;
+        const uint32_t par_next = ((it + 1) >> 1) & 1;
+        const bool has_next = it + 1 < T;
+        ok = mbar_wait(bar_p_full, par, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dv(sdO + st * L::kTileBytes, it == 0);
+        if (has_next) {
+          ok = mbar_wait(bar_q_full(nx), par_next, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_kd(kColS, sK, sQ + nx * L::kTileBytes);
+          mma_commit(bar_s_full);
+        }
+        ok = mbar_wait(bar_ds_full, par, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dk(sQ + st * L::kTileBytes, it == 0);
+        issue_dq();
+        mma_commit(bar_dq_full);
+        mma_commit(bar_q_empty(st));
+        mma_commit(bar_do_empty(st));
+        if (has_next) {
+          ok = mbar_wait(bar_dq_drained, par, abort_flag);
+          if (ok) ok = mbar_wait(bar_do_full(nx), par_next, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_kd(kColdP, sV, sdO + nx * L::kTileBytes);
+          mma_commit(bar_dp_full);
+        }
+      }
+      if (ok) mma_commit(bar_dkv_full);
+      if (!ok) atomicOr(p.status, 16);
+    }
+    __syncwarp();
+  } else if (warp >= 8) {
+    // =========================== dQ drain ====================================================
+    const int r = tid - 256;   // query row inside the tile == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tdQ = tmem_base + lane_base + kColdQ;
+    bool ok = true;
+    for (int it = 0; it < T; ++it) {
+      int h, i;
+      step_coords(it, h, i);
+      ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      float* dst = p.dq_acc + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * (kBM * D) + r * 4;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tdQ + c * 32, v);
+        tc_wait_ld();
+        if (c == D / 32 - 1) {
+          tc_fence_before();
+          mbar_arrive(bar_dq_drained);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4)
+          red_add_v4(dst + (c * 8 + q4) * (128 * 4), __uint_as_float(v[4 * q4]),
+                     __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
+                     __uint_as_float(v[4 * q4 + 3]));
+      }
+    }
+    if (!ok && r == 0) atomicOr(p.status, 32);
+  } else {
+    // =========================== P / dS warps + dK, dV epilogue ==============================
+    const int w = warp >> 2;            // 0: queries [0,64) of each tile, dK; 1: [64,128), dV
+    const int r = tid & 127;            // key row inside the tile == TMEM lane
+    const int kv = n * kBN + r;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + kColS + 64 * w;
+    const uint32_t tdP = tmem_base + lane_base + kColdP + 64 * w;
+    const float* stats_s = reinterpret_cast<const float*>(smem_gen + L::kStatsOff);
+    uint8_t* ds_row = smem_gen + L::kdSOff + w * L::kBlockBytes + r * 128;
+    bool ok = true;
+
+    for (int it = 0; it < T; ++it) {
+      const int st = it & 1;
+      int h, i;
+      step_coords(it, h, i);
+      const float* lse2 = stats_s + st * 256 + 64 * w;
+      const float* delta = lse2 + 128;
+      const int q_first = i * kBM + 64 * w;
+      ok = mbar_wait(bar_q_full(st), (it >> 1) & 1, abort_flag);
+      if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      // some (query, key) pairs of this step are above the causal diagonal
+      const bool diag = kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off);
+      float pv[64];
+      uint32_t keep_bits[2] = {0xffffffffu, 0xffffffffu};
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32];
+        tmem_ld32(tS + 32 * half, s);
+        tc_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int col = 32 * half + c;
+          const int qi = q_first + col;
+          float x = __uint_as_float(s[c]) * p.scale_log2;
+          if constexpr (kFeat) {
+            if (qi < p.Sq && kv < p.Sk) {
+              if (p.bias.ptr)
+                x = fmaf(load_term<kBf16>(p.bias, b * p.bias.sb + h * p.bias.sh +
+                                                      static_cast<long long>(qi) * p.bias.sq + kv),
+                         kLog2e, x);
+              if (p.mask.ptr)
+                x = fmaf(load_term<kBf16>(p.mask, b * p.mask.sb + h * p.mask.sh +
+                                                      static_cast<long long>(qi) * p.mask.sq + kv),
+                         kLog2e, x);
+            }
+          }
+          float pe = ex2_approx(x - lse2[col]);
+          if (diag && kv > qi + p.causal_off) pe = 0.f;
+          pv[col] = pe;
+        }
+        uint32_t pk[16];
+        if constexpr (kFeat) {
+          if (p.drop.enabled) {
+            const uint32_t bh_glob =
+                static_cast<uint32_t>((p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
+            uint32_t bits = 0;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              uint32_t rnd[4];
+              philox4x32_10(static_cast<uint32_t>(kv >> 2),
+                            static_cast<uint32_t>(q_first + 32 * half + c), bh_glob, 0u,
+                            p.drop.seed_lo, p.drop.seed_hi, rnd);
+              const uint32_t sel = (kv & 3) == 0 ? rnd[0] : (kv & 3) == 1 ? rnd[1]
+                                   : (kv & 3) == 2 ? rnd[2] : rnd[3];
+              if (sel >= p.drop.threshold) bits |= (1u << c);
+            }
+            keep_bits[half] = bits;
+          }
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float a0 = ((keep_bits[half] >> (2 * c)) & 1u) ? pv[32 * half + 2 * c] * p.drop.inv_keep : 0.f;
+            const float a1 = ((keep_bits[half] >> (2 * c + 1)) & 1u) ? pv[32 * half + 2 * c + 1] * p.drop.inv_keep : 0.f;
+            pk[c] = pack2<kBf16>(a0, a1);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            pk[c] = pack2<kBf16>(pv[32 * half + 2 * c], pv[32 * half + 2 * c + 1]);
+        }
+        tmem_st16(tS + 16 * half, pk);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p_full);
+
+      ok = mbar_wait(bar_dp_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t dp[32];
+        tmem_ld32(tdP + 32 * half, dp);
+        tc_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float d0 = __uint_as_float(dp[2 * c]), d1 = __uint_as_float(dp[2 * c + 1]);
+          if constexpr (kFeat) {
+            d0 = ((keep_bits[half] >> (2 * c)) & 1u) ? d0 * p.drop.inv_keep : 0.f;
+            d1 = ((keep_bits[half] >> (2 * c + 1)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
+          }
+          const int col = 32 * half + 2 * c;
+          pk[c] = pack2<kBf16>(pv[col] * (d0 - delta[col]), pv[col + 1] * (d1 - delta[col + 1]));
+        }
+        // dS^T row r, queries [64w + 32 half, +32): four 16-byte chunks of the 128-byte line
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = half * 4 + q4;
+          *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar_ds_full);
+    }
+
+    // ---- epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV ---------------------
+    if (ok && T > 0) ok = mbar_wait(bar_dkv_full, 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t tAcc = tmem_base + lane_base + (w == 0 ? kColdK : kColdV);
+      const float f = (w == 0) ? p.scale : 1.f;
+      uint8_t* stage = smem_gen + (w == 0 ? L::kQOff : L::kdOOff);
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t a[32];
+        if (T > 0) {
+          tmem_ld32(tAcc + c * 32, a);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) a[k] = 0u;
+        }
+        uint8_t* line = stage + (c >> 1) * L::kBlockBytes + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 v;
+          v.x = pack2<kBf16>(__uint_as_float(a[8 * q4 + 0]) * f, __uint_as_float(a[8 * q4 + 1]) * f);
+          v.y = pack2<kBf16>(__uint_as_float(a[8 * q4 + 2]) * f, __uint_as_float(a[8 * q4 + 3]) * f);
+          v.z = pack2<kBf16>(__uint_as_float(a[8 * q4 + 4]) * f, __uint_as_float(a[8 * q4 + 5]) * f);
+          v.w = pack2<kBf16>(__uint_as_float(a[8 * q4 + 6]) * f, __uint_as_float(a[8 * q4 + 7]) * f);
+          const int chunk = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(line + ((chunk ^ (r & 7)) << 4)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+    }
+    named_bar_sync(1 + w, 128);
+    if (ok && r == 0 && !*abort_flag) {
+      tma_store_5d(w == 0 ? &tmdK : &tmdV, (w == 0 ? sQ : sdO), 0, n * kBN, 0, hk, b);
+      tma_store_commit();
+      tma_store_wait_read0();
+    }
+    if (!ok && r == 0) atomicOr(p.status, 128);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// launcher
+// ---------------------------------------------------------------------------------------------
+template <int D, bool kBf16, bool kCausal, bool kFeat>
+static cudaError_t launch_main(const BwdLaunch& a, cudaStream_t stream) {
+  using L = BwdSmem<D>;
+  auto kern = bwd_main_kernel<D, kBf16, kCausal, kFeat>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  if (e != cudaSuccess) return e;
+  const long long nblocks = static_cast<long long>(a.kp.n_kvblk) * a.kp.B * a.kp.Hkv;
+  kern<<<static_cast<unsigned>(nblocks), kThreads, L::kDynamicBytes, stream>>>(
+      a.tmQ, a.tmK, a.tmV, a.tmdO, a.tmdK, a.tmdV, a.delta, a.kp);
+  return cudaGetLastError();
+}
+
+template <int D, bool kBf16>
+static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
+  const BwdKernelParams& kp = a.kp;
+  const int nQ = (kp.Sq + kBM - 1) / kBM;
+  const dim3 grid(nQ, kp.B * kp.Hq);
+  bwd_pre_kernel<D, kBf16><<<grid, 128, 0, stream>>>(
+      static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
+      a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
+      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);
+  switch (key) {
+    case 0: e = launch_main<D, kBf16, false, false>(a, stream); break;
+    case 1: e = launch_main<D, kBf16, false, true>(a, stream); break;
+    case 2: e = launch_main<D, kBf16, true, false>(a, stream); break;
+    default: e = launch_main<D, kBf16, true, true>(a, stream); break;
+  }
+  if (e != cudaSuccess) return e;
+  bwd_dq_convert<D, kBf16><<<grid, 128, 0, stream>>>(kp.dq_acc, static_cast<uint16_t*>(a.dq),
+                                                     a.dq_strides[0], a.dq_strides[1],
+                                                     a.dq_strides[2], kp.Sq, kp.Hq, nQ, kp.scale);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd(const BwdLaunch& a, cudaStream_t stream) {
+  if (a.head_dim == 64) return a.bf16 ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);
+  if (a.head_dim == 128) return a.bf16 ? launch_all<128, true>(a, stream) : launch_all<128, false>(a, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fa2

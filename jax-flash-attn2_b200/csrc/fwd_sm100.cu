@@ -168,6 +168,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     tma_prefetch_desc(&tmO);
   }
   if (warp == 0) {
+    __syncwarp();
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
     tc_fence_before();
   }
