@@ -155,7 +155,7 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   w.sq_pad = (p.seqlen_q + 127) / 128 * 128;
   const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * w.sq_pad;
   w.delta_off = 0;
-  w.dq_off = align_up(rows * sizeof(float), 256);
+  w.dq_off = align_up(2 * rows * sizeof(float), 256);   // (lse2, delta) per row
   w.total = w.dq_off + align_up(rows * p.head_dim * sizeof(float), 256);
   return w;
 }
