@@ -1,0 +1,403 @@
+"""Benchmark of the attention hot path: forward + backward of one attention call per step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Prints ONE JSON line (rank 0). At N=1 the workload is the Llama-3-8B-shaped causal bf16 config
+(B=8, Hq=32, Hkv=8, S=4096, D=128); at N>1 every rank runs that same per-GPU workload on its own
+batch slice of a global batch 8*N (independent (batch, kv-head) units, no collective on the
+path: weak scaling). `value` is fwd+bwd attention TFLOP/s with inputs resident in HBM, timed with
+CUDA events; `e2e` is the same metric through the host-buffer path (pinned host inputs copied in,
+results copied out, inside the timed region). FLOPs: forward 4*B*Hq*Sq*Sk*D, halved for causal;
+backward 2.5x forward.
+
+`--impl reference` times the CPU restatement of the reference's blockwise JAX algorithm (the
+reference itself needs jax, which is not installed) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "jax-flash-attn2_b200"))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import torch  # noqa: E402
+
+METRIC = "attention TFLOP/s fwd & fwd+bwd per B200, % of bf16 tensor peak; 1/2/4/8 GPU"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# name -> (B, Sq, Sk, Hq, Hkv, D, dtype, causal, input scale)
+WORKLOADS = {
+    "llama3_8b_causal_bf16": (8, 4096, 4096, 32, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
+    "readme_gqa_causal_fp16": (2, 512, 512, 16, 4, 64, torch.float16, True, 1.0),
+    "long_context_causal_bf16": (1, 32768, 32768, 64, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
+}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward main kernel at the
+# default workload, from the ncu capture summarised under profiles/ (None until captured).
+BWD_MAIN_DRAM_TRAFFIC_BYTES = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def flops_fwd(B, Sq, Sk, Hq, D, causal):
+    f = 4.0 * B * Hq * Sq * Sk * D
+    return 0.5 * f if causal else f
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.05):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:   # NVML missing: the clocks record says so
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        if self.ok:
+            self.join(timeout=2)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: CPU restatement of the reference's blockwise algorithm
+# ------------------------------------------------------------------------------------------------
+def cpu_sample(workload, seconds_budget=20.0):
+    """Times forward + backward of (batch element, kv-head group) units of the workload with the
+    CPU oracle on all host cores. Units are independent, so TFLOP/s of a sample of whole units is
+    the throughput of the whole job. Returns (tflops, units_timed, seconds, cores)."""
+    from oracle.block import BlockAttention
+    import workloads as W
+    B, Sq, Sk, Hq, Hkv, D, dtype, causal, scale = workload
+    G = Hq // Hkv
+    # very long sequences: time a prefix of the rows of one unit (still whole key range up to the diagonal)
+    Sq_s, Sk_s = min(Sq, 4096), min(Sk, 4096)
+    q, k, v, do = W.make_qkv(1, Sq_s, Sk_s, G, 1, D, dtype, scale)
+    blk = BlockAttention(128, 128)
+    unit_flops = 3.5 * flops_fwd(1, Sq_s, Sk_s, G, D, causal)
+    t0 = time.perf_counter()
+    units = 0
+    while True:
+        o, lse = blk.forward(q, k, v, causal=causal)
+        blk.backward(do, q, k, v, o, lse, causal=causal)
+        units += 1
+        dt = time.perf_counter() - t0
+        if dt > seconds_budget or units >= 4:
+            break
+    return unit_flops * units / dt / 1e12, units, dt, torch.get_num_threads(), (Sq_s, Sk_s, G)
+
+
+def run_reference(args, workload_name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = WORKLOADS[workload_name]
+    B, Sq, Sk, Hq, Hkv, D, dtype, causal, _ = wl
+    torch.set_num_threads(os.cpu_count() or 1)
+    budget = max(2.0, 20.0 / max(1, args.steps + args.warmup))
+    vals, ms = [], []
+    sample_desc = ""
+    for step in range(args.warmup + args.steps):
+        tf, units, dt, cores, (sq_s, sk_s, g) = cpu_sample(wl, budget)
+        sample_desc = (f"{units} unit(s) of (1 batch element x 1 kv head = {g} q heads), Sq={sq_s}, Sk={sk_s}, "
+                       f"D={D}, fwd+bwd, block 128x128, torch CPU fp32")
+        if step >= args.warmup:
+            vals.append(tf)
+            ms.append(dt * 1e3)
+    v = statistics.mean(vals)
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": statistics.mean(ms), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 (cpu)", "data": "synthetic",
+        "config": {"workload": workload_name, "shape": f"B={B} Sq={Sq} Sk={Sk} Hq={Hq} Hkv={Hkv} D={D} causal={causal}"},
+        "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample_desc},
+        "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "reference JAX/CPU path cannot run (jax not installed); this is the CPU restatement of its blockwise algorithm",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# product arm
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="fa2_b200", choices=["fa2_b200", "reference"])
+    ap.add_argument("--workload", default="llama3_8b_causal_bf16", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args, args.workload)
+        return
+
+    import jax_flash_attn2 as J
+    from jax_flash_attn2 import _capi
+    import workloads as W
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    B, Sq, Sk, Hq, Hkv, D, dtype, causal, scale = WORKLOADS[args.workload]
+    # every rank draws the same per-GPU batch slice shape; seeds differ per rank
+    g = torch.Generator().manual_seed(1000 + rank)
+    def draw(shape, s):
+        return (torch.randn(shape, generator=g, dtype=torch.float32) * s).to(dtype)
+    hq = draw((B, Sq, Hq, D), scale).pin_memory()
+    hk = draw((B, Sk, Hkv, D), scale).pin_memory()
+    hv = draw((B, Sk, Hkv, D), scale).pin_memory()
+    hdo = draw((B, Sq, Hq, D), 1.0).pin_memory()
+    q, k, v, do = (x.cuda(non_blocking=True) for x in (hq, hk, hv, hdo))
+    torch.cuda.synchronize()
+
+    fwd = lambda: J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, causal, None)
+    def bwd(o, lse):
+        return J.bwd_attention_kernel_call(do, q, k, v, None, None, o, lse, 0.0, causal, None, None)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    f_fwd = flops_fwd(B, Sq, Sk, Hq, D, causal)
+    f_step = 3.5 * f_fwd
+
+    # ---- warm-up -------------------------------------------------------------------------------
+    for _ in range(args.warmup):
+        o, lse = fwd()
+        bwd(o, lse)
+    barrier()
+
+    # ---- timed region: K steps of fwd + bwd, device-resident inputs ----------------------------
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(args.steps):
+        o, lse = fwd()
+        bwd(o, lse)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    status = J.device_status()
+
+    # ---- forward alone, and the kernels of the backward (same K, separate loops) ---------------
+    barrier()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(args.steps):
+        o, lse = fwd()
+    e1.record()
+    barrier()
+    ms_fwd = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+
+    stage = [ev() for _ in range(4)]
+    for e in stage:
+        e.record()          # creates the underlying CUDA events
+    torch.cuda.synchronize()
+    lib = _capi.load()
+    pre_ms, main_ms, conv_ms = [], [], []
+    for _ in range(args.steps):
+        arr = (C.c_void_p * 4)(*[C.c_void_p(e.cuda_event) for e in stage])
+        lib.fa2_debug_bwd_stage_events(arr)
+        bwd(o, lse)
+        torch.cuda.synchronize()
+        pre_ms.append(stage[0].elapsed_time(stage[1]))
+        main_ms.append(stage[1].elapsed_time(stage[2]))
+        conv_ms.append(stage[2].elapsed_time(stage[3]))
+    ms_main = max_over_ranks(statistics.mean(main_ms))
+
+    # ---- end to end: host buffers in, host buffers out, every step -----------------------------
+    ho = torch.empty_like(hq).pin_memory()
+    hdq = torch.empty_like(hq).pin_memory()
+    hdk = torch.empty_like(hk).pin_memory()
+    hdv = torch.empty_like(hv).pin_memory()
+    dq_, dk_, dv_ = (torch.empty_like(x) for x in (q, k, v))
+    def e2e_step():
+        q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
+        v.copy_(hv, non_blocking=True); do.copy_(hdo, non_blocking=True)
+        o_, lse_ = fwd()
+        g_ = bwd(o_, lse_)
+        ho.copy_(o_, non_blocking=True); hdq.copy_(g_[0], non_blocking=True)
+        hdk.copy_(g_[1], non_blocking=True); hdv.copy_(g_[2], non_blocking=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_step()
+    barrier()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
+    h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv, hdo))
+    d2h = sum(x.numel() * x.element_size() for x in (ho, hdq, hdk, hdv))
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = load_peaks()
+    peak_burst = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    peak_sust = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    value = f_step * world / (ms_step * 1e-3) / 1e12
+    fwd_tflops = f_fwd * world / (ms_fwd * 1e-3) / 1e12
+    main_tflops = 2.5 * f_fwd / (ms_main * 1e-3) / 1e12      # per GPU: a property of the kernel
+
+    line = {
+        "metric": METRIC,
+        "value": value,
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16" if dtype == torch.bfloat16 else "fp16",
+        "data": "synthetic",
+        "config": {
+            "workload": args.workload,
+            "shape_per_gpu": f"B={B} Sq={Sq} Sk={Sk} Hq={Hq} Hkv={Hkv} D={D} causal={causal}",
+            "global_batch": B * world,
+            "parallelism": f"{world} x independent (batch, kv-head) shards, no collective",
+            "l2": "inputs (640 MiB per step) exceed the 126 MB L2; no explicit flush",
+            "flops": "fwd 4*B*Hq*Sq*Sk*D (x0.5 causal), bwd 2.5x fwd",
+        },
+        "per_gpu": {
+            "fwd_bwd_tflops": value / world,
+            "fwd_tflops": fwd_tflops / world,
+            "fwd_ms": ms_fwd,
+            "bwd_pre_ms": statistics.mean(pre_ms),
+            "bwd_main_ms": ms_main,
+            "bwd_dq_convert_ms": statistics.mean(conv_ms),
+            "fwd_frac_of_peak": fwd_tflops / world / peak_burst,
+            "fwd_bwd_frac_of_peak": value / world / peak_burst,
+            "peak": f"{peak_burst} TFLOP/s bf16 burst, {peak_kind}",
+        },
+        "roofline": {
+            "bound": "tensor",
+            "kernel": "bwd_main_kernel",
+            "achieved": main_tflops,
+            "peak": peak_burst,
+            "unit": "TFLOP/s",
+            "frac": main_tflops / peak_burst,
+            "frac_of_sustained_peak": main_tflops / peak_sust,
+            "peak_source": f"{peak_kind}: cuBLAS bf16 burst {peak_burst}, sustained {peak_sust}",
+            "traffic": BWD_MAIN_DRAM_TRAFFIC_BYTES,
+        },
+        "e2e": {
+            "value": f_step * world / (ms_e2e * 1e-3) / 1e12,
+            "unit": "TFLOP/s",
+            "ms_per_step": ms_e2e,
+            "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h,
+        },
+        "gpu_launches": 4 * args.steps,
+        "device_status": status,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        tf, units, dt, cores, (sq_s, sk_s, g_) = cpu_sample(WORKLOADS[args.workload], 15.0)
+        line["cpu_baseline"] = {
+            "value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{units} unit(s) of (1 batch element x 1 kv head = {g_} q heads), Sq={sq_s}, Sk={sk_s}, "
+                      f"fwd+bwd with the CPU restatement of the reference's blockwise algorithm, {dt:.1f} s",
+        }
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

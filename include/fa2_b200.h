@@ -119,6 +119,12 @@ int fa2_version(void);
  * (0 = no time-out seen). Synchronises the stream; meant for tests and debugging. */
 int fa2_debug_device_status(void* cuda_stream);
 
+/* Profiling hook: arms four CUDA events (cudaEvent_t cast to void*) for the next fa2_bwd call on
+ * this thread. They are recorded on that call's stream before the rowsum pre-pass, before the
+ * main kernel, after it and after the dq conversion, so a caller can time each kernel of the
+ * backward (the three launches that replace _backward_triton.py:1049-1154). NULL disarms. */
+int fa2_debug_bwd_stage_events(void* const* events);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,6 +20,7 @@ namespace fa2 {
 namespace {
 
 thread_local char g_err[512] = "";
+thread_local cudaEvent_t g_bwd_events[4] = {nullptr, nullptr, nullptr, nullptr};
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -184,6 +185,11 @@ int fa2_debug_device_status(void* cuda_stream) {
   return v;
 }
 
+int fa2_debug_bwd_stage_events(void* const* events) {
+  for (int i = 0; i < 4; ++i) g_bwd_events[i] = events ? static_cast<cudaEvent_t>(events[i]) : nullptr;
+  return FA2_OK;
+}
+
 int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
   const fa2_problem& p = a->p;
@@ -295,6 +301,10 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   L.delta = reinterpret_cast<float*>(ws + w.delta_off);
   L.dq_acc_bytes = w.total - w.dq_off;
 
+  for (int i = 0; i < 4; ++i) {
+    L.stage_events[i] = g_bwd_events[i];
+    g_bwd_events[i] = nullptr;   // armed for one call only
+  }
   const cudaError_t e = launch_bwd(L, static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess)
     return fail(FA2_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));

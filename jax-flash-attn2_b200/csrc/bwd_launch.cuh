@@ -17,6 +17,9 @@ struct BwdLaunch {
   void* dq;        long long dq_strides[3];
   float* delta;    // start of the row-statistics area of the workspace
   size_t dq_acc_bytes;
+  // Optional: recorded before the pre-pass, before the main kernel, after it, after the dq
+  // conversion (profiling hook; null = not recorded).
+  cudaEvent_t stage_events[4];
 };
 
 // Runs the three kernels of the backward pass on `stream`.

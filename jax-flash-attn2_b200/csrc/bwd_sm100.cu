@@ -590,6 +590,10 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   const BwdKernelParams& kp = a.kp;
   const int nQ = (kp.Sq + kBM - 1) / kBM;
   const dim3 grid(nQ, kp.B * kp.Hq);
+  auto mark = [&](int i) {
+    if (a.stage_events[i]) cudaEventRecord(a.stage_events[i], stream);
+  };
+  mark(0);
   bwd_pre_kernel<D, kBf16><<<grid, 128, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
@@ -597,6 +601,7 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);
+  mark(1);
   switch (key) {
     case 0: e = launch_main<D, kBf16, false, false>(a, stream); break;
     case 1: e = launch_main<D, kBf16, false, true>(a, stream); break;
@@ -604,9 +609,11 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
     default: e = launch_main<D, kBf16, true, true>(a, stream); break;
   }
   if (e != cudaSuccess) return e;
+  mark(2);
   bwd_dq_convert<D, kBf16><<<grid, 128, 0, stream>>>(kp.dq_acc, static_cast<uint16_t*>(a.dq),
                                                      a.dq_strides[0], a.dq_strides[1],
                                                      a.dq_strides[2], kp.Sq, kp.Hq, nQ, kp.scale);
+  mark(3);
   return cudaGetLastError();
 }
 

@@ -22,6 +22,7 @@ EXPORTED_SYMBOLS = (
     "fa2_last_error",
     "fa2_version",
     "fa2_debug_device_status",
+    "fa2_debug_bwd_stage_events",
 )
 
 
@@ -126,6 +127,8 @@ def load() -> C.CDLL:
     lib.fa2_version.restype = C.c_int
     lib.fa2_debug_device_status.argtypes = [C.c_void_p]
     lib.fa2_debug_device_status.restype = C.c_int
+    lib.fa2_debug_bwd_stage_events.argtypes = [C.POINTER(C.c_void_p)]
+    lib.fa2_debug_bwd_stage_events.restype = C.c_int
     _lib = lib
     return lib
 

@@ -1,0 +1,124 @@
+"""GPU tests of the public class API, autograd, sharding equivalence and full-size properties."""
+import math
+
+import pytest
+import torch
+
+import workloads as W
+from oracle import dense
+from oracle.block import BlockAttention
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-30)).item()
+
+
+def test_flash_attention_class_forward_and_grad():
+    import jax_flash_attn2 as J
+    fa = J.FlashAttention(J.AttentionConfig(platform=J.Platform.TRITON, backend=J.Backend.GPU))
+    c = W.config1(batch=1, seq=256)
+    q, k, v = (c[n].cuda().requires_grad_(True) for n in ("q", "k", "v"))
+    out = fa(query=q, key=k, value=v, causal=True)
+    loss = out.float().mean() * 1000.0
+    loss.backward()
+    od, _ = dense.attention(c["q"], c["k"], c["v"], causal=True)
+    assert (out.detach().cpu().double() - od).abs().max().item() <= 5e-3
+    do = torch.full_like(c["q"], 1000.0 / c["q"].numel(), dtype=torch.float32)
+    gd = dense.attention_grads(do, c["q"], c["k"], c["v"], causal=True)
+    for mine, ref in zip((q.grad, k.grad, v.grad), gd):
+        assert rel_l2(mine.cpu(), ref) <= 2e-2
+
+
+def test_class_rules_sq1_drops_causal_and_sq_ne_sk_drops_mask():
+    import jax_flash_attn2 as J
+    fa = J.create_flash_attention("gpu", "triton")
+    q, k, v, _ = W.make_qkv(2, 1, 256, 4, 2, 64, torch.bfloat16)
+    mask = torch.zeros(2, 1, 1, 256, dtype=torch.bfloat16)
+    out = fa(q.cuda(), k.cuda(), v.cuda(), attention_mask=mask.cuda(), causal=True)
+    od, _ = dense.attention(q, k, v, causal=False)
+    assert (out.cpu().double() - od).abs().max().item() <= 2e-2
+
+
+def test_2d_padding_mask_masks_keys_and_zeroes_padded_rows():
+    import jax_flash_attn2 as J
+    fa = J.create_flash_attention("gpu", "triton")
+    B, S, H, D = 2, 256, 2, 64
+    q, k, v, _ = W.make_qkv(B, S, S, H, H, D, torch.float16)
+    lengths = [200, 77]
+    m2 = torch.zeros(B, S, dtype=torch.int32)
+    for b, n in enumerate(lengths):
+        m2[b, :n] = 1
+    out = fa(q.cuda(), k.cuda(), v.cuda(), attention_mask=m2.cuda(), causal=True).cpu()
+    for b, n in enumerate(lengths):
+        od, _ = dense.attention(q[b:b + 1, :n], k[b:b + 1, :n], v[b:b + 1, :n], causal=True)
+        assert (out[b:b + 1, :n].double() - od).abs().max().item() <= 5e-3
+        assert torch.all(out[b, n:] == 0)
+
+
+def test_bias_with_kv_heads_is_repeated_per_group():
+    import jax_flash_attn2 as J
+    fa = J.create_flash_attention("gpu", "triton")
+    q, k, v, _ = W.make_qkv(1, 128, 128, 4, 2, 64, torch.bfloat16)
+    bias = (torch.randn(1, 2, 128, 128) * 0.5).bfloat16()
+    out = fa(q.cuda(), k.cuda(), v.cuda(), bias=bias.cuda())
+    od, _ = dense.attention(q, k, v, bias=bias.repeat_interleave(2, dim=1))
+    assert (out.cpu().double() - od).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_equals_unsharded_bitwise(world):
+    """Every (batch, kv head) unit is independent: running the shards one after the other on one
+    GPU must reproduce the unsharded result bit for bit, dropout included."""
+    import jax_flash_attn2 as J
+    from jax_flash_attn2 import sharding
+    B, S, Hq, Hkv, D, p, seed = 2, 256, 8, 4, 64, 0.1, 7
+    q, k, v, do = (x.cuda() for x in W.make_qkv(B, S, S, Hq, Hkv, D, torch.bfloat16))
+    out, lse = J.fwd_attention_kernel_call(q, k, v, None, None, None, p, True, seed)
+    dq, dk, dv = J.bwd_attention_kernel_call(do, q, k, v, None, None, out, lse, p, True, None, seed)
+    G = Hq // Hkv
+    for rank in range(world):
+        sh = sharding.plan(B, Hkv, world, rank)
+        qs, ks, vs, dos, kw = sharding.slice_inputs(sh, G, q, k, v, do)
+        o_s, l_s = J.fwd_attention_kernel_call(qs, ks, vs, None, None, None, p, True, seed, **kw)
+        b0, b1, h0, h1 = sh.batch_start, sh.batch_stop, sh.kv_head_start, sh.kv_head_stop
+        assert torch.equal(o_s, out[b0:b1, :, h0 * G:h1 * G])
+        assert torch.equal(l_s, lse[b0:b1, h0 * G:h1 * G])
+        g = J.bwd_attention_kernel_call(dos, qs, ks, vs, None, None, o_s, l_s, p, True, None, seed, **kw)
+        assert torch.equal(g[1], dk[b0:b1, :, h0:h1]) and torch.equal(g[2], dv[b0:b1, :, h0:h1])
+        assert rel_l2(g[0], dq[b0:b1, :, h0 * G:h1 * G]) < 1e-2
+
+
+def test_full_size_config2_properties():
+    """Llama-3-8B-shaped causal bf16 attention at full size (B=8, S=4096, Hq=32, Hkv=8, D=128),
+    checked through properties that need no full-size oracle:
+      * causal prefix: the first 512 rows depend on the first 512 keys only;
+      * one (batch, head) slice against the dense float64 oracle;
+      * linearity of the backward in dO;  * rows of P sum to one => dO = const per row gives dq = 0.
+    """
+    import jax_flash_attn2 as J
+    c = W.config2()
+    q, k, v, do = (c[n].cuda() for n in ("q", "k", "v", "do"))
+    out, lse = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    o_pre, l_pre = J.fwd_attention_kernel_call(q[:, :512], k[:, :512], v[:, :512], None, None, None, 0.0, True, None)
+    assert torch.equal(o_pre, out[:, :512]) and torch.equal(l_pre, lse[:, :, :512])
+    b, h = 3, 13
+    od, ld = dense.attention(c["q"][b:b + 1, :1024, h:h + 1], c["k"][b:b + 1, :1024, h // 4:h // 4 + 1],
+                             c["v"][b:b + 1, :1024, h // 4:h // 4 + 1], causal=True)
+    assert (out[b:b + 1, :1024, h:h + 1].cpu().double() - od).abs().max().item() <= 2e-2
+    assert (lse[b, h, :1024].cpu().double() - ld[0, 0]).abs().max().item() <= 1e-3
+    dq, dk, dv = J.bwd_attention_kernel_call(do, q, k, v, None, None, out, lse, 0.0, True, None, None)
+    dq2, dk2, dv2 = J.bwd_attention_kernel_call(do * 2, q, k, v, None, None, out, lse, 0.0, True, None, None)
+    for a, b2 in ((dq, dq2), (dk, dk2), (dv, dv2)):
+        assert torch.isfinite(a.float()).all()
+        assert rel_l2(a.float() * 2, b2) <= 1e-2
+    # one slice of the gradients against the dense oracle (keys of head group 2, batch 1, truncated problem)
+    S = 768
+    qs, ks, vs, dos = (x[1:2, :S] for x in (c["q"], c["k"], c["v"], c["do"]))
+    o_s, l_s = J.fwd_attention_kernel_call(qs.cuda(), ks.cuda(), vs.cuda(), None, None, None, 0.0, True, None)
+    g = J.bwd_attention_kernel_call(dos.cuda(), qs.cuda(), ks.cuda(), vs.cuda(), None, None, o_s, l_s, 0.0, True, None, None)
+    gd = dense.attention_grads(dos, qs, ks, vs, causal=True)
+    for mine, ref in zip(g, gd):
+        assert rel_l2(mine.cpu(), ref) <= 1e-2

@@ -1,0 +1,136 @@
+"""CPU tests: public API surface, argument validation, C-ABI exports, shard planning."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+import jax_flash_attn2 as J
+from jax_flash_attn2 import _capi, sharding
+from jax_flash_attn2._kernel_calls import _score_term, normalise_attention_mask
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "fa2_b200.h")).read()
+    declared = set(re.findall(r"\b(fa2_[a-z_0-9]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = _capi.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert set(_capi.EXPORTED_SYMBOLS) <= declared
+    assert lib.fa2_version() == 1000
+
+
+def test_validation_errors_come_before_any_launch():
+    lib = _capi.load()
+    a = _capi.FwdParams()
+    assert lib.fa2_fwd(None, None) == _capi.FA2_ERR_INVALID_ARG
+    a.p.batch, a.p.seqlen_q, a.p.seqlen_k = 1, 128, 128
+    a.p.heads_q, a.p.heads_kv, a.p.head_dim = 3, 2, 128
+    a.p.dtype = _capi.FA2_BF16
+    a.p.softmax_scale = 1.0
+    assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_INVALID_ARG
+    assert b"divisible" in lib.fa2_last_error()
+    a.p.heads_q = 4
+    a.p.head_dim = 96
+    assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_UNSUPPORTED
+    a.p.head_dim = 128
+    a.p.dropout_p = 1.0
+    assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_INVALID_ARG
+    a.p.dropout_p = 0.0
+    a.p.dtype = _capi.FA2_FP32
+    assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_UNSUPPORTED
+    a.p.dtype = _capi.FA2_BF16
+    assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_INVALID_ARG   # null pointers
+    assert b"non-null" in lib.fa2_last_error()
+    # workspace size is pure arithmetic
+    n = lib.fa2_bwd_workspace_bytes(C.byref(a.p))
+    rows = 1 * 4 * 128
+    assert n == 2 * rows * 4 + rows * 128 * 4
+    b = _capi.BwdParams()
+    b.p = a.p
+    assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_INVALID_ARG
+
+
+def test_config_defaults_and_pairs():
+    cfg = J.AttentionConfig(backend=J.Backend.GPU)
+    assert cfg.platform == J.Platform.TRITON and cfg.blocksize_q == 128 and cfg.blocksize_k == 128
+    assert J.AttentionConfig(backend=J.Backend.CPU).platform == J.Platform.JAX
+    assert J.AttentionConfig(backend=J.Backend.TPU).platform == J.Platform.PALLAS
+    with pytest.raises(ValueError):
+        J.FlashAttention(J.AttentionConfig(backend=J.Backend.CPU, platform=J.Platform.TRITON))
+    fa = J.create_flash_attention("gpu", "triton", softmax_scale=0.5)
+    assert fa.config.softmax_scale == 0.5
+    assert "triton" in repr(fa).lower() or "TRITON" in repr(fa)
+    assert J.FlashAttention.forward is J.FlashAttention.__call__
+
+
+def test_head_and_bias_rules():
+    fa = J.create_flash_attention("gpu", "triton")
+    q = torch.zeros(1, 8, 6, 64, dtype=torch.bfloat16)
+    k = torch.zeros(1, 8, 4, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="divisible"):
+        fa(q, k, k)
+    assert fa._handle_bias(torch.zeros(1, 2, 8, 8), 4, 2).shape == (1, 4, 8, 8)
+    assert fa._handle_bias(torch.zeros(1, 1, 8, 8), 4, 2).shape == (1, 1, 8, 8)
+    with pytest.raises(ValueError, match="Incompatible bias shape"):
+        fa._handle_bias(torch.zeros(1, 3, 8, 8), 4, 2)
+    # repeat follows "b h q k -> b (h r) q k": q head h uses bias head h // r
+    bias = torch.arange(2).float()[None, :, None, None].expand(1, 2, 8, 8)
+    rep = fa._handle_bias(bias, 4, 2)
+    assert rep[0, :, 0, 0].tolist() == [0, 0, 1, 1]
+    with pytest.raises(NotImplementedError):
+        J.FlashAttention(J.AttentionConfig(backend=J.Backend.CPU))(q, q, q)
+
+
+def test_score_term_broadcast_rules():
+    t, _ = _score_term(torch.zeros(1, 1, 16, 32), 2, 4, 16, 32, "bias")
+    assert (t.stride_b, t.stride_h, t.stride_q) == (0, 0, 32)
+    t, _ = _score_term(torch.zeros(2, 4, 16, 32), 2, 4, 16, 32, "bias")
+    assert (t.stride_b, t.stride_h, t.stride_q) == (4 * 16 * 32, 16 * 32, 32)
+    t, _ = _score_term(torch.zeros(2, 1, 1, 32), 2, 4, 16, 32, "mask")
+    assert t.stride_q == 0
+    for bad in ((3, 1, 16, 32), (2, 3, 16, 32), (2, 4, 15, 32), (2, 4, 16, 31)):
+        with pytest.raises(ValueError):
+            _score_term(torch.zeros(*bad), 2, 4, 16, 32, "bias")
+
+
+def test_mask_normalisation():
+    add, rows = normalise_attention_mask(torch.tensor([[1, 1, 0], [1, 0, 0]]), torch.bfloat16, 3, 3)
+    assert add.shape == (2, 1, 1, 3) and rows.tolist() == [[True, True, False], [True, False, False]]
+    assert add[0, 0, 0].tolist() == [0.0, 0.0, float("-inf")]
+    m4 = torch.ones(1, 1, 3, 3, dtype=torch.bool).tril()
+    add, rows = normalise_attention_mask(m4, torch.float16, 3, 3)
+    assert rows is None and add.dtype == torch.float16 and add[0, 0, 0, 1] == float("-inf")
+    fm = torch.zeros(1, 1, 3, 3)
+    assert normalise_attention_mask(fm, torch.float16, 3, 3)[0] is fm
+    with pytest.raises(AssertionError):
+        normalise_attention_mask(torch.ones(2, 3), torch.float16, 3, 4)
+
+
+@pytest.mark.parametrize("batch,hkv", [(2, 4), (8, 8), (4, 16), (1, 8), (4, 8)])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_shard_plan_covers_every_unit_once(batch, hkv, world):
+    seen = set()
+    for rank in range(world):
+        s = sharding.plan(batch, hkv, world, rank)
+        assert s.units == batch * hkv // world
+        for b in range(s.batch_start, s.batch_stop):
+            for h in range(s.kv_head_start, s.kv_head_stop):
+                assert (b, h) not in seen
+                seen.add((b, h))
+    assert len(seen) == batch * hkv
+
+
+def test_shard_plan_rejects_uneven_split():
+    with pytest.raises(ValueError):
+        sharding.plan(1, 6, 4, 0)
+
+
+def test_cuda_path_refuses_cpu_tensors():
+    q = torch.zeros(1, 128, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        J.fwd_attention_kernel_call(q, q, q)
