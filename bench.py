@@ -38,6 +38,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # name -> (B, Sq, Sk, Hq, Hkv, D, dtype, causal, input scale)
 WORKLOADS = {
     "llama3_8b_causal_bf16": (8, 4096, 4096, 32, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
+    # the same shape with a quarter of the batch: the small case the ncu captures run on
+    "llama3_8b_causal_bf16_b2": (2, 4096, 4096, 32, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
     "readme_gqa_causal_fp16": (2, 512, 512, 16, 4, 64, torch.float16, True, 1.0),
     "long_context_causal_bf16": (1, 32768, 32768, 64, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
 }
