@@ -4,11 +4,13 @@
 // (jax_flash_attn2/flash_attention_triton/_forward_triton.py:60-164, 213-459).
 //
 // One CTA owns 256 query rows of one (batch, query head): two 128-row tiles that share one
-// stream of K/V tiles. Roles (10 warps):
-//   warps 0-3 : softmax of query tile 0, one thread per row (TMEM lane == row)
-//   warps 4-7 : softmax of query tile 1
-//   warp  8   : tcgen05.mma issuer (one elected thread)
-//   warp  9   : TMA producer (Q once, then K_j, V_j into a ring of shared-memory slots)
+// stream of K/V tiles. Roles (12 warps; registers are moved from the last warpgroup to the
+// softmax warpgroups with setmaxnreg):
+//   warps 0-3  : softmax of query tile 0, one thread per row (TMEM lane == row)
+//   warps 4-7  : softmax of query tile 1
+//   warp  8    : tcgen05.mma issuer (one elected thread)
+//   warp  9    : TMA producer (Q once, then K_j, V_j into a ring of shared-memory slots)
+//   warps 10-11: idle (they complete the warpgroup that gives up its registers)
 // Tensor memory (columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 // P (16-bit, two values per column) overwrites the first 64 columns of its S tile and is the
 // A operand of the P.V MMA, read straight from tensor memory.
@@ -24,7 +26,17 @@ namespace {
 constexpr int kBM = 128;            // rows of one query tile
 constexpr int kBN = 128;            // keys per K/V tile
 constexpr int kTilesPerCta = 2;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
+constexpr int kRegsSoftmax = 208;   // per scheduler: 2 softmax warps + 1 other warp share the 3 * 168 registers of the launch
+constexpr int kRegsOther = 88;
+// Of every 8 column pairs, this many take their exponential from the FMA-pipe polynomial
+// instead of the XU pipe. Measured on B200 (B=8, S=4096, Hq=32, D=128, causal): 0 -> 1.016 ms,
+// 2 -> 1.019 ms, 3 -> 1.048 ms, 4 -> 1.039 ms, 5 -> 1.083 ms, so the default is 0: with packed
+// f32x2 arithmetic the XU pipe is not what limits the kernel.
+#ifndef FA2_FWD_POLY_PER8
+#define FA2_FWD_POLY_PER8 0
+#endif
+constexpr int kPolyPer8 = FA2_FWD_POLY_PER8;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // in log2 units: P stays below 2^8
@@ -177,7 +189,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const uint32_t tmem_base = *tmem_slot;
   constexpr uint32_t kColS = 0, kColO = 256;
 
-  if (warp == 9) {
+
+  if (warp >= 8) {
+    // One warpgroup, one instruction: all four warps release their registers here.
+    setmaxnreg_dec<kRegsOther>();
+  }
+  if (warp >= 10) {
+    // idle
+  } else if (warp == 9) {
     // =========================== TMA producer ================================================
     if (lane == 0) {
 #pragma unroll
@@ -270,8 +289,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       if (!ok) atomicOr(p.status, 2);
     }
     __syncwarp();
-  } else {
+  } else if (warp < 8) {
     // =========================== softmax + epilogue ==========================================
+    setmaxnreg_inc<kRegsSoftmax>();
     const int t = warp >> 2;                   // query tile of this warpgroup
     const int r = tid & (kBM - 1);             // row inside the tile == TMEM lane
     const int qi = q0 + t * kBM + r;           // global query row
@@ -314,15 +334,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         for (int c = 0; c < kBN; ++c)
           if (kv0 + c > row_lim) x[c] = -INFINITY;
       }
-      float mx0 = x[0], mx1 = x[1], mx2 = x[2], mx3 = x[3];
+      float mx0 = fmaxf(x[0], x[1]), mx1 = fmaxf(x[2], x[3]), mx2 = fmaxf(x[4], x[5]),
+            mx3 = fmaxf(x[6], x[7]);
 #pragma unroll
-      for (int c = 4; c < kBN; c += 4) {
-        mx0 = fmaxf(mx0, x[c]);
-        mx1 = fmaxf(mx1, x[c + 1]);
-        mx2 = fmaxf(mx2, x[c + 2]);
-        mx3 = fmaxf(mx3, x[c + 3]);
+      for (int c = 8; c < kBN; c += 8) {
+        mx0 = max3(mx0, x[c], x[c + 1]);
+        mx1 = max3(mx1, x[c + 2], x[c + 3]);
+        mx2 = max3(mx2, x[c + 4], x[c + 5]);
+        mx3 = max3(mx3, x[c + 6], x[c + 7]);
       }
-      const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      const float m_new = max3(m, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       // Lazy rescaling: keep the stale maximum while the true one is less than 2^8 above it.
       const bool resc = (m_new - m) * sc > kRescaleThreshold;
       if (__any_sync(0xffffffffu, resc)) {
@@ -349,14 +370,22 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
       for (int c = 0; c < kBN; c += 4) {
-        x[c] = ex2_approx(fmaf(x[c], sc, neg_ms));
-        x[c + 1] = ex2_approx(fmaf(x[c + 1], sc, neg_ms));
-        x[c + 2] = ex2_approx(fmaf(x[c + 2], sc, neg_ms));
-        x[c + 3] = ex2_approx(fmaf(x[c + 3], sc, neg_ms));
-        l0 += x[c];
-        l1 += x[c + 1];
-        l2 += x[c + 2];
-        l3 += x[c + 3];
+        fma2(x[c], x[c + 1], x[c], x[c + 1], sc, sc, neg_ms, neg_ms);
+        fma2(x[c + 2], x[c + 3], x[c + 2], x[c + 3], sc, sc, neg_ms, neg_ms);
+        if (((c >> 1) & 7) < kPolyPer8) {
+          ex2_poly2(x[c], x[c + 1]);
+        } else {
+          x[c] = ex2_approx(x[c]);
+          x[c + 1] = ex2_approx(x[c + 1]);
+        }
+        if ((((c >> 1) + 1) & 7) < kPolyPer8) {
+          ex2_poly2(x[c + 2], x[c + 3]);
+        } else {
+          x[c + 2] = ex2_approx(x[c + 2]);
+          x[c + 3] = ex2_approx(x[c + 3]);
+        }
+        add2(l0, l1, l0, l1, x[c], x[c + 1]);
+        add2(l2, l3, l2, l3, x[c + 2], x[c + 3]);
       }
       l += (l0 + l1) + (l2 + l3);
       if constexpr (kFeat) {

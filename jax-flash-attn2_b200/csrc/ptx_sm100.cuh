@@ -83,6 +83,14 @@ __device__ __forceinline__ void tc_wait_ld() {
 __device__ __forceinline__ void tc_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
@@ -253,6 +261,66 @@ __device__ __forceinline__ float lg2_approx(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed fp32 pair arithmetic (one instruction for two lanes of data).
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1,
+                                     float c0, float c1) {
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// round-towards-minus-infinity packed add (used to split a value into floor and fraction)
+__device__ __forceinline__ void add2_rm(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "add.rm.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for a pair of values on the FMA / ALU pipes: x is split into floor and fraction with a
+// round-down add of 1.5 * 2^23, 2^fraction is a cubic (relative error about 1e-4, below the
+// resolution of the 16-bit weights it feeds), and the integer part is added to the exponent
+// field. Inputs below -126 are clamped (the result is then about 1e-38 instead of 0).
+__device__ __forceinline__ void ex2_poly2(float& y0, float& y1) {
+  constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
+  const float x0 = fmaxf(y0, -126.f), x1 = fmaxf(y1, -126.f);
+  float t0, t1, fl0, fl1, f0, f1, p0, p1;
+  add2_rm(t0, t1, x0, x1, kMagic, kMagic);
+  add2(fl0, fl1, t0, t1, -kMagic, -kMagic);
+  fma2(f0, f1, fl0, fl1, -1.f, -1.f, x0, x1);
+  fma2(p0, p1, f0, f1, 0.077119029f, 0.077119029f, 0.227564394f, 0.227564394f);
+  fma2(p0, p1, p0, p1, f0, f1, 0.695146143f, 0.695146143f);
+  fma2(p0, p1, p0, p1, f0, f1, 1.0f, 1.0f);
+  y0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+  y1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+
 // Pack two floats into one 32-bit word of two 16-bit values; `lo` ends up in the low half.
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {

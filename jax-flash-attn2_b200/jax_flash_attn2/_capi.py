@@ -9,7 +9,9 @@ import ctypes as C
 import os
 
 _PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LIB_PATH = os.path.join(_PKG_ROOT, "libfa2_b200.so")
+# FA2_B200_LIB points at another build of the same library (e.g. one compiled with other tuning
+# macros); by default the in-tree build is used.
+LIB_PATH = os.environ.get("FA2_B200_LIB") or os.path.join(_PKG_ROOT, "libfa2_b200.so")
 
 FA2_FP16, FA2_BF16, FA2_FP32 = 0, 1, 2
 FA2_OK = 0
