@@ -27,7 +27,11 @@ namespace {
 
 constexpr int kBM = 128;   // query rows per step
 constexpr int kBN = 128;   // keys per CTA
-constexpr int kThreads = 448;
+constexpr int kThreads = 512;
+// Registers per thread after setmaxnreg: each scheduler holds 2 P/dS warps, 1 drain warp and 1
+// warp of the last warpgroup; 2 * 128 + 152 + 104 = 4 * 128 (the launch allocation).
+constexpr int kRegsDrain = 152;
+constexpr int kRegsOther = 104;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kMaxDynSmem = 232448;
 
@@ -38,8 +42,11 @@ struct BwdSmem {
   static constexpr int kKOff = 0;
   static constexpr int kVOff = kKOff + kTileBytes;
   static constexpr int kQOff = kVOff + kTileBytes;         // 2 stages
-  static constexpr int kdOOff = kQOff + 2 * kTileBytes;    // 2 stages
-  static constexpr int kdSOff = kdOOff + 2 * kTileBytes;   // [128 keys][128 queries] 16 bit
+  static constexpr int kdOOff = kQOff + 2 * kTileBytes;    // 1 stage
+  // dQ leaves through two staging chunks of [D/16][128 rows][4 floats] (a quarter tile each)
+  static constexpr int kChunkBytes = kTileBytes / 2;
+  static constexpr int kStageOff = kdOOff + kTileBytes;
+  static constexpr int kdSOff = kStageOff + 2 * kChunkBytes;   // [128 keys][128 queries] 16 bit
   static constexpr int kStatsOff = kdSOff + 128 * 128 * 2; // 2 stages x (lse2[128], delta[128])
   static constexpr int kBarOff = kStatsOff + 2 * 1024;
   static constexpr int kNumBars = 16;
@@ -57,11 +64,20 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
       : "memory");
 }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
+// dst[0 .. bytes) += src[0 .. bytes) as float32, done by the TMA unit (asynchronous).
+__device__ __forceinline__ void bulk_reduce_add_f32(float* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst),
+               "r"(src_smem), "r"(bytes)
                : "memory");
 }
+
+#ifdef FA2_TRACE
+// Development aid (not compiled by default): per-role time stamps of CTA 0.
+__device__ long long g_trace[16 * 4096];
+#define FA2_T(role, idx) do { if (blockIdx.x == FA2_TRACE_CTA && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
+#else
+#define FA2_T(role, idx) do { } while (0)
+#endif
 
 template <bool kBf16>
 __device__ __forceinline__ float load_term(const ScoreTermDev& t, long long idx) {
@@ -178,9 +194,8 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t bars = smem_base + L::kBarOff;
   const uint32_t bar_kv_full = bars;
   auto bar_q_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto bar_do_full = [&](int s) { return bars + 8u * (3 + s); };
+  const uint32_t bar_do_full = bars + 8u * 3, bar_do_empty = bars + 8u * 4;
   auto bar_q_empty = [&](int s) { return bars + 8u * (5 + s); };
-  auto bar_do_empty = [&](int s) { return bars + 8u * (7 + s); };
   const uint32_t bar_s_full = bars + 8u * 9, bar_p_full = bars + 8u * 10;
   const uint32_t bar_dp_full = bars + 8u * 11, bar_ds_full = bars + 8u * 12;
   const uint32_t bar_dq_full = bars + 8u * 13, bar_dq_drained = bars + 8u * 14;
@@ -212,10 +227,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar_kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_q_full(s), 1);
-      mbar_init(bar_do_full(s), 1);
       mbar_init(bar_q_empty(s), 1);
-      mbar_init(bar_do_empty(s), 1);
     }
+    mbar_init(bar_do_full, 1);
+    mbar_init(bar_do_empty, 1);
     mbar_init(bar_s_full, 1);
     mbar_init(bar_p_full, 256);
     mbar_init(bar_dp_full, 1);
@@ -248,7 +263,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     h = hk * p.G + g;
   };
 
-  if (warp == 13) {
+  if (warp >= 12) setmaxnreg_dec<kRegsOther>();   // one site for the whole warpgroup
+  if (warp >= 14) {
+    // idle: these two warps only complete the warpgroup that gives up registers
+  } else if (warp == 13) {
     // =========================== TMA producer ================================================
     if (lane == 0 && T > 0) {
       mbar_arrive_expect_tx(bar_kv_full, 2 * L::kTileBytes);
@@ -267,10 +285,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         bulk_load_1d(sStats + st * 1024,
                      stats + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * 256, 1024,
                      bar_q_full(st));
-        ok = mbar_wait(bar_do_empty(st), par, abort_flag);
+        ok = mbar_wait(bar_do_empty, (it & 1) ^ 1, abort_flag);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_do_full(st), L::kTileBytes);
-        tma_load_5d(sdO + st * L::kTileBytes, &tmdO, bar_do_full(st), 0, i * kBM, 0, h, b);
+        mbar_arrive_expect_tx(bar_do_full, L::kTileBytes);
+        tma_load_5d(sdO, &tmdO, bar_do_full, 0, i * kBM, 0, h, b);
       }
       if (!ok) atomicOr(p.status, 8);
     }
@@ -328,7 +346,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         issue_kd(kColS, sK, sQ);
         mma_commit(bar_s_full);
-        ok = mbar_wait(bar_do_full(0), 0, abort_flag);
+        ok = mbar_wait(bar_do_full, 0, abort_flag);
       }
       if (ok) {
         tc_fence_after();
@@ -342,8 +360,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool has_next = it + 1 < T;
         ok = mbar_wait(bar_p_full, par, abort_flag);
         if (!ok) break;
+        FA2_T(0, it);
         tc_fence_after();
-        issue_dv(sdO + st * L::kTileBytes, it == 0);
+        issue_dv(sdO, it == 0);
+        mma_commit(bar_do_empty);          // the single dO buffer can be refilled
         if (has_next) {
           ok = mbar_wait(bar_q_full(nx), par_next, abort_flag);
           if (!ok) break;
@@ -351,20 +371,23 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           issue_kd(kColS, sK, sQ + nx * L::kTileBytes);
           mma_commit(bar_s_full);
         }
+        FA2_T(1, it);
         ok = mbar_wait(bar_ds_full, par, abort_flag);
         if (!ok) break;
+        FA2_T(2, it);
         tc_fence_after();
-        issue_dk(sQ + st * L::kTileBytes, it == 0);
         issue_dq();
         mma_commit(bar_dq_full);
+        issue_dk(sQ + st * L::kTileBytes, it == 0);
         mma_commit(bar_q_empty(st));
-        mma_commit(bar_do_empty(st));
         if (has_next) {
+          FA2_T(3, it);
           ok = mbar_wait(bar_dq_drained, par, abort_flag);
-          if (ok) ok = mbar_wait(bar_do_full(nx), par_next, abort_flag);
+          if (ok) ok = mbar_wait(bar_do_full, (it + 1) & 1, abort_flag);
           if (!ok) break;
+          FA2_T(4, it);
           tc_fence_after();
-          issue_kd(kColdP, sV, sdO + nx * L::kTileBytes);
+          issue_kd(kColdP, sV, sdO);
           mma_commit(bar_dp_full);
         }
       }
@@ -374,6 +397,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else if (warp >= 8) {
     // =========================== dQ drain ====================================================
+    setmaxnreg_inc<kRegsDrain>();
     const int r = tid - 256;   // query row inside the tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tdQ = tmem_base + lane_base + kColdQ;
@@ -383,24 +407,47 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       step_coords(it, h, i);
       ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
       if (!ok) break;
+      if (r == 0) FA2_T(5, it);
       tc_fence_after();
-      float* dst = p.dq_acc + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * (kBM * D) + r * 4;
+      // Pull the whole tile into registers first so that the tensor-memory columns are handed
+      // back at once; the reductions (slow: they queue in the memory pipe) then overlap with the
+      // MMAs of the next step.
+      uint32_t v[D];
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tdQ + c * 32, v);
-        tc_wait_ld();
-        if (c == D / 32 - 1) {
-          tc_fence_before();
-          mbar_arrive(bar_dq_drained);
+      for (int c = 0; c < D / 32; ++c)
+        tmem_ld32(tdQ + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_dq_drained);
+      if (r == 0) FA2_T(6, it);
+      // Hand the tile to the TMA unit in four chunks of D/4 columns through two staging
+      // buffers: cp.reduce.async.bulk adds each chunk to the global fp32 accumulator while the
+      // next chunk is written. (Reductions issued from registers would queue in the memory
+      // pipe in front of the tensor-memory traffic of the other warps.)
+      float* dst_tile = p.dq_acc + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * (kBM * D);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int buf = c & 1;
+        // at most one reduction may still be reading: the one from the other buffer
+        if (r == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        named_bar_sync(3, 128);
+        uint8_t* stage = smem_gen + L::kStageOff + buf * L::kChunkBytes;
+#pragma unroll
+        for (int c4 = 0; c4 < D / 16; ++c4) {
+          const int cc = c * (D / 16) + c4;
+          *reinterpret_cast<uint4*>(stage + (c4 * 128 + r) * 16) =
+              make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
         }
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4)
-          red_add_v4(dst + (c * 8 + q4) * (128 * 4), __uint_as_float(v[4 * q4]),
-                     __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
-                     __uint_as_float(v[4 * q4 + 3]));
+        fence_proxy_async_smem();
+        named_bar_sync(3, 128);
+        if (r == 0) {
+          bulk_reduce_add_f32(dst_tile + c * (kBM * D / 4), smem_base + L::kStageOff + buf * L::kChunkBytes,
+                              L::kChunkBytes);
+          tma_store_commit();
+        }
       }
     }
+    if (r == 0) tma_store_wait_read0();   // staging buffers stay valid until the TMA unit has read them
     if (!ok && r == 0) atomicOr(p.status, 32);
   } else {
     // =========================== P / dS warps + dK, dV epilogue ==============================
@@ -424,6 +471,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = mbar_wait(bar_q_full(st), (it >> 1) & 1, abort_flag);
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
+      if (tid == 0) FA2_T(7, it);
       tc_fence_after();
       // some (query, key) pairs of this step are above the causal diagonal
       const bool diag = kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off);
@@ -435,25 +483,31 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld32(tS + 32 * half, s);
         tc_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int col = 32 * half + c;
-          const int qi = q_first + col;
-          float x = __uint_as_float(s[c]) * p.scale_log2;
-          if constexpr (kFeat) {
-            if (qi < p.Sq && kv < p.Sk) {
-              if (p.bias.ptr)
-                x = fmaf(load_term<kBf16>(p.bias, b * p.bias.sb + h * p.bias.sh +
-                                                      static_cast<long long>(qi) * p.bias.sq + kv),
-                         kLog2e, x);
-              if (p.mask.ptr)
-                x = fmaf(load_term<kBf16>(p.mask, b * p.mask.sb + h * p.mask.sh +
-                                                      static_cast<long long>(qi) * p.mask.sq + kv),
-                         kLog2e, x);
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 t4 = reinterpret_cast<const float4*>(lse2)[8 * half + c4];
+          const float lse_v[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int c = 4 * c4 + k;
+            const int col = 32 * half + c;
+            const int qi = q_first + col;
+            float x = __uint_as_float(s[c]) * p.scale_log2;
+            if constexpr (kFeat) {
+              if (qi < p.Sq && kv < p.Sk) {
+                if (p.bias.ptr)
+                  x = fmaf(load_term<kBf16>(p.bias, b * p.bias.sb + h * p.bias.sh +
+                                                        static_cast<long long>(qi) * p.bias.sq + kv),
+                           kLog2e, x);
+                if (p.mask.ptr)
+                  x = fmaf(load_term<kBf16>(p.mask, b * p.mask.sb + h * p.mask.sh +
+                                                        static_cast<long long>(qi) * p.mask.sq + kv),
+                           kLog2e, x);
+              }
             }
+            float pe = ex2_approx(x - lse_v[k]);
+            if (diag && kv > qi + p.causal_off) pe = 0.f;
+            pv[col] = pe;
           }
-          float pe = ex2_approx(x - lse2[col]);
-          if (diag && kv > qi + p.causal_off) pe = 0.f;
-          pv[col] = pe;
         }
         uint32_t pk[16];
         if constexpr (kFeat) {
@@ -489,9 +543,11 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);
+      if (tid == 0) FA2_T(8, it);
 
       ok = mbar_wait(bar_dp_full, it & 1, abort_flag);
       if (!ok) break;
+      if (tid == 0) FA2_T(9, it);
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -500,14 +556,20 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_wait_ld();
         uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          float d0 = __uint_as_float(dp[2 * c]), d1 = __uint_as_float(dp[2 * c + 1]);
-          if constexpr (kFeat) {
-            d0 = ((keep_bits[half] >> (2 * c)) & 1u) ? d0 * p.drop.inv_keep : 0.f;
-            d1 = ((keep_bits[half] >> (2 * c + 1)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 t4 = reinterpret_cast<const float4*>(delta)[8 * half + c4];
+          const float dl_v[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+          for (int k2 = 0; k2 < 2; ++k2) {
+            const int c = 2 * c4 + k2;
+            float d0 = __uint_as_float(dp[2 * c]), d1 = __uint_as_float(dp[2 * c + 1]);
+            if constexpr (kFeat) {
+              d0 = ((keep_bits[half] >> (2 * c)) & 1u) ? d0 * p.drop.inv_keep : 0.f;
+              d1 = ((keep_bits[half] >> (2 * c + 1)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
+            }
+            const int col = 32 * half + 2 * c;
+            pk[c] = pack2<kBf16>(pv[col] * (d0 - dl_v[2 * k2]), pv[col + 1] * (d1 - dl_v[2 * k2 + 1]));
           }
-          const int col = 32 * half + 2 * c;
-          pk[c] = pack2<kBf16>(pv[col] * (d0 - delta[col]), pv[col + 1] * (d1 - delta[col + 1]));
         }
         // dS^T row r, queries [64w + 32 half, +32): four 16-byte chunks of the 128-byte line
 #pragma unroll
@@ -519,6 +581,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       fence_proxy_async_smem();
       mbar_arrive(bar_ds_full);
+      if (tid == 0) FA2_T(10, it);
     }
 
     // ---- epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV ---------------------
@@ -527,7 +590,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const uint32_t tAcc = tmem_base + lane_base + (w == 0 ? kColdK : kColdV);
       const float f = (w == 0) ? p.scale : 1.f;
-      uint8_t* stage = smem_gen + (w == 0 ? L::kQOff : L::kdOOff);
+      uint8_t* stage = smem_gen + L::kQOff + w * L::kTileBytes;   // both Q stages are free now
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t a[32];
@@ -554,7 +617,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     named_bar_sync(1 + w, 128);
     if (ok && r == 0 && !*abort_flag) {
-      tma_store_5d(w == 0 ? &tmdK : &tmdV, (w == 0 ? sQ : sdO), 0, n * kBN, 0, hk, b);
+      tma_store_5d(w == 0 ? &tmdK : &tmdV, sQ + w * L::kTileBytes, 0, n * kBN, 0, hk, b);
       tma_store_commit();
       tma_store_wait_read0();
     }
@@ -616,6 +679,12 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   mark(3);
   return cudaGetLastError();
 }
+
+#ifdef FA2_TRACE
+extern "C" int fa2_trace_read_bwd(long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n));
+}
+#endif
 
 cudaError_t launch_bwd(const BwdLaunch& a, cudaStream_t stream) {
   if (a.head_dim == 64) return a.bf16 ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);
