@@ -90,7 +90,7 @@ __device__ __forceinline__ float load_term(const ScoreTermDev& t, long long idx)
 // ---------------------------------------------------------------------------------------------
 // 1. pre-pass
 // ---------------------------------------------------------------------------------------------
-// stats layout: [B, Hq, nQ, 2, 128] float: (lse * log2e | +inf for rows that take no gradient,
+// stats layout: [B, Hq, nQ, 2, 128] float: (-lse * log2e | -inf for rows that take no gradient,
 // delta). dq_acc layout: [B, Hq, nQ, D/4, 128, 4] float.
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(128)
@@ -127,10 +127,10 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
     for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
       acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (sub == 0) {
-      float l2 = INFINITY;
+      float l2 = -INFINITY;      // -lse*log2(e); -inf makes every weight of the row exp2(-inf) = 0
       if (row < Sq) {
         const float l = lse[b * lse_sb + h * lse_sh + row];
-        if (l > -INFINITY && l < INFINITY) l2 = l * kLog2e;
+        if (l > -INFINITY && l < INFINITY) l2 = -l * kLog2e;
       }
       st[r] = l2;
       st[128 + r] = (row < Sq) ? acc : 0.f;
@@ -465,8 +465,9 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int st = it & 1;
       int h, i;
       step_coords(it, h, i);
-      const float* lse2 = stats_s + st * 256 + 64 * w;
-      const float* delta = lse2 + 128;
+      // per query column of this warpgroup: -lse*log2(e) (or -inf) and delta
+      const float4* nlse4 = reinterpret_cast<const float4*>(stats_s + st * 256 + 64 * w);
+      const float4* delta4 = nlse4 + 32;
       const int q_first = i * kBM + 64 * w;
       ok = mbar_wait(bar_q_full(st), (it >> 1) & 1, abort_flag);
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
@@ -475,108 +476,131 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       // some (query, key) pairs of this step are above the causal diagonal
       const bool diag = kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off);
-      float pv[64];
-      uint32_t keep_bits[2] = {0xffffffffu, 0xffffffffu};
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t s[32];
-        tmem_ld32(tS + 32 * half, s);
+      const int q_lim = kv - p.causal_off;     // masked iff query index < q_lim
+
+      // ---- P^T = exp2(S^T * scale*log2e - lse*log2e): 64 query columns of this key row -------
+      uint32_t pk[32];                          // P as 16-bit pairs; also the input of dS below
+      uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;
+      {
+        uint32_t s[64];
+        tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+        tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
         tc_wait_ld();
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 t4 = reinterpret_cast<const float4*>(lse2)[8 * half + c4];
-          const float lse_v[4] = {t4.x, t4.y, t4.z, t4.w};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int c = 4 * c4 + k;
-            const int col = 32 * half + c;
-            const int qi = q_first + col;
-            float x = __uint_as_float(s[c]) * p.scale_log2;
-            if constexpr (kFeat) {
-              if (qi < p.Sq && kv < p.Sk) {
-                if (p.bias.ptr)
-                  x = fmaf(load_term<kBf16>(p.bias, b * p.bias.sb + h * p.bias.sh +
-                                                        static_cast<long long>(qi) * p.bias.sq + kv),
-                           kLog2e, x);
-                if (p.mask.ptr)
-                  x = fmaf(load_term<kBf16>(p.mask, b * p.mask.sb + h * p.mask.sh +
-                                                        static_cast<long long>(qi) * p.mask.sq + kv),
-                           kLog2e, x);
-              }
-            }
-            float pe = ex2_approx(x - lse_v[k]);
-            if (diag && kv > qi + p.causal_off) pe = 0.f;
-            pv[col] = pe;
-          }
-        }
-        uint32_t pk[16];
         if constexpr (kFeat) {
           if (p.drop.enabled) {
             const uint32_t bh_glob =
                 static_cast<uint32_t>((p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
-            uint32_t bits = 0;
+            uint32_t bits[2] = {0u, 0u};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
+            for (int c = 0; c < 64; ++c) {
               uint32_t rnd[4];
-              philox4x32_10(static_cast<uint32_t>(kv >> 2),
-                            static_cast<uint32_t>(q_first + 32 * half + c), bh_glob, 0u,
-                            p.drop.seed_lo, p.drop.seed_hi, rnd);
+              philox4x32_10(static_cast<uint32_t>(kv >> 2), static_cast<uint32_t>(q_first + c),
+                            bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
               const uint32_t sel = (kv & 3) == 0 ? rnd[0] : (kv & 3) == 1 ? rnd[1]
                                    : (kv & 3) == 2 ? rnd[2] : rnd[3];
-              if (sel >= p.drop.threshold) bits |= (1u << c);
+              if (sel >= p.drop.threshold) bits[c >> 5] |= (1u << (c & 31));
             }
-            keep_bits[half] = bits;
+            keep_lo = bits[0];
+            keep_hi = bits[1];
           }
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float a0 = ((keep_bits[half] >> (2 * c)) & 1u) ? pv[32 * half + 2 * c] * p.drop.inv_keep : 0.f;
-            const float a1 = ((keep_bits[half] >> (2 * c + 1)) & 1u) ? pv[32 * half + 2 * c + 1] * p.drop.inv_keep : 0.f;
-            pk[c] = pack2<kBf16>(a0, a1);
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 16; ++c)
-            pk[c] = pack2<kBf16>(pv[32 * half + 2 * c], pv[32 * half + 2 * c + 1]);
         }
-        tmem_st16(tS + 16 * half, pk);
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 nl = nlse4[c4];
+          const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
+#pragma unroll
+          for (int k2 = 0; k2 < 2; ++k2) {
+            const int c = 4 * c4 + 2 * k2;     // columns c, c + 1
+            float x0 = __uint_as_float(s[c]), x1 = __uint_as_float(s[c + 1]);
+            if constexpr (kFeat) {
+              x0 *= p.scale_log2;
+              x1 *= p.scale_log2;
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int qi = q_first + c + e;
+                float add = 0.f;
+                if (qi < p.Sq && kv < p.Sk) {
+                  if (p.bias.ptr)
+                    add += load_term<kBf16>(p.bias, b * p.bias.sb + h * p.bias.sh +
+                                                        static_cast<long long>(qi) * p.bias.sq + kv);
+                  if (p.mask.ptr)
+                    add += load_term<kBf16>(p.mask, b * p.mask.sb + h * p.mask.sh +
+                                                        static_cast<long long>(qi) * p.mask.sq + kv);
+                }
+                (e == 0 ? x0 : x1) = fmaf(add, kLog2e, e == 0 ? x0 : x1);
+              }
+              x0 += nlv[2 * k2];
+              x1 += nlv[2 * k2 + 1];
+            } else {
+              fma2(x0, x1, x0, x1, p.scale_log2, p.scale_log2, nlv[2 * k2], nlv[2 * k2 + 1]);
+            }
+            float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            if (diag) {
+              if (q_first + c < q_lim) p0 = 0.f;
+              if (q_first + c + 1 < q_lim) p1 = 0.f;
+            }
+            pk[c >> 1] = pack2<kBf16>(p0, p1);
+          }
+        }
+      }
+      if constexpr (kFeat) {
+        if (p.drop.enabled) {
+          // the weights that reach dV carry the dropout mask and its 1/(1-p)
+          uint32_t pd[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const uint32_t bits = (c < 16) ? keep_lo : keep_hi;
+            const int sh = (2 * c) & 31;
+            float a0 = ((bits >> sh) & 1u) ? unpack_lo<kBf16>(pk[c]) * p.drop.inv_keep : 0.f;
+            float a1 = ((bits >> (sh + 1)) & 1u) ? unpack_hi<kBf16>(pk[c]) * p.drop.inv_keep : 0.f;
+            pd[c] = pack2<kBf16>(a0, a1);
+          }
+          tmem_st32(tS, pd);
+        } else {
+          tmem_st32(tS, pk);
+        }
+      } else {
+        tmem_st32(tS, pk);
       }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);
       if (tid == 0) FA2_T(8, it);
 
+      // ---- dS^T = P^T * (dP^T * keep/(1-p) - delta) -> shared memory, 16 bit ------------------
       ok = mbar_wait(bar_dp_full, it & 1, abort_flag);
       if (!ok) break;
       if (tid == 0) FA2_T(9, it);
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t dp[32];
-        tmem_ld32(tdP + 32 * half, dp);
+      {
+        uint32_t dp[64];
+        tmem_ld32(tdP, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+        tmem_ld32(tdP + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
         tc_wait_ld();
-        uint32_t pk[16];
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 t4 = reinterpret_cast<const float4*>(delta)[8 * half + c4];
-          const float dl_v[4] = {t4.x, t4.y, t4.z, t4.w};
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 dl = delta4[c4];
+          const float dlv[4] = {dl.x, dl.y, dl.z, dl.w};
 #pragma unroll
           for (int k2 = 0; k2 < 2; ++k2) {
-            const int c = 2 * c4 + k2;
-            float d0 = __uint_as_float(dp[2 * c]), d1 = __uint_as_float(dp[2 * c + 1]);
+            const int c = 4 * c4 + 2 * k2;
+            float d0 = __uint_as_float(dp[c]), d1 = __uint_as_float(dp[c + 1]);
             if constexpr (kFeat) {
-              d0 = ((keep_bits[half] >> (2 * c)) & 1u) ? d0 * p.drop.inv_keep : 0.f;
-              d1 = ((keep_bits[half] >> (2 * c + 1)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
+              const uint32_t bits = (c < 32) ? keep_lo : keep_hi;
+              d0 = ((bits >> (c & 31)) & 1u) ? d0 * p.drop.inv_keep : 0.f;
+              d1 = ((bits >> ((c + 1) & 31)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
             }
-            const int col = 32 * half + 2 * c;
-            pk[c] = pack2<kBf16>(pv[col] * (d0 - dl_v[2 * k2]), pv[col + 1] * (d1 - dl_v[2 * k2 + 1]));
+            float t0, t1;
+            add2(t0, t1, d0, d1, -dlv[2 * k2], -dlv[2 * k2 + 1]);
+            const float p0 = unpack_lo<kBf16>(pk[c >> 1]), p1 = unpack_hi<kBf16>(pk[c >> 1]);
+            dp[c >> 1] = pack2<kBf16>(p0 * t0, p1 * t1);     // reuse dp[0..31] for the packed dS
           }
         }
-        // dS^T row r, queries [64w + 32 half, +32): four 16-byte chunks of the 128-byte line
+        // dS^T row r, queries [64w, 64w + 64): the eight 16-byte chunks of one 128-byte line
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = half * 4 + q4;
-          *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        for (int q4 = 0; q4 < 8; ++q4) {
+          *reinterpret_cast<uint4*>(ds_row + ((q4 ^ (r & 7)) << 4)) =
+              make_uint4(dp[4 * q4], dp[4 * q4 + 1], dp[4 * q4 + 2], dp[4 * q4 + 3]);
         }
       }
       fence_proxy_async_smem();

@@ -332,6 +332,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
   return r;
 }
+// The two halves of a packed 16-bit pair as floats.
+template <bool kBf16>
+__device__ __forceinline__ float unpack_lo(uint32_t v) {
+  if constexpr (kBf16) {
+    return __uint_as_float(v << 16);
+  } else {
+    return __half2float(__ushort_as_half(static_cast<uint16_t>(v & 0xffffu)));
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ float unpack_hi(uint32_t v) {
+  if constexpr (kBf16) {
+    return __uint_as_float(v & 0xffff0000u);
+  } else {
+    return __half2float(__ushort_as_half(static_cast<uint16_t>(v >> 16)));
+  }
+}
 template <bool kBf16>
 __device__ __forceinline__ float to_float16bit(uint16_t v) {
   if constexpr (kBf16) {
