@@ -119,6 +119,36 @@ int fa2_version(void);
  * (0 = no time-out seen). Synchronises the stream; meant for tests and debugging. */
 int fa2_debug_device_status(void* cuda_stream);
 
+/* Size of the scratch array built into the library for fa2_bwd_static_scratch (32 MiB). */
+#define FA2_BWD_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+/* Backward for callers that cannot give the library a workspace. This entry point has no
+ * counterpart in the reference (there XLA allocates every temporary of the Triton launches).
+ *
+ * Who needs it: code that runs where device memory must not be allocated or where no allocator
+ * is reachable - a host function called from inside a running inference server whose memory
+ * pool is owned by another component, a plugin interface that only forwards input and output
+ * buffers, a real-time loop in which an allocation could stall. Such callers pass the same
+ * inputs and outputs as for fa2_bwd and leave `workspace` / `workspace_bytes` unset (they are
+ * ignored). The scratch (row statistics and the float32 dq accumulator) lives in an array that
+ * is part of the library image: FA2_BWD_STATIC_SCRATCH_BYTES on every GPU that loads the
+ * library, for as long as the process lives.
+ *
+ *  - Limit: fa2_bwd_workspace_bytes(problem) must not exceed FA2_BWD_STATIC_SCRATCH_BYTES,
+ *    i.e. batch * heads_q * ceil(seqlen_q / 128) * 128 * (head_dim + 2) * 4 bytes <= 32 MiB
+ *    (for head_dim 128: 64512 query rows over all batches and heads). Larger problems are
+ *    refused with FA2_ERR_WORKSPACE and a message; nothing is launched.
+ *  - The call allocates and frees nothing (no cudaMalloc / cudaFree, no allocating library
+ *    routine). The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current) and caches it; make that first call before
+ *    starting any stream capture.
+ *  - Every call on a device uses the same array. Its contents from the previous call are
+ *    overwritten: the pre-pass rewrites the statistics and zeroes the accumulator before the main
+ *    kernel adds to it. Two calls that overlap on the GPU (different streams, or the same call
+ *    from two threads) race on the array and give wrong gradients: keep calls on one device in
+ *    stream order. fa2_bwd with caller-owned workspaces has no such restriction. */
+int fa2_bwd_static_scratch(const fa2_bwd_params* params, void* cuda_stream);
+
 /* Profiling hook: arms four CUDA events (cudaEvent_t cast to void*) for the next fa2_bwd call on
  * this thread. They are recorded on that call's stream before the rowsum pre-pass, before the
  * main kernel, after it and after the dq conversion, so a caller can time each kernel of the

@@ -311,4 +311,57 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   return FA2_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Backward without a caller-provided workspace
+// ---------------------------------------------------------------------------------------------
+namespace {
+// Scratch of the backward (row statistics + fp32 dq accumulator) for callers that cannot hand
+// in device memory of their own. One array per GPU that loads the library, held until exit.
+static __device__ __align__(256) unsigned char g_bwd_static_scratch[FA2_BWD_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the array on the current device. In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, so the address is looked up once per
+// device (with that device current) and cached.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return fail(FA2_ERR_CUDA, "cannot identify the current CUDA device");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_bwd_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(FA2_ERR_CUDA, "cudaGetSymbolAddress failed for the static scratch: %s",
+                  cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return FA2_OK;
+}
+}  // namespace
+
+int fa2_bwd_static_scratch(const fa2_bwd_params* a, void* cuda_stream) {
+  if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
+  const int rc = check_problem(a->p);
+  if (rc) return rc;
+  const size_t need = bwd_workspace(a->p).total;
+  if (need > static_cast<size_t>(FA2_BWD_STATIC_SCRATCH_BYTES))
+    return fail(FA2_ERR_WORKSPACE,
+                "this problem needs %zu bytes of scratch; the built-in scratch holds %zu bytes "
+                "(batch * heads_q * ceil(seqlen_q/128)*128 * (head_dim + 2) * 4 must not exceed it); "
+                "use fa2_bwd with a workspace instead",
+                need, static_cast<size_t>(FA2_BWD_STATIC_SCRATCH_BYTES));
+  void* scratch = nullptr;
+  const int rs = static_scratch_address(&scratch);
+  if (rs) return rs;
+  fa2_bwd_params b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = FA2_BWD_STATIC_SCRATCH_BYTES;
+  return fa2_bwd(&b, cuda_stream);
+}
+
 }  // extern "C"

@@ -25,7 +25,9 @@ EXPORTED_SYMBOLS = (
     "fa2_version",
     "fa2_debug_device_status",
     "fa2_debug_bwd_stage_events",
+    "fa2_bwd_static_scratch",
 )
+FA2_BWD_STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 
 class Strides(C.Structure):
@@ -129,6 +131,8 @@ def load() -> C.CDLL:
     lib.fa2_version.restype = C.c_int
     lib.fa2_debug_device_status.argtypes = [C.c_void_p]
     lib.fa2_debug_device_status.restype = C.c_int
+    lib.fa2_bwd_static_scratch.argtypes = [C.POINTER(BwdParams), C.c_void_p]
+    lib.fa2_bwd_static_scratch.restype = C.c_int
     lib.fa2_debug_bwd_stage_events.argtypes = [C.POINTER(C.c_void_p)]
     lib.fa2_debug_bwd_stage_events.restype = C.c_int
     _lib = lib
