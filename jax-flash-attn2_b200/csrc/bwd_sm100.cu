@@ -73,7 +73,7 @@ __device__ __forceinline__ void bulk_reduce_add_f32(float* dst, uint32_t src_sme
 
 #ifdef FA2_TRACE
 // Development aid (not compiled by default): per-role time stamps of CTA 0.
-__device__ long long g_trace[16 * 4096];
+__device__ long long g_trace[48 * 4096];
 #define FA2_T(role, idx) do { if (blockIdx.x == FA2_TRACE_CTA && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
 #else
 #define FA2_T(role, idx) do { } while (0)
@@ -302,41 +302,48 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_dq = make_idesc(kBf16, 128, D, true, true);
       bool ok = true;
 
+      // Shared-memory descriptors are built once; every MMA only adds a constant to the start
+      // address (the issuing thread is a serial instruction stream: what it executes per MMA
+      // delays every barrier it has to look at).
+      const uint64_t dK_k = make_sdesc(sK, 16, 1024), dK_mn = make_sdesc(sK, L::kBlockBytes, 1024);
+      const uint64_t dV_k = make_sdesc(sV, 16, 1024);
+      const uint64_t dQ_k0 = make_sdesc(sQ, 16, 1024), dQ_mn0 = make_sdesc(sQ, L::kBlockBytes, 1024);
+      const uint64_t ddO_k = make_sdesc(sdO, 16, 1024), ddO_mn = make_sdesc(sdO, L::kBlockBytes, 1024);
+      const uint64_t ddS_k = make_sdesc(sdS, 16, 1024), ddS_mn = make_sdesc(sdS, L::kBlockBytes, 1024);
+
       // D[kv, q] = A[kv, d] * B[q, d]^T, both operands K-major over the head dim
-      auto issue_kd = [&](uint32_t d_col, uint32_t a0, uint32_t b0) {
+      auto issue_kd = [&](uint32_t d_col, uint64_t a_desc, uint64_t b_desc) {
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
-          mma_ss(tmem_base + d_col, make_sdesc(a0 + off, 16, 1024), make_sdesc(b0 + off, 16, 1024),
-                 idesc_s, k > 0 ? 1u : 0u);
+          mma_ss(tmem_base + d_col, sdesc_advance(a_desc, off), sdesc_advance(b_desc, off), idesc_s,
+                 k > 0 ? 1u : 0u);
         }
       };
-      auto issue_dv = [&](uint32_t do_tile, bool first) {
+      auto issue_dv = [&](bool first) {
 #pragma unroll
         for (int k = 0; k < kBM / 16; ++k) {
           // P^T for queries [16k, 16k+16): 8 packed columns; the two 64-query halves were written
           // by different warpgroups at columns 0 and 64 of the S region.
           const uint32_t a_col = kColS + (k < 4 ? 8 * k : 64 + 8 * (k - 4));
-          mma_ts(tmem_base + kColdV, tmem_base + a_col,
-                 make_sdesc(do_tile + k * 2048, L::kBlockBytes, 1024), idesc_dv,
+          mma_ts(tmem_base + kColdV, tmem_base + a_col, sdesc_advance(ddO_mn, k * 2048), idesc_dv,
                  (first && k == 0) ? 0u : 1u);
         }
       };
-      auto issue_dk = [&](uint32_t q_tile, bool first) {
+      auto issue_dk = [&](uint64_t q_mn, bool first) {
 #pragma unroll
         for (int k = 0; k < kBM / 16; ++k) {
           const uint32_t a_off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
-          mma_ss(tmem_base + kColdK, make_sdesc(sdS + a_off, 16, 1024),
-                 make_sdesc(q_tile + k * 2048, L::kBlockBytes, 1024), idesc_dk,
-                 (first && k == 0) ? 0u : 1u);
+          mma_ss(tmem_base + kColdK, sdesc_advance(ddS_k, a_off), sdesc_advance(q_mn, k * 2048),
+                 idesc_dk, (first && k == 0) ? 0u : 1u);
         }
       };
       auto issue_dq = [&]() {
 #pragma unroll
         for (int k = 0; k < kBN / 16; ++k) {
           // A = dS (M = query, contiguous in the dS^T rows; K = key rows), B = K tile, both MN-major
-          mma_ss(tmem_base + kColdQ, make_sdesc(sdS + k * 2048, L::kBlockBytes, 1024),
-                 make_sdesc(sK + k * 2048, L::kBlockBytes, 1024), idesc_dq, k > 0 ? 1u : 0u);
+          mma_ss(tmem_base + kColdQ, sdesc_advance(ddS_mn, k * 2048), sdesc_advance(dK_mn, k * 2048),
+                 idesc_dq, k > 0 ? 1u : 0u);
         }
       };
 
@@ -344,13 +351,13 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) ok = mbar_wait(bar_q_full(0), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        issue_kd(kColS, sK, sQ);
+        issue_kd(kColS, dK_k, dQ_k0);
         mma_commit(bar_s_full);
         ok = mbar_wait(bar_do_full, 0, abort_flag);
       }
       if (ok) {
         tc_fence_after();
-        issue_kd(kColdP, sV, sdO);
+        issue_kd(kColdP, dV_k, ddO_k);
         mma_commit(bar_dp_full);
       }
       for (int it = 0; it < T && ok; ++it) {
@@ -362,13 +369,15 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!ok) break;
         FA2_T(0, it);
         tc_fence_after();
-        issue_dv(sdO, it == 0);
+        issue_dv(it == 0);
         mma_commit(bar_do_empty);          // the single dO buffer can be refilled
         if (has_next) {
+          FA2_T(40, it);
           ok = mbar_wait(bar_q_full(nx), par_next, abort_flag);
           if (!ok) break;
+          FA2_T(41, it);
           tc_fence_after();
-          issue_kd(kColS, sK, sQ + nx * L::kTileBytes);
+          issue_kd(kColS, dK_k, sdesc_advance(dQ_k0, nx * L::kTileBytes));
           mma_commit(bar_s_full);
         }
         FA2_T(1, it);
@@ -378,7 +387,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_fence_after();
         issue_dq();
         mma_commit(bar_dq_full);
-        issue_dk(sQ + st * L::kTileBytes, it == 0);
+        issue_dk(sdesc_advance(dQ_mn0, st * L::kTileBytes), it == 0);
         mma_commit(bar_q_empty(st));
         if (has_next) {
           FA2_T(3, it);
@@ -387,7 +396,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!ok) break;
           FA2_T(4, it);
           tc_fence_after();
-          issue_kd(kColdP, sV, sdO);
+          issue_kd(kColdP, dV_k, ddO_k);
           mma_commit(bar_dp_full);
         }
       }
@@ -473,6 +482,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
       if (tid == 0) FA2_T(7, it);
+      if (lane == 0) FA2_T(32 + warp, it);
       tc_fence_after();
       // some (query, key) pairs of this step are above the causal diagonal
       const bool diag = kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off);
@@ -486,6 +496,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(s[0]));
         tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
         tc_wait_ld();
+        if (tid == 0) FA2_T(11, it);
         if constexpr (kFeat) {
           if (p.drop.enabled) {
             const uint32_t bh_glob =
@@ -562,10 +573,12 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       } else {
         tmem_st32(tS, pk);
       }
+      if (tid == 0) FA2_T(14, it);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);
       if (tid == 0) FA2_T(8, it);
+      if (lane == 0) FA2_T(16 + warp, it);
 
       // ---- dS^T = P^T * (dP^T * keep/(1-p) - delta) -> shared memory, 16 bit ------------------
       ok = mbar_wait(bar_dp_full, it & 1, abort_flag);
@@ -577,6 +590,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_ld32(tdP, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
         tmem_ld32(tdP + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
         tc_wait_ld();
+        if (tid == 0) FA2_T(12, it);
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 dl = delta4[c4];
@@ -603,9 +617,11 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               make_uint4(dp[4 * q4], dp[4 * q4 + 1], dp[4 * q4 + 2], dp[4 * q4 + 3]);
         }
       }
+      if (tid == 0) FA2_T(13, it);
       fence_proxy_async_smem();
       mbar_arrive(bar_ds_full);
       if (tid == 0) FA2_T(10, it);
+      if (lane == 0) FA2_T(24 + warp, it);
     }
 
     // ---- epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV ---------------------

@@ -225,24 +225,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       constexpr uint32_t idesc_o = make_idesc(kBf16, kBM, D, false, true);
       bool ok = true;
 
+      // Descriptors are built once; each MMA adds a constant to the start address.
+      const uint64_t dQ0 = make_sdesc(sQ, 16, 1024);
+      const uint64_t dKV_k0 = make_sdesc(sKV, 16, 1024);                 // K tile, K-major
+      const uint64_t dKV_mn0 = make_sdesc(sKV, L::kBlockBytes, 1024);    // V tile, MN-major
       auto issue_s = [&](int t, int slot) {
-        const uint32_t a0 = sQ + t * L::kQTileBytes;
-        const uint32_t b0 = sKV + slot * L::kKVTileBytes;
+        const uint64_t a0 = sdesc_advance(dQ0, t * L::kQTileBytes);
+        const uint64_t b0 = sdesc_advance(dKV_k0, slot * L::kKVTileBytes);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
-          mma_ss(tmem_base + kColS + t * kBN, make_sdesc(a0 + off, 16, 1024),
-                 make_sdesc(b0 + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+          mma_ss(tmem_base + kColS + t * kBN, sdesc_advance(a0, off), sdesc_advance(b0, off), idesc_s,
+                 k > 0 ? 1u : 0u);
         }
         mma_commit(bar_s_full(t));
       };
       auto issue_o = [&](int t, int slot, bool first) {
-        const uint32_t b0 = sKV + slot * L::kKVTileBytes;
+        const uint64_t b0 = sdesc_advance(dKV_mn0, slot * L::kKVTileBytes);
 #pragma unroll
         for (int k = 0; k < kBN / 16; ++k) {
           mma_ts(tmem_base + kColO + t * D, tmem_base + kColS + t * kBN + k * 8,
-                 make_sdesc(b0 + k * 2048, L::kBlockBytes, 1024), idesc_o,
-                 (first && k == 0) ? 0u : 1u);
+                 sdesc_advance(b0, k * 2048), idesc_o, (first && k == 0) ? 0u : 1u);
         }
       };
 

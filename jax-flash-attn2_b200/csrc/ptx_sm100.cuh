@@ -173,6 +173,12 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr, uint32_t lbo_byte
   return d;
 }
 
+// The same descriptor for a start address `bytes` further on (bytes is a multiple of 16; the
+// address field cannot carry into the next field while the operand stays inside shared memory).
+__device__ __forceinline__ uint64_t sdesc_advance(uint64_t desc, uint32_t bytes) {
+  return desc + static_cast<uint64_t>(bytes >> 4);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                        uint32_t idesc, uint32_t accumulate) {
