@@ -143,29 +143,45 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
 // ---------------------------------------------------------------------------------------------
 // 3. dq conversion
 // ---------------------------------------------------------------------------------------------
+// One block converts one 128-row tile. The accumulator is read in its own order (coalesced
+// float4 runs), transposed through shared memory 64 columns at a time, and written so that eight
+// consecutive threads cover the 128 contiguous bytes those columns take in a row of dq.
 template <int D, bool kBf16>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long long sb,
                long long ss, long long sh, int Sq, int Hq, int nQ, float scale) {
+  constexpr int kPitch = 129;                       // float4 per column chunk: 128 rows + 1 pad
+  __shared__ float4 tile[16 * kPitch];              // 16 chunks of 4 columns = 64 columns
   const int i = blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / Hq, h = bh - b * Hq;
-  const int r = threadIdx.x;
-  const int row = i * kBM + r;
-  if (row >= Sq) return;
+  const int tid = threadIdx.x;
   const float4* src = reinterpret_cast<const float4*>(dq_acc) +
-                      (static_cast<long long>(bh) * nQ + i) * (kBM * D / 4) + r;
-  uint4* dst = reinterpret_cast<uint4*>(dq + b * sb + row * ss + h * sh);
+                      (static_cast<long long>(bh) * nQ + i) * (kBM * D / 4);
+  for (int part = 0; part < D / 64; ++part) {
+    if (part) __syncthreads();
 #pragma unroll
-  for (int c8 = 0; c8 < D / 8; ++c8) {
-    const float4 x = src[(2 * c8) * 128];
-    const float4 y = src[(2 * c8 + 1) * 128];
-    uint4 v;
-    v.x = pack2<kBf16>(x.x * scale, x.y * scale);
-    v.y = pack2<kBf16>(x.z * scale, x.w * scale);
-    v.z = pack2<kBf16>(y.x * scale, y.y * scale);
-    v.w = pack2<kBf16>(y.z * scale, y.w * scale);
-    dst[c8] = v;
+    for (int k = 0; k < 8; ++k) {
+      const int idx = tid + k * 256;                // 0 .. 2047 = 16 chunks x 128 rows
+      tile[(idx >> 7) * kPitch + (idx & 127)] = src[part * 2048 + idx];
+    }
+    __syncthreads();
+    const int j = tid & 7;                          // 16-byte piece of the 128-byte row segment
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+      const int r = pass * 32 + (tid >> 3);
+      const int row = i * kBM + r;
+      if (row < Sq) {
+        const float4 x = tile[(2 * j) * kPitch + r];
+        const float4 y = tile[(2 * j + 1) * kPitch + r];
+        uint4 v;
+        v.x = pack2<kBf16>(x.x * scale, x.y * scale);
+        v.y = pack2<kBf16>(x.z * scale, x.w * scale);
+        v.z = pack2<kBf16>(y.x * scale, y.y * scale);
+        v.w = pack2<kBf16>(y.z * scale, y.w * scale);
+        reinterpret_cast<uint4*>(dq + b * sb + row * ss + h * sh)[part * 8 + j] = v;
+      }
+    }
   }
 }
 
@@ -713,7 +729,7 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   }
   if (e != cudaSuccess) return e;
   mark(2);
-  bwd_dq_convert<D, kBf16><<<grid, 128, 0, stream>>>(kp.dq_acc, static_cast<uint16_t*>(a.dq),
+  bwd_dq_convert<D, kBf16><<<grid, 256, 0, stream>>>(kp.dq_acc, static_cast<uint16_t*>(a.dq),
                                                      a.dq_strides[0], a.dq_strides[1],
                                                      a.dq_strides[2], kp.Sq, kp.Hq, nQ, kp.scale);
   mark(3);
