@@ -91,7 +91,7 @@ int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, 
   return FA2_OK;
 }
 
-int check_problem(const fa2_problem& p) {
+int check_problem(const fa2_problem& p, bool backward = false) {
   if (p.batch <= 0 || p.seqlen_q <= 0 || p.seqlen_k <= 0 || p.heads_q <= 0 || p.heads_kv <= 0)
     return fail(FA2_ERR_INVALID_ARG, "batch, sequence lengths and head counts must be positive");
   if (p.heads_q % p.heads_kv != 0)
@@ -99,8 +99,9 @@ int check_problem(const fa2_problem& p) {
                 p.heads_q, p.heads_kv);
   if (p.dtype != FA2_FP16 && p.dtype != FA2_BF16)
     return fail(FA2_ERR_UNSUPPORTED, "only fp16 and bf16 inputs are supported");
-  if (p.head_dim != 64 && p.head_dim != 128)
-    return fail(FA2_ERR_UNSUPPORTED, "head_dim %d is not supported (64 and 128 are)", p.head_dim);
+  if (p.head_dim != 64 && p.head_dim != 128 && !(p.head_dim == 256 && !backward))
+    return fail(FA2_ERR_UNSUPPORTED,
+                "head_dim %d is not supported (forward: 64, 128, 256; backward: 64, 128)", p.head_dim);
   if (!(p.dropout_p >= 0.f) || !(p.dropout_p < 1.f))
     return fail(FA2_ERR_INVALID_ARG, "dropout_p must be in [0, 1)");
   if (!std::isfinite(p.softmax_scale))
@@ -148,7 +149,7 @@ void make_dropout(DropoutDev* d, const fa2_problem& p) {
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct BwdWorkspace {
-  size_t delta_off, dq_off, total;
+  size_t delta_off, dq_off, absmax_off, total;
   int sq_pad;
 };
 BwdWorkspace bwd_workspace(const fa2_problem& p) {
@@ -157,7 +158,8 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * w.sq_pad;
   w.delta_off = 0;
   w.dq_off = align_up(2 * rows * sizeof(float), 256);   // (lse2, delta) per row
-  w.total = w.dq_off + align_up(rows * p.head_dim * sizeof(float), 256);
+  w.absmax_off = w.dq_off + align_up(rows * p.head_dim * sizeof(float), 256);
+  w.total = w.absmax_off + 256;   // one word: max|dO| of the call (fp16 range guard)
   return w;
 }
 
@@ -237,14 +239,14 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
 }
 
 size_t fa2_bwd_workspace_bytes(const fa2_problem* problem) {
-  if (!problem || check_problem(*problem)) return 0;
+  if (!problem || check_problem(*problem, true)) return 0;
   return bwd_workspace(*problem).total;
 }
 
 int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
   const fa2_problem& p = a->p;
-  int rc = check_problem(p);
+  int rc = check_problem(p, true);
   if (rc) return rc;
   if (!a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->dq || !a->dk || !a->dv)
     return fail(FA2_ERR_INVALID_ARG, "q, k, v, o, d_o, lse, dq, dk and dv must be non-null");
@@ -283,6 +285,7 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   kp.delta = reinterpret_cast<float*>(ws + w.delta_off);
   kp.dq_acc = reinterpret_cast<float*>(ws + w.dq_off);
   kp.Sq_pad = w.sq_pad;
+  kp.do_absmax_bits = reinterpret_cast<const unsigned*>(ws + w.absmax_off);
   if ((rc = make_score_term(&kp.bias, a->bias, p, "bias")) ||
       (rc = make_score_term(&kp.mask, a->mask, p, "mask")))
     return rc;
@@ -299,7 +302,7 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   L.d_o = a->d_o; L.do_strides[0] = a->do_strides.b; L.do_strides[1] = a->do_strides.s; L.do_strides[2] = a->do_strides.h;
   L.dq = a->dq; L.dq_strides[0] = a->dq_strides.b; L.dq_strides[1] = a->dq_strides.s; L.dq_strides[2] = a->dq_strides.h;
   L.delta = reinterpret_cast<float*>(ws + w.delta_off);
-  L.dq_acc_bytes = w.total - w.dq_off;
+  L.dq_acc_bytes = w.absmax_off - w.dq_off;
 
   for (int i = 0; i < 4; ++i) {
     L.stage_events[i] = g_bwd_events[i];
@@ -346,7 +349,7 @@ int static_scratch_address(void** out) {
 
 int fa2_bwd_static_scratch(const fa2_bwd_params* a, void* cuda_stream) {
   if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
-  const int rc = check_problem(a->p);
+  const int rc = check_problem(a->p, true);
   if (rc) return rc;
   const size_t need = bwd_workspace(a->p).total;
   if (need > static_cast<size_t>(FA2_BWD_STATIC_SCRATCH_BYTES))

@@ -79,6 +79,18 @@ __device__ long long g_trace[48 * 4096];
 #define FA2_T(role, idx) do { } while (0)
 #endif
 
+// Power of two that brings max|dO| to [1, 2): fp16 inputs only. With a loss like mean(out) the
+// cotangent is ~1e-6 and dS = P (dP - delta) would sit in fp16's subnormal range; scaling dS by
+// this factor (and dK, dQ back by its inverse) keeps the 16-bit operand of the dK / dQ MMAs in
+// the normal range. Exact: powers of two do not round.
+__device__ __forceinline__ float do_scale_from_bits(const unsigned* bits) {
+  if (bits == nullptr) return 1.f;
+  const float mx = __uint_as_float(__ldg(bits));
+  if (!(mx > 0.f) || !(mx < INFINITY)) return 1.f;
+  const int e = static_cast<int>(floorf(log2f(mx)));
+  return exp2f(static_cast<float>(-max(-60, min(60, e))));
+}
+
 template <bool kBf16>
 __device__ __forceinline__ float load_term(const ScoreTermDev& t, long long idx) {
   if (t.is_f32) return __ldg(static_cast<const float*>(t.ptr) + idx);
@@ -97,7 +109,8 @@ __global__ void __launch_bounds__(128)
 bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                long long o_sb, long long o_ss, long long o_sh, long long do_sb, long long do_ss,
                long long do_sh, const float* __restrict__ lse, long long lse_sb, long long lse_sh,
-               float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ) {
+               float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ,
+               unsigned* __restrict__ do_absmax_bits) {
   const int i = blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / Hq, h = bh - b * Hq;
@@ -107,6 +120,7 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
   const int sub = tid % kLanesPerRow;
   const long long tile = (static_cast<long long>(bh) * nQ + i);
   float* st = stats + tile * 256;
+  float amax = 0.f;
   for (int r0 = 0; r0 < kBM; r0 += kRowsPerPass) {
     const int r = r0 + tid / kLanesPerRow;
     const int row = i * kBM + r;
@@ -121,6 +135,12 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                    to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] & 0xffff)), acc);
         acc = fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(aw[k] >> 16)),
                    to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] >> 16)), acc);
+        if constexpr (!kBf16) {
+          const float g0 = fabsf(to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] & 0xffff)));
+          const float g1 = fabsf(to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] >> 16)));
+          if (g0 < INFINITY) amax = fmaxf(amax, g0);
+          if (g1 < INFINITY) amax = fmaxf(amax, g1);
+        }
       }
     }
 #pragma unroll
@@ -138,6 +158,17 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
   }
   float4* acc4 = reinterpret_cast<float4*>(dq_acc + tile * (kBM * D));
   for (int k = tid; k < kBM * D / 4; k += 128) acc4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if constexpr (!kBf16) {
+    // block maximum of |dO| -> one atomic per block (non-negative floats order like their bits)
+    __shared__ float warp_max[4];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
+    __syncthreads();
+    if (tid == 0 && do_absmax_bits != nullptr)
+      atomicMax(do_absmax_bits, __float_as_uint(fmaxf(fmaxf(warp_max[0], warp_max[1]),
+                                                      fmaxf(warp_max[2], warp_max[3]))));
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -149,7 +180,9 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(256)
 bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long long sb,
-               long long ss, long long sh, int Sq, int Hq, int nQ, float scale) {
+               long long ss, long long sh, int Sq, int Hq, int nQ, float scale_in,
+               const unsigned* __restrict__ do_absmax_bits) {
+  const float scale = scale_in / (kBf16 ? 1.f : do_scale_from_bits(do_absmax_bits));
   constexpr int kPitch = 129;                       // float4 per column chunk: 128 rows + 1 pad
   __shared__ float4 tile[16 * kPitch];              // 16 chunks of 4 columns = 64 columns
   const int i = blockIdx.x;
@@ -484,6 +517,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t tdP = tmem_base + lane_base + kColdP + 64 * w;
     const float* stats_s = reinterpret_cast<const float*>(smem_gen + L::kStatsOff);
     uint8_t* ds_row = smem_gen + L::kdSOff + w * L::kBlockBytes + r * 128;
+    const float do_scale = kBf16 ? 1.f : do_scale_from_bits(p.do_absmax_bits);
     bool ok = true;
 
     for (int it = 0; it < T; ++it) {
@@ -622,6 +656,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             }
             float t0, t1;
             add2(t0, t1, d0, d1, -dlv[2 * k2], -dlv[2 * k2 + 1]);
+            if constexpr (!kBf16) fma2(t0, t1, t0, t1, do_scale, do_scale, 0.f, 0.f);
             const float p0 = unpack_lo<kBf16>(pk[c >> 1]), p1 = unpack_hi<kBf16>(pk[c >> 1]);
             dp[c >> 1] = pack2<kBf16>(p0 * t0, p1 * t1);     // reuse dp[0..31] for the packed dS
           }
@@ -645,7 +680,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok) {
       tc_fence_after();
       const uint32_t tAcc = tmem_base + lane_base + (w == 0 ? kColdK : kColdV);
-      const float f = (w == 0) ? p.scale : 1.f;
+      const float f = (w == 0) ? p.scale / do_scale : 1.f;
       uint8_t* stage = smem_gen + L::kQOff + w * L::kTileBytes;   // both Q stages are free now
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -712,11 +747,16 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   auto mark = [&](int i) {
     if (a.stage_events[i]) cudaEventRecord(a.stage_events[i], stream);
   };
+  unsigned* absmax = const_cast<unsigned*>(kp.do_absmax_bits);
+  if (!kBf16) {
+    const cudaError_t em = cudaMemsetAsync(absmax, 0, sizeof(unsigned), stream);
+    if (em != cudaSuccess) return em;
+  }
   mark(0);
   bwd_pre_kernel<D, kBf16><<<grid, 128, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
-      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ);
+      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ, kBf16 ? nullptr : absmax);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);
@@ -731,7 +771,8 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   mark(2);
   bwd_dq_convert<D, kBf16><<<grid, 256, 0, stream>>>(kp.dq_acc, static_cast<uint16_t*>(a.dq),
                                                      a.dq_strides[0], a.dq_strides[1],
-                                                     a.dq_strides[2], kp.Sq, kp.Hq, nQ, kp.scale);
+                                                     a.dq_strides[2], kp.Sq, kp.Hq, nQ, kp.scale,
+                                                     kBf16 ? nullptr : kp.do_absmax_bits);
   mark(3);
   return cudaGetLastError();
 }

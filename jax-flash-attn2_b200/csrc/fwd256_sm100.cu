@@ -1,0 +1,257 @@
+// Forward attention kernel for head dim 256 on sm_100a.
+//
+// Same job as fwd_kernel (fwd_sm100.cu) and the same reference counterpart
+// (jax_flash_attn2/flash_attention_triton/_forward_triton.py:60-164, 213-459), with the tile
+// plan the tensor-memory budget of D = 256 forces: the O accumulator alone takes 256 of the 512
+// columns, so one CTA owns ONE 128-row query tile and the other 256 columns hold two S buffers.
+// While the softmax warpgroup works on S_j, the tensor core already computes S_{j+1} into the
+// other buffer, and P_j (16 bit, over S_j) then feeds O += P_j V_j.
+//   warps 0-3 : softmax, one thread per query row
+//   warp  4   : tcgen05.mma issuer
+//   warp  5   : TMA producer: Q once; K tiles through slot 0 and V tiles through slot 1
+// Shared memory: Q 64 KiB + K slot 64 KiB + V slot 64 KiB.
+#include "fwd_launch.cuh"
+#include "fwd_row.cuh"
+#include "ptx_sm100.cuh"
+
+namespace fa2 {
+
+namespace {
+
+constexpr int kD = 256;
+constexpr int kThreads256 = 192;
+
+struct Smem256 {
+  static constexpr int kQTileBytes = kBM * kD * 2;    // 64 KiB = 4 blocks of [128][64]
+  static constexpr int kKVTileBytes = kBN * kD * 2;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + kQTileBytes;
+  static constexpr int kVOff = kKOff + kKVTileBytes;
+  static constexpr int kBarOff = kVOff + kKVTileBytes;
+  // barriers: q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2], pv_done, o_full
+  static constexpr int kNumBars = 11;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kDynamicBytes = kTotal + 1024;
+};
+
+}  // namespace
+
+template <bool kBf16, bool kCausal, bool kFeat>
+__global__ void __launch_bounds__(kThreads256, 1)
+fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+              const FwdKernelParams p) {
+  using L = Smem256;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base + L::kQOff, sK = smem_base + L::kKOff, sV = smem_base + L::kVOff;
+  const uint32_t bars = smem_base + L::kBarOff;
+  const uint32_t bar_q_full = bars, bar_k_full = bars + 8, bar_k_empty = bars + 16;
+  const uint32_t bar_v_full = bars + 24, bar_v_empty = bars + 32;
+  auto bar_s_full = [&](int s) { return bars + 8u * (5 + s); };
+  auto bar_p_full = [&](int s) { return bars + 8u * (7 + s); };
+  const uint32_t bar_pv_done = bars + 8u * 9, bar_o_full = bars + 8u * 10;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- work item: one 128-row query tile of one (batch, head); longest tiles first if causal --
+  const int nbh = p.B * p.Hq;
+  const int n_qtiles = (p.Sq + kBM - 1) / kBM;
+  const int rank = blockIdx.x / nbh;
+  const int bh = blockIdx.x - rank * nbh;
+  const int qt = kCausal ? (n_qtiles - 1 - rank) : rank;
+  const int b = bh / p.Hq;
+  const int h = bh - b * p.Hq;
+  const int hk = h / p.G;
+  const int q0 = qt * kBM;
+  int nt;
+  if (kCausal) {
+    const int row_last = min(q0 + kBM - 1, p.Sq - 1);
+    const int last_col = min(p.Sk - 1, row_last + p.causal_off);
+    nt = last_col >= 0 ? last_col / kBN + 1 : 0;
+  } else {
+    nt = (p.Sk + kBN - 1) / kBN;
+  }
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_k_full, 1);
+    mbar_init(bar_k_empty, 1);
+    mbar_init(bar_v_full, 1);
+    mbar_init(bar_v_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_s_full(s), 1);
+      mbar_init(bar_p_full(s), kBM);
+    }
+    mbar_init(bar_pv_done, 1);
+    mbar_init(bar_o_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 5 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColO = 0, kColS = 256;   // S buffer s at kColS + 128 s
+
+  if (warp == 5) {
+    // =========================== TMA producer ================================================
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar_q_full, L::kQTileBytes);
+      tma_load_5d(sQ, &tmQ, bar_q_full, 0, q0, 0, h, b);
+      bool ok = true;
+      for (int j = 0; j < nt && ok; ++j) {
+        ok = mbar_wait(bar_k_empty, (j & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_k_full, L::kKVTileBytes);
+        tma_load_5d(sK, &tmK, bar_k_full, 0, j * kBN, 0, hk, b);
+        ok = mbar_wait(bar_v_empty, (j & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_v_full, L::kKVTileBytes);
+        tma_load_5d(sV, &tmV, bar_v_full, 0, j * kBN, 0, hk, b);
+      }
+      if (!ok) atomicOr(p.status, 1);
+    }
+    __syncwarp();
+  } else if (warp == 4) {
+    // =========================== MMA issuer ==================================================
+    if (lane == 0 && nt > 0) {
+      constexpr uint32_t idesc_s = make_idesc(kBf16, kBM, kBN, false, false);
+      constexpr uint32_t idesc_o = make_idesc(kBf16, kBM, kD, false, true);
+      const uint64_t dQ = make_sdesc(sQ, 16, 1024);
+      const uint64_t dK = make_sdesc(sK, 16, 1024);
+      const uint64_t dV = make_sdesc(sV, kBlockBytes, 1024);
+      bool ok = true;
+      auto issue_s = [&](int buf) {
+#pragma unroll
+        for (int k = 0; k < kD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kBlockBytes + (k & 3) * 32;
+          mma_ss(tmem_base + kColS + buf * kBN, sdesc_advance(dQ, off), sdesc_advance(dK, off),
+                 idesc_s, k > 0 ? 1u : 0u);
+        }
+        mma_commit(bar_s_full(buf));
+        mma_commit(bar_k_empty);
+      };
+      ok = mbar_wait(bar_q_full, 0, abort_flag);
+      if (ok) ok = mbar_wait(bar_k_full, 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < nt && ok; ++j) {
+        const int buf = j & 1;
+        if (j + 1 < nt) {
+          ok = mbar_wait(bar_k_full, (j + 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(buf ^ 1);
+        }
+        ok = mbar_wait(bar_v_full, j & 1, abort_flag);
+        if (ok) ok = mbar_wait(bar_p_full(buf), (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < kBN / 16; ++k) {
+          mma_ts(tmem_base + kColO, tmem_base + kColS + buf * kBN + k * 8,
+                 sdesc_advance(dV, k * 2048), idesc_o, (j == 0 && k == 0) ? 0u : 1u);
+        }
+        mma_commit(bar_v_empty);
+        mma_commit(bar_pv_done);
+        if (j + 1 == nt) mma_commit(bar_o_full);
+      }
+      if (!ok) atomicOr(p.status, 2);
+    }
+    __syncwarp();
+  } else {
+    // =========================== softmax + epilogue ==========================================
+    const int r = tid;                         // row inside the tile == TMEM lane
+    const int qi = q0 + r;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tO = tmem_base + lane_base + kColO;
+    const int row_lim = kCausal ? min(p.Sk - 1, qi + p.causal_off) : p.Sk - 1;
+    const float sc = kFeat ? 1.0f : p.scale_log2;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < nt; ++j) {
+      const int buf = j & 1;
+      ok = mbar_wait(bar_s_full(buf), (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      const uint32_t tS = tmem_base + lane_base + kColS + buf * kBN;
+      // O may only be rescaled once the previous P.V has finished accumulating into it
+      auto wait_pv = [&] {
+        if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag)) ok = false;
+        tc_fence_after();
+      };
+      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv);
+      mbar_arrive(bar_p_full(buf));
+      if (!ok) break;
+    }
+
+    if (ok) ok = mbar_wait(bar_q_full, 0, abort_flag);
+    if (ok && nt > 0) ok = mbar_wait(bar_o_full, 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      epilogue_row<kD, kBf16, kFeat>(tO, nt > 0, smem_gen + L::kQOff, r, p, b, h, qi, sc, m, l);
+    }
+    named_bar_sync(1, kBM);
+    if (ok && r == 0 && !*abort_flag) {
+      tma_store_5d(&tmO, sQ, 0, q0, 0, h, b);
+      tma_store_commit();
+      tma_store_wait_read0();
+    }
+    if (!ok && r == 0) atomicOr(p.status, 4);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <bool kBf16, bool kCausal, bool kFeat>
+static cudaError_t launch256_one(const FwdLaunch& a, cudaStream_t stream) {
+  auto kern = fwd256_kernel<kBf16, kCausal, kFeat>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Smem256::kDynamicBytes);
+  if (e != cudaSuccess) return e;
+  const long long nblocks =
+      static_cast<long long>((a.kp.Sq + kBM - 1) / kBM) * a.kp.B * a.kp.Hq;
+  kern<<<static_cast<unsigned>(nblocks), kThreads256, Smem256::kDynamicBytes, stream>>>(
+      a.tmQ, a.tmK, a.tmV, a.tmO, a.kp);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fwd256(const FwdLaunch& a, cudaStream_t stream) {
+  const int key = (a.bf16 ? 4 : 0) | (a.causal ? 2 : 0) | (a.feat ? 1 : 0);
+  switch (key) {
+    case 0: return launch256_one<false, false, false>(a, stream);
+    case 1: return launch256_one<false, false, true>(a, stream);
+    case 2: return launch256_one<false, true, false>(a, stream);
+    case 3: return launch256_one<false, true, true>(a, stream);
+    case 4: return launch256_one<true, false, false>(a, stream);
+    case 5: return launch256_one<true, false, true>(a, stream);
+    case 6: return launch256_one<true, true, false>(a, stream);
+    default: return launch256_one<true, true, true>(a, stream);
+  }
+}
+
+}  // namespace fa2

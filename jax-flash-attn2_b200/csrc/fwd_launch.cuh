@@ -17,4 +17,7 @@ struct FwdLaunch {
 // Launches the forward kernel specialised for (head_dim, dtype, causal, score terms/dropout).
 cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream);
 
+// Head dim 256 variant (one query tile per CTA, two S buffers); called by launch_fwd.
+cudaError_t launch_fwd256(const FwdLaunch& a, cudaStream_t stream);
+
 }  // namespace fa2

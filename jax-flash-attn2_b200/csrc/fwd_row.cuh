@@ -1,0 +1,226 @@
+// Per-row pieces of the forward kernels: one thread owns one query row (one tensor-memory lane).
+// Shared by the two-tile kernel (head dim 64 / 128) and the one-tile kernel (head dim 256).
+#pragma once
+#include "kernel_params.cuh"
+#include "ptx_sm100.cuh"
+
+namespace fa2 {
+
+constexpr int kBM = 128;            // rows of one query tile
+constexpr int kBN = 128;            // keys per K/V tile
+constexpr int kBlockBytes = kBM * 128;   // one [128 rows][64 elements] block of a swizzled tile
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;   // in log2 units: P stays below 2^8
+
+// Of every 8 column pairs, this many take their exponential from the FMA-pipe polynomial
+// instead of the XU pipe. Measured on B200 (B=8, S=4096, Hq=32, D=128, causal): 0 -> 1.016 ms,
+// 2 -> 1.019 ms, 3 -> 1.048 ms, 4 -> 1.039 ms, 5 -> 1.083 ms, so the default is 0: with packed
+// f32x2 arithmetic the XU pipe is not what limits the kernel.
+#ifndef FA2_FWD_POLY_PER8
+#define FA2_FWD_POLY_PER8 0
+#endif
+constexpr int kPolyPer8 = FA2_FWD_POLY_PER8;
+
+template <bool kBf16>
+__device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermDev& t, int b,
+                                               int h, int qi, int kv0, int Sk) {
+  const long long base = static_cast<long long>(b) * t.sb + static_cast<long long>(h) * t.sh +
+                         static_cast<long long>(qi) * t.sq + kv0;
+  const bool full = (kv0 + kBN <= Sk);
+  if (t.is_f32) {
+    const float* p = static_cast<const float*>(t.ptr) + base;
+    if (t.vec_ok && full) {
+#pragma unroll
+      for (int c4 = 0; c4 < kBN / 4; ++c4) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p) + c4);
+        x[4 * c4 + 0] = fmaf(v.x, kLog2e, x[4 * c4 + 0]);
+        x[4 * c4 + 1] = fmaf(v.y, kLog2e, x[4 * c4 + 1]);
+        x[4 * c4 + 2] = fmaf(v.z, kLog2e, x[4 * c4 + 2]);
+        x[4 * c4 + 3] = fmaf(v.w, kLog2e, x[4 * c4 + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < kBN; ++c)
+        if (kv0 + c < Sk) x[c] = fmaf(__ldg(p + c), kLog2e, x[c]);
+    }
+  } else {
+    const uint16_t* p = static_cast<const uint16_t*>(t.ptr) + base;
+    if (t.vec_ok && full) {
+#pragma unroll
+      for (int c8 = 0; c8 < kBN / 8; ++c8) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + c8);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          x[8 * c8 + 2 * k + 0] =
+              fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(w[k] & 0xffff)), kLog2e,
+                   x[8 * c8 + 2 * k + 0]);
+          x[8 * c8 + 2 * k + 1] = fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(w[k] >> 16)),
+                                       kLog2e, x[8 * c8 + 2 * k + 1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < kBN; ++c)
+        if (kv0 + c < Sk) x[c] = fmaf(to_float16bit<kBf16>(__ldg(p + c)), kLog2e, x[c]);
+    }
+  }
+}
+
+
+// One K/V tile of the online softmax for this thread's row:
+//   S (tensor memory, 128 fp32 columns at tS) -> scores in the log2 domain (+ bias / mask),
+//   causal / padding mask, running maximum with lazy rescaling of O (D columns at tO, only if
+//   `have_o`), P = exp2(.) summed into l, dropout, P written back over S as 16-bit pairs.
+// Ends with the fences after which the caller may signal the MMA warp.
+// `before_o_rescale()` is called (by the whole warp) just before O is touched, so that a kernel
+// whose P.V MMA may still be running can wait for it there.
+template <int D, bool kBf16, bool kFeat, class BeforeRescale>
+__device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j, bool have_o,
+                                                 const FwdKernelParams& p, int b, int h, int qi,
+                                                 int row_lim, float sc, float& m, float& l,
+                                                 BeforeRescale before_o_rescale) {
+  tc_fence_after();
+  float x[kBN];
+  {
+    uint32_t(&xr)[kBN] = reinterpret_cast<uint32_t(&)[kBN]>(x);
+#pragma unroll
+    for (int c = 0; c < kBN / 32; ++c)
+      tmem_ld32(tS + c * 32, reinterpret_cast<uint32_t(&)[32]>(xr[c * 32]));
+    tc_wait_ld();
+  }
+  const int kv0 = j * kBN;
+  if constexpr (kFeat) {
+#pragma unroll
+    for (int c = 0; c < kBN; ++c) x[c] *= p.scale_log2;
+    if (qi < p.Sq) {
+      if (p.bias.ptr) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk);
+      if (p.mask.ptr) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk);
+    }
+  }
+  if (kv0 + kBN - 1 > row_lim) {   // boundary tile for this row: causal edge or key padding
+#pragma unroll
+    for (int c = 0; c < kBN; ++c)
+      if (kv0 + c > row_lim) x[c] = -INFINITY;
+  }
+  float mx0 = fmaxf(x[0], x[1]), mx1 = fmaxf(x[2], x[3]), mx2 = fmaxf(x[4], x[5]),
+        mx3 = fmaxf(x[6], x[7]);
+#pragma unroll
+  for (int c = 8; c < kBN; c += 8) {
+    mx0 = max3(mx0, x[c], x[c + 1]);
+    mx1 = max3(mx1, x[c + 2], x[c + 3]);
+    mx2 = max3(mx2, x[c + 4], x[c + 5]);
+    mx3 = max3(mx3, x[c + 6], x[c + 7]);
+  }
+  const float m_new = max3(m, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+  // Lazy rescaling: keep the stale maximum while the true one is less than 2^8 above it.
+  const bool resc = (m_new - m) * sc > kRescaleThreshold;
+  if (__any_sync(0xffffffffu, resc)) {
+    float alpha = 1.f;
+    if (resc) {
+      alpha = ex2_approx((m - m_new) * sc);
+      m = m_new;
+      l *= alpha;
+    }
+    if (have_o) {
+      before_o_rescale();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tO + c * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+        tmem_st32(tO + c * 32, o);
+      }
+    }
+  }
+  const float m_use = (m == -INFINITY) ? 0.f : m;
+  const float neg_ms = -m_use * sc;
+  float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+  for (int c = 0; c < kBN; c += 4) {
+    fma2(x[c], x[c + 1], x[c], x[c + 1], sc, sc, neg_ms, neg_ms);
+    fma2(x[c + 2], x[c + 3], x[c + 2], x[c + 3], sc, sc, neg_ms, neg_ms);
+    if (((c >> 1) & 7) < kPolyPer8) {
+      ex2_poly2(x[c], x[c + 1]);
+    } else {
+      x[c] = ex2_approx(x[c]);
+      x[c + 1] = ex2_approx(x[c + 1]);
+    }
+    if ((((c >> 1) + 1) & 7) < kPolyPer8) {
+      ex2_poly2(x[c + 2], x[c + 3]);
+    } else {
+      x[c + 2] = ex2_approx(x[c + 2]);
+      x[c + 3] = ex2_approx(x[c + 3]);
+    }
+    add2(l0, l1, l0, l1, x[c], x[c + 1]);
+    add2(l2, l3, l2, l3, x[c + 2], x[c + 3]);
+  }
+  l += (l0 + l1) + (l2 + l3);
+  if constexpr (kFeat) {
+    if (p.drop.enabled) {
+      const uint32_t bh_glob = static_cast<uint32_t>(
+          (p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
+#pragma unroll
+      for (int c = 0; c < kBN; c += 4) {
+        uint32_t rnd[4];
+        philox4x32_10(static_cast<uint32_t>((kv0 + c) >> 2), static_cast<uint32_t>(qi),
+                      bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (rnd[k] < p.drop.threshold) x[c + k] = 0.f;
+      }
+    }
+  }
+  {
+    uint32_t pk[kBN / 2];
+#pragma unroll
+    for (int c = 0; c < kBN / 2; ++c) pk[c] = pack2<kBf16>(x[2 * c], x[2 * c + 1]);
+    tmem_st32(tS, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+    tmem_st32(tS + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
+  }
+  tc_wait_st();
+  tc_fence_before();
+}
+
+// Final scaling of this thread's output row: O / l (and 1/(1-p)) -> 16 bit -> 128-byte-swizzled
+// tile in shared memory at `so_gen` (D/64 blocks of [128][64]); stores the row's log-sum-exp.
+template <int D, bool kBf16, bool kFeat>
+__device__ __forceinline__ void epilogue_row(uint32_t tO, bool has_acc, uint8_t* so_gen, int r,
+                                             const FwdKernelParams& p, int b, int h, int qi, float sc,
+                                             float m, float l) {
+  tc_fence_after();
+  const float inv = (l > 0.f) ? (kFeat ? p.drop.inv_keep : 1.f) / l : 0.f;
+  const float lse = (l > 0.f) ? (m * sc + lg2_approx(l)) * kLn2 : -INFINITY;
+  if (qi < p.Sq)
+    p.lse[static_cast<long long>(b) * p.lse_sb + static_cast<long long>(h) * p.lse_sh + qi] =
+        lse;
+  #pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t o[32];
+    if (has_acc) {
+      tmem_ld32(tO + c * 32, o);
+      tc_wait_ld();
+    } else {
+#pragma unroll
+      for (int k = 0; k < 32; ++k) o[k] = 0u;
+    }
+    // 32 columns = 64 bytes = four 16-byte chunks of this row's 128-byte line
+    uint8_t* line = so_gen + (c >> 1) * kBlockBytes + r * 128;
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      uint4 v;
+      v.x = pack2<kBf16>(__uint_as_float(o[8 * q4 + 0]) * inv, __uint_as_float(o[8 * q4 + 1]) * inv);
+      v.y = pack2<kBf16>(__uint_as_float(o[8 * q4 + 2]) * inv, __uint_as_float(o[8 * q4 + 3]) * inv);
+      v.z = pack2<kBf16>(__uint_as_float(o[8 * q4 + 4]) * inv, __uint_as_float(o[8 * q4 + 5]) * inv);
+      v.w = pack2<kBf16>(__uint_as_float(o[8 * q4 + 6]) * inv, __uint_as_float(o[8 * q4 + 7]) * inv);
+      const int chunk = (c & 1) * 4 + q4;
+      *reinterpret_cast<uint4*>(line + ((chunk ^ (r & 7)) << 4)) = v;
+    }
+  }
+  fence_proxy_async_smem();
+}
+
+}  // namespace fa2

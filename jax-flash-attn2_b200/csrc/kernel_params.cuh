@@ -45,6 +45,9 @@ struct BwdKernelParams {
   ScoreTermDev bias, mask;
   DropoutDev drop;
   int n_kvblk;          // number of 128-row key blocks
+  // fp16 only: bit pattern of max|dO| over the whole call (written by the pre-pass); dS is
+  // scaled by a power of two derived from it so that small cotangents do not underflow in fp16.
+  const unsigned* do_absmax_bits;
   int* status;
 };
 

@@ -88,6 +88,30 @@ def test_ragged_and_unequal_lengths(shape, causal):
     run_case(B, Sq, Sk, Hq, Hkv, 128, torch.bfloat16, causal)
 
 
+@pytest.mark.parametrize("shape,causal,dtype", [
+    ((1, 128, 128, 1, 1), False, torch.float16), ((2, 512, 512, 2, 2), True, torch.bfloat16),
+    ((1, 300, 457, 2, 1), True, torch.float16), ((1, 384, 128, 2, 2), True, torch.float16),
+    ((1, 1, 200, 4, 2), False, torch.bfloat16),
+])
+def test_head_dim_256_forward(shape, causal, dtype):
+    B, Sq, Sk, Hq, Hkv = shape
+    run_case(B, Sq, Sk, Hq, Hkv, 256, dtype, causal, scale=1.0 / 16, backward=False)
+
+
+def test_head_dim_256_forward_with_bias_mask_dropout():
+    run_case(1, 256, 320, 2, 2, 256, torch.bfloat16, False, scale=1.0 / 16, bias_heads=1, mask_kind="pad", p=0.2,
+             backward=False)
+
+
+def test_head_dim_256_backward_is_refused_not_faked():
+    J = _J()
+    from jax_flash_attn2._capi import Fa2Error
+    q, k, v, do = (x.cuda() for x in W.make_qkv(1, 128, 128, 1, 1, 256, torch.float16))
+    out, lse = J.fwd_attention_kernel_call(q, k, v)
+    with pytest.raises(Fa2Error):
+        J.bwd_attention_kernel_call(do, q, k, v, None, None, out, lse, 0.0, False, None, None)
+
+
 @pytest.mark.parametrize("G", [1, 2, 4, 8])
 def test_gqa_groups(G):
     run_case(1, 256, 256, 8, 8 // G, 64, torch.float16, True)
@@ -132,13 +156,27 @@ def test_config1_shape_fp16_mean_loss():
     do = c["do"]
     dq, dk, dv = J.bwd_attention_kernel_call(do.cuda(), q.cuda(), k.cuda(), v.cuda(), None, None, out, lse,
                                              0.0, True, None, None)
-    # As stored (fp16, values of 1e-7..1e-5 on a 6e-8 grid) the gradients cannot meet 1e-2: the
-    # bound below is what fp16 storage of dS and of the results allows; dv, which needs no 16-bit
-    # dS, is much closer.
+    # As stored, the gradients are fp16 values of 1e-7..1e-5 on a 6e-8 grid: against the float32
+    # oracle the storage format alone costs up to 13 %. Against the oracle rounded to fp16 the
+    # kernel still has to meet 1e-2 (the backward rescales dS by a power of two taken from
+    # max|dO|, so nothing underflows before that final rounding).
     s = float(do.flatten()[0])
-    for mine, ref, tol in ((dq, rq, 0.35), (dk, rk, 0.35), (dv, rv, 0.1)):
+    for mine, ref in ((dq, rq), (dk, rk), (dv, rv)):
         ref16 = (ref * s).to(torch.float16)
-        assert rel_l2(mine.cpu(), ref16) <= tol
+        assert rel_l2(mine.cpu(), ref16) <= GRAD_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_cotangent_magnitude_does_not_matter(dtype):
+    """dO scaled by 2^-18 or 2^10 must give gradients scaled by the same factor (to rounding)."""
+    J = _J()
+    q, k, v, do = (x.cuda() for x in W.make_qkv(1, 256, 256, 4, 2, 64, dtype))
+    out, lse = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)
+    base = J.bwd_attention_kernel_call(do, q, k, v, None, None, out, lse, 0.0, True, None, None)
+    for f in (2.0 ** -18, 2.0 ** 10):
+        g = J.bwd_attention_kernel_call((do.float() * f).to(dtype), q, k, v, None, None, out, lse, 0.0, True, None, None)
+        for a, b in zip(g, base):
+            assert rel_l2(a.float() / f, b) <= GRAD_TOL
 
 
 def test_dropout_mask_is_reproducible_and_keep_rate_matches():
