@@ -62,7 +62,8 @@ EncodeTiledFn get_encode_fn() {
 // tensor (64, S, D/64, H, B); one box is (64, rows, D/64, 1, 1) and lands in shared memory as
 // D/64 consecutive [rows][64] blocks with the 128-byte swizzle the MMA descriptors expect.
 int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, int D,
-              const fa2_strides& st, int box_rows, const char* what) {
+              const fa2_strides& st, int box_rows, const char* what, int box_dblocks = 0) {
+  if (box_dblocks == 0) box_dblocks = D / 64;   // default: the full head dim
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(FA2_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0)
@@ -77,8 +78,8 @@ int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, 
   const cuuint64_t sh = static_cast<cuuint64_t>(st.h > 0 ? st.h : D) * 2;
   const cuuint64_t sb = static_cast<cuuint64_t>(st.b > 0 ? st.b : static_cast<int64_t>(D)) * 2;
   const cuuint64_t strides[4] = {static_cast<cuuint64_t>(st.s) * 2, 128, sh, sb};
-  const cuuint32_t box[5] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(D / 64),
-                             1, 1};
+  const cuuint32_t box[5] = {64, static_cast<cuuint32_t>(box_rows),
+                             static_cast<cuuint32_t>(box_dblocks), 1, 1};
   const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   const CUresult r =
       enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
@@ -99,9 +100,9 @@ int check_problem(const fa2_problem& p, bool backward = false) {
                 p.heads_q, p.heads_kv);
   if (p.dtype != FA2_FP16 && p.dtype != FA2_BF16)
     return fail(FA2_ERR_UNSUPPORTED, "only fp16 and bf16 inputs are supported");
-  if (p.head_dim != 64 && p.head_dim != 128 && !(p.head_dim == 256 && !backward))
-    return fail(FA2_ERR_UNSUPPORTED,
-                "head_dim %d is not supported (forward: 64, 128, 256; backward: 64, 128)", p.head_dim);
+  (void)backward;
+  if (p.head_dim != 64 && p.head_dim != 128 && p.head_dim != 256)
+    return fail(FA2_ERR_UNSUPPORTED, "head_dim %d is not supported (64, 128 and 256 are)", p.head_dim);
   if (!(p.dropout_p >= 0.f) || !(p.dropout_p < 1.f))
     return fail(FA2_ERR_INVALID_ARG, "dropout_p must be in [0, 1)");
   if (!std::isfinite(p.softmax_scale))
@@ -262,12 +263,15 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   std::memset(&L, 0, sizeof(L));
   const bool bf16 = p.dtype == FA2_BF16;
   const int D = p.head_dim;
-  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->q_strides, 128, "q")) ||
+  // head dim 256: 64-row query tiles, and dk / dv leave in halves of the head dim
+  const int q_rows = (D == 256) ? 64 : 128;
+  const int dkv_blocks = (D == 256) ? 2 : D / 64;
+  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->q_strides, q_rows, "q")) ||
       (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->k_strides, 128, "k")) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->v_strides, 128, "v")) ||
-      (rc = make_tmap(&L.tmdO, a->d_o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->do_strides, 128, "d_o")) ||
-      (rc = make_tmap(&L.tmdK, a->dk, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dk_strides, 128, "dk")) ||
-      (rc = make_tmap(&L.tmdV, a->dv, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dv_strides, 128, "dv")))
+      (rc = make_tmap(&L.tmdO, a->d_o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->do_strides, q_rows, "d_o")) ||
+      (rc = make_tmap(&L.tmdK, a->dk, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dk_strides, 128, "dk", dkv_blocks)) ||
+      (rc = make_tmap(&L.tmdV, a->dv, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dv_strides, 128, "dv", dkv_blocks)))
     return rc;
   if ((a->o_strides.b % 8) || (a->o_strides.s % 8) || (a->o_strides.h % 8) ||
       (a->dq_strides.b % 8) || (a->dq_strides.s % 8) || (a->dq_strides.h % 8) ||

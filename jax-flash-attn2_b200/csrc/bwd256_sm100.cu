@@ -1,0 +1,588 @@
+// Backward attention kernels for head dim 256 on sm_100a.
+//
+// Same job and reference counterparts as bwd_sm100.cu (_attn_bwd_preprocess, _attn_bwd and the
+// per-group dk / dv reduction of jax_flash_attn2/flash_attention_triton/_backward_triton.py:79-147,
+// 150-945, 1156-1161). At D = 256 the dK and dV accumulators of one 128-key tile would fill
+// tensor memory on their own (2 x 256 columns), and full-width K, V, Q and dO tiles do not fit
+// shared memory next to each other, so the plan changes:
+//   * one CTA owns (batch, kv head, 128-key tile, HALF of the head dim): it accumulates
+//     dK[:, half] and dV[:, half] (128 columns each) and produces dQ[:, half]; the two halves are
+//     two CTAs, each recomputing S and dP over the full head dim (14 instead of 10 GEMM units);
+//   * a step covers 64 query rows: S^T = K Q^T and dP^T = V dO^T are [128 keys x 64 queries];
+//   * dQ is produced transposed, dQ^T[:, half] = K[:, half]^T dS^T ([128 dims x 64 queries]), so
+//     that every MMA keeps M = 128.
+// Tensor memory: S^T 64 | dP^T 64 | dQ^T 64 | free 64 | dK_half 128 | dV_half 128.
+// Shared memory: K 64 KiB, V 64 KiB, Q 32 KiB, dO 32 KiB (single buffers), dS^T 16 KiB,
+// dQ staging 2 x 8 KiB.
+#include "bwd_common.cuh"
+#include "bwd_launch.cuh"
+#include "ptx_sm100.cuh"
+
+namespace fa2 {
+
+namespace {
+
+constexpr int kD = 256;
+constexpr int kBQ = 64;      // query rows per step
+constexpr int kBK = 128;     // keys per CTA
+constexpr int kThreads256 = 512;
+constexpr int kRegsDrain256 = 152;   // 2 * 128 + 152 + 104 = 4 * 128 registers per scheduler lane
+constexpr int kRegsOther256 = 104;
+
+struct BSmem256 {
+  static constexpr int kKVBytes = kBK * kD * 2;     // 64 KiB: 4 blocks of [128][64]
+  static constexpr int kQBytes = kBQ * kD * 2;      // 32 KiB: 4 blocks of [64][64]
+  static constexpr int kKBlock = kBK * 128;         // 16 KiB
+  static constexpr int kQBlock = kBQ * 128;         // 8 KiB
+  static constexpr int kdSBytes = kBK * kBQ * 2;    // 16 KiB: one [128][64] block
+  static constexpr int kChunkBytes = 16 * 128 * 4;  // 16 query columns x 128 dims, fp32
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kKOff + kKVBytes;
+  static constexpr int kQOff = kVOff + kKVBytes;
+  static constexpr int kdOOff = kQOff + kQBytes;
+  static constexpr int kdSOff = kdOOff + kQBytes;
+  static constexpr int kStageOff = kdSOff + kdSBytes;
+  static constexpr int kStatsOff = kStageOff + 2 * kChunkBytes;   // -lse*log2e [64], delta [64]
+  static constexpr int kBarOff = kStatsOff + 512;
+  static constexpr int kNumBars = 12;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kDynamicBytes = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
+  static_assert(kTotal + 1024 <= kMaxDynSmem, "shared memory budget exceeded");
+};
+
+}  // namespace
+
+// dq accumulator layout at D = 256: [B, Hq, ceil(Sq/64), 2 halves, 16 (query/4), 128 dims, 4 queries].
+template <bool kBf16>
+__global__ void __launch_bounds__(256)
+bwd256_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long long sb,
+                  long long ss, long long sh, int Sq, int Hq, int nQ64, float scale_in,
+                  const unsigned* __restrict__ do_absmax_bits) {
+  const float scale = scale_in / (kBf16 ? 1.f : do_scale_from_bits(do_absmax_bits));
+  const int i = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / Hq, h = bh - b * Hq;
+  const int tid = threadIdx.x;
+  const int dpair = tid & 63;                 // dims 2*dpair, 2*dpair + 1 of a half
+  const float4* src = reinterpret_cast<const float4*>(dq_acc) +
+                      (static_cast<long long>(bh) * nQ64 + i) * (kBQ * kD / 4);
+  // 32 (half, query/4) slabs of [128 dims][4 queries]; four slabs per pass
+#pragma unroll 1
+  for (int pass = 0; pass < 8; ++pass) {
+    const int slab = pass * 4 + (tid >> 6);
+    const int half = slab >> 4, c4 = slab & 15;
+    const float4 x = src[slab * 128 + 2 * dpair];
+    const float4 y = src[slab * 128 + 2 * dpair + 1];
+    const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int row = i * kBQ + c4 * 4 + e;
+      if (row < Sq)
+        reinterpret_cast<uint32_t*>(dq + b * sb + row * ss + h * sh)[half * 64 + dpair] =
+            pack2<kBf16>(xs[e] * scale, ys[e] * scale);
+    }
+  }
+}
+
+template <bool kBf16, bool kCausal, bool kFeat>
+__global__ void __launch_bounds__(kThreads256, 1)
+bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
+                   const float* __restrict__ stats, const BwdKernelParams p) {
+  using L = BSmem256;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t pad = smem_base - smem_u32(smem_raw);
+  if (pad + L::kTotal > static_cast<uint32_t>(L::kDynamicBytes)) {
+    if (threadIdx.x == 0) atomicOr(p.status, 64);
+    return;
+  }
+  uint8_t* smem_gen = smem_raw + pad;
+  const uint32_t sK = smem_base + L::kKOff, sV = smem_base + L::kVOff;
+  const uint32_t sQ = smem_base + L::kQOff, sdO = smem_base + L::kdOOff;
+  const uint32_t sdS = smem_base + L::kdSOff, sStats = smem_base + L::kStatsOff;
+  const uint32_t bars = smem_base + L::kBarOff;
+  const uint32_t bar_kv_full = bars, bar_q_full = bars + 8, bar_q_empty = bars + 16;
+  const uint32_t bar_do_full = bars + 24, bar_do_empty = bars + 32;
+  const uint32_t bar_s_full = bars + 40, bar_p_full = bars + 48;
+  const uint32_t bar_dp_full = bars + 56, bar_ds_full = bars + 64;
+  const uint32_t bar_dq_full = bars + 72, bar_dq_drained = bars + 80, bar_dkv_full = bars + 88;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ---- work item: (batch, kv head, key tile, half of the head dim) ---------------------------
+  const int half = blockIdx.x & 1;
+  const int rest = blockIdx.x >> 1;
+  const int n = rest % p.n_kvblk;
+  const int bhk = rest / p.n_kvblk;
+  const int b = bhk / p.Hkv;
+  const int hk = bhk - b * p.Hkv;
+  const int nQ64 = (p.Sq + kBQ - 1) / kBQ;
+  const int nQ128 = (p.Sq + 127) / 128;
+  int i_start = 0;
+  if (kCausal) {
+    const int first_row = n * kBK - p.causal_off;   // first query row that sees key n*128
+    i_start = first_row > 0 ? first_row / kBQ : 0;
+    if (i_start > nQ64) i_start = nQ64;
+  }
+  const int nI = nQ64 - i_start;
+  const int T = nI * p.G;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_kv_full, 1);
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_empty, 1);
+    mbar_init(bar_do_full, 1);
+    mbar_init(bar_do_empty, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_p_full, 256);
+    mbar_init(bar_dp_full, 1);
+    mbar_init(bar_ds_full, 256);
+    mbar_init(bar_dq_full, 1);
+    mbar_init(bar_dq_drained, 128);
+    mbar_init(bar_dkv_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 13 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmdO);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColS = 0, kColdP = 64, kColdQ = 128, kColdK = 256, kColdV = 384;
+
+  auto step_coords = [&](int it, int& h, int& i) {
+    const int g = it / nI;
+    i = i_start + (it - g * nI);
+    h = hk * p.G + g;
+  };
+
+  if (warp >= 12) setmaxnreg_dec<kRegsOther256>();
+  if (warp >= 14) {
+    // idle
+  } else if (warp == 13) {
+    // =========================== TMA producer ================================================
+    if (lane == 0 && T > 0) {
+      mbar_arrive_expect_tx(bar_kv_full, 2 * L::kKVBytes);
+      tma_load_5d(sK, &tmK, bar_kv_full, 0, n * kBK, 0, hk, b);
+      tma_load_5d(sV, &tmV, bar_kv_full, 0, n * kBK, 0, hk, b);
+      bool ok = true;
+      for (int it = 0; it < T && ok; ++it) {
+        int h, i;
+        step_coords(it, h, i);
+        ok = mbar_wait(bar_q_empty, (it & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_q_full, L::kQBytes + 512);
+        tma_load_5d(sQ, &tmQ, bar_q_full, 0, i * kBQ, 0, h, b);
+        const float* st =
+            stats + ((static_cast<long long>(b) * p.Hq + h) * nQ128 + (i >> 1)) * 256 + (i & 1) * 64;
+        bulk_load_1d(sStats, st, 256, bar_q_full);
+        bulk_load_1d(sStats + 256, st + 128, 256, bar_q_full);
+        ok = mbar_wait(bar_do_empty, (it & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        mbar_arrive_expect_tx(bar_do_full, L::kQBytes);
+        tma_load_5d(sdO, &tmdO, bar_do_full, 0, i * kBQ, 0, h, b);
+      }
+      if (!ok) atomicOr(p.status, 8);
+    }
+    __syncwarp();
+  } else if (warp == 12) {
+    // =========================== MMA issuer ==================================================
+    if (lane == 0 && T > 0) {
+      constexpr uint32_t idesc_s = make_idesc(kBf16, 128, kBQ, false, false);
+      constexpr uint32_t idesc_dkv = make_idesc(kBf16, 128, 128, false, true);
+      constexpr uint32_t idesc_dq = make_idesc(kBf16, 128, kBQ, true, true);
+      const uint64_t dK_k = make_sdesc(sK, 16, 1024), dV_k = make_sdesc(sV, 16, 1024);
+      const uint64_t dQ_k = make_sdesc(sQ, 16, 1024), ddO_k = make_sdesc(sdO, 16, 1024);
+      // halves of Q / dO as MN-major B operands: two 64-dim blocks, L::kQBlock apart
+      const uint64_t dQ_mn = make_sdesc(sQ + 2 * half * L::kQBlock, L::kQBlock, 1024);
+      const uint64_t ddO_mn = make_sdesc(sdO + 2 * half * L::kQBlock, L::kQBlock, 1024);
+      // half of K as MN-major A operand (M = head dim): two 64-dim blocks, L::kKBlock apart
+      const uint64_t dKh_mn = make_sdesc(sK + 2 * half * L::kKBlock, L::kKBlock, 1024);
+      const uint64_t ddS_k = make_sdesc(sdS, 16, 1024), ddS_mn = make_sdesc(sdS, 16, 1024);
+      bool ok = true;
+
+      // D[key, query] = A[key, d] * B[query, d]^T over the full head dim
+      auto issue_kd = [&](uint32_t d_col, uint64_t a_desc, uint64_t b_desc) {
+#pragma unroll
+        for (int k = 0; k < kD / 16; ++k) {
+          const uint32_t offa = (k >> 2) * L::kKBlock + (k & 3) * 32;
+          const uint32_t offb = (k >> 2) * L::kQBlock + (k & 3) * 32;
+          mma_ss(tmem_base + d_col, sdesc_advance(a_desc, offa), sdesc_advance(b_desc, offb),
+                 idesc_s, k > 0 ? 1u : 0u);
+        }
+      };
+      auto issue_dv = [&](bool first) {
+#pragma unroll
+        for (int k = 0; k < kBQ / 16; ++k) {
+          // P^T for queries [16k, 16k+16): 8 packed columns; queries [0,32) were written by
+          // warpgroup 0 at column 0, queries [32,64) by warpgroup 1 at column 32
+          const uint32_t a_col = kColS + (k < 2 ? 8 * k : 32 + 8 * (k - 2));
+          mma_ts(tmem_base + kColdV, tmem_base + a_col, sdesc_advance(ddO_mn, k * 2048), idesc_dkv,
+                 (first && k == 0) ? 0u : 1u);
+        }
+      };
+      auto issue_dk = [&](bool first) {
+#pragma unroll
+        for (int k = 0; k < kBQ / 16; ++k)
+          mma_ss(tmem_base + kColdK, sdesc_advance(ddS_k, k * 32), sdesc_advance(dQ_mn, k * 2048),
+                 idesc_dkv, (first && k == 0) ? 0u : 1u);
+      };
+      auto issue_dq = [&]() {
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k)
+          mma_ss(tmem_base + kColdQ, sdesc_advance(dKh_mn, k * 2048), sdesc_advance(ddS_mn, k * 2048),
+                 idesc_dq, k > 0 ? 1u : 0u);
+      };
+
+      ok = mbar_wait(bar_kv_full, 0, abort_flag);
+      if (ok) ok = mbar_wait(bar_q_full, 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_kd(kColS, dK_k, dQ_k);
+        mma_commit(bar_s_full);
+        ok = mbar_wait(bar_do_full, 0, abort_flag);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_kd(kColdP, dV_k, ddO_k);
+        mma_commit(bar_dp_full);
+      }
+      for (int it = 0; it < T && ok; ++it) {
+        const uint32_t par = it & 1;
+        ok = mbar_wait(bar_p_full, par, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dv(it == 0);
+        mma_commit(bar_do_empty);
+        ok = mbar_wait(bar_ds_full, par, abort_flag);
+        if (ok && it > 0) ok = mbar_wait(bar_dq_drained, (it - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_dq();
+        mma_commit(bar_dq_full);
+        issue_dk(it == 0);
+        mma_commit(bar_q_empty);
+        if (it + 1 < T) {
+          ok = mbar_wait(bar_q_full, (it + 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_kd(kColS, dK_k, dQ_k);
+          mma_commit(bar_s_full);
+          ok = mbar_wait(bar_do_full, (it + 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_kd(kColdP, dV_k, ddO_k);
+          mma_commit(bar_dp_full);
+        }
+      }
+      if (ok) mma_commit(bar_dkv_full);
+      if (!ok) atomicOr(p.status, 16);
+    }
+    __syncwarp();
+  } else if (warp >= 8) {
+    // =========================== dQ^T drain ==================================================
+    setmaxnreg_inc<kRegsDrain256>();
+    const int r = tid - 256;   // head-dim index inside the half == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tdQ = tmem_base + lane_base + kColdQ;
+    bool ok = true;
+    for (int it = 0; it < T; ++it) {
+      int h, i;
+      step_coords(it, h, i);
+      ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t v[kBQ];
+      tmem_ld32(tdQ, reinterpret_cast<uint32_t(&)[32]>(v[0]));
+      tmem_ld32(tdQ + 32, reinterpret_cast<uint32_t(&)[32]>(v[32]));
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_dq_drained);
+      float* dst_tile = p.dq_acc +
+                        (((static_cast<long long>(b) * p.Hq + h) * nQ64 + i) * 2 + half) * (kBQ * 128);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int buf = c & 1;
+        if (r == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        named_bar_sync(3, 128);
+        uint8_t* stage = smem_gen + L::kStageOff + buf * L::kChunkBytes;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int cc = c * 4 + c4;
+          *reinterpret_cast<uint4*>(stage + (c4 * 128 + r) * 16) =
+              make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(3, 128);
+        if (r == 0) {
+          bulk_reduce_add_f32(dst_tile + c * (16 * 128), smem_base + L::kStageOff + buf * L::kChunkBytes,
+                              L::kChunkBytes);
+          tma_store_commit();
+        }
+      }
+    }
+    if (r == 0) tma_store_wait_read0();
+    if (!ok && r == 0) atomicOr(p.status, 32);
+  } else {
+    // =========================== P / dS warps + dK, dV epilogue ==============================
+    const int w = warp >> 2;            // 0: queries [0,32) of each step, dK; 1: [32,64), dV
+    const int r = tid & 127;            // key row inside the tile == TMEM lane
+    const int kv = n * kBK + r;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + kColS + 32 * w;
+    const uint32_t tdP = tmem_base + lane_base + kColdP + 32 * w;
+    const float4* nlse4 = reinterpret_cast<const float4*>(smem_gen + L::kStatsOff) + 8 * w;
+    const float4* delta4 = nlse4 + 16;
+    uint8_t* ds_row = smem_gen + L::kdSOff + r * 128;
+    const float do_scale = kBf16 ? 1.f : do_scale_from_bits(p.do_absmax_bits);
+    bool ok = true;
+
+    for (int it = 0; it < T; ++it) {
+      int h, i;
+      step_coords(it, h, i);
+      const int q_first = i * kBQ + 32 * w;
+      ok = mbar_wait(bar_q_full, it & 1, abort_flag);
+      if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const bool diag = kCausal && (n * kBK + kBK - 1 > i * kBQ + p.causal_off);
+      const int q_lim = kv - p.causal_off;     // masked iff query index < q_lim
+
+      uint32_t pk[16];
+      uint32_t keep = 0xffffffffu;
+      {
+        uint32_t s[32];
+        tmem_ld32(tS, s);
+        tc_wait_ld();
+        if constexpr (kFeat) {
+          if (p.drop.enabled) {
+            const uint32_t bh_glob =
+                static_cast<uint32_t>((p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
+            uint32_t bits = 0u;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              uint32_t rnd[4];
+              philox4x32_10(static_cast<uint32_t>(kv >> 2), static_cast<uint32_t>(q_first + c),
+                            bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
+              const uint32_t sel = (kv & 3) == 0 ? rnd[0] : (kv & 3) == 1 ? rnd[1]
+                                   : (kv & 3) == 2 ? rnd[2] : rnd[3];
+              if (sel >= p.drop.threshold) bits |= (1u << c);
+            }
+            keep = bits;
+          }
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 nl = nlse4[c4];
+          const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
+#pragma unroll
+          for (int k2 = 0; k2 < 2; ++k2) {
+            const int c = 4 * c4 + 2 * k2;
+            float x0 = __uint_as_float(s[c]), x1 = __uint_as_float(s[c + 1]);
+            if constexpr (kFeat) {
+              x0 *= p.scale_log2;
+              x1 *= p.scale_log2;
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int qi = q_first + c + e;
+                float add = 0.f;
+                if (qi < p.Sq && kv < p.Sk) {
+                  if (p.bias.ptr)
+                    add += load_term<kBf16>(p.bias, b * p.bias.sb + h * p.bias.sh +
+                                                        static_cast<long long>(qi) * p.bias.sq + kv);
+                  if (p.mask.ptr)
+                    add += load_term<kBf16>(p.mask, b * p.mask.sb + h * p.mask.sh +
+                                                        static_cast<long long>(qi) * p.mask.sq + kv);
+                }
+                (e == 0 ? x0 : x1) = fmaf(add, kLog2e, e == 0 ? x0 : x1);
+              }
+              x0 += nlv[2 * k2];
+              x1 += nlv[2 * k2 + 1];
+            } else {
+              fma2(x0, x1, x0, x1, p.scale_log2, p.scale_log2, nlv[2 * k2], nlv[2 * k2 + 1]);
+            }
+            float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            if (diag) {
+              if (q_first + c < q_lim) p0 = 0.f;
+              if (q_first + c + 1 < q_lim) p1 = 0.f;
+            }
+            pk[c >> 1] = pack2<kBf16>(p0, p1);
+          }
+        }
+      }
+      if constexpr (kFeat) {
+        if (p.drop.enabled) {
+          uint32_t pd[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            float a0 = ((keep >> (2 * c)) & 1u) ? unpack_lo<kBf16>(pk[c]) * p.drop.inv_keep : 0.f;
+            float a1 = ((keep >> (2 * c + 1)) & 1u) ? unpack_hi<kBf16>(pk[c]) * p.drop.inv_keep : 0.f;
+            pd[c] = pack2<kBf16>(a0, a1);
+          }
+          tmem_st16(tS, pd);
+        } else {
+          tmem_st16(tS, pk);
+        }
+      } else {
+        tmem_st16(tS, pk);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p_full);
+
+      ok = mbar_wait(bar_dp_full, it & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      {
+        uint32_t dp[32];
+        tmem_ld32(tdP, dp);
+        tc_wait_ld();
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 dl = delta4[c4];
+          const float dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+          for (int k2 = 0; k2 < 2; ++k2) {
+            const int c = 4 * c4 + 2 * k2;
+            float d0 = __uint_as_float(dp[c]), d1 = __uint_as_float(dp[c + 1]);
+            if constexpr (kFeat) {
+              d0 = ((keep >> c) & 1u) ? d0 * p.drop.inv_keep : 0.f;
+              d1 = ((keep >> (c + 1)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
+            }
+            float t0, t1;
+            add2(t0, t1, d0, d1, -dlv[2 * k2], -dlv[2 * k2 + 1]);
+            if constexpr (!kBf16) fma2(t0, t1, t0, t1, do_scale, do_scale, 0.f, 0.f);
+            const float p0 = unpack_lo<kBf16>(pk[c >> 1]), p1 = unpack_hi<kBf16>(pk[c >> 1]);
+            dp[c >> 1] = pack2<kBf16>(p0 * t0, p1 * t1);
+          }
+        }
+        // dS^T row r, queries [32w, 32w + 32): chunks 4w .. 4w+3 of the row's 128-byte line
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = 4 * w + q4;
+          *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(dp[4 * q4], dp[4 * q4 + 1], dp[4 * q4 + 2], dp[4 * q4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar_ds_full);
+    }
+
+    // ---- epilogue: warpgroup 0 writes dK[:, half] (scaled), warpgroup 1 writes dV[:, half] ----
+    if (ok && T > 0) ok = mbar_wait(bar_dkv_full, 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t tAcc = tmem_base + lane_base + (w == 0 ? kColdK : kColdV);
+      const float f = (w == 0) ? p.scale / do_scale : 1.f;
+      uint8_t* stage = smem_gen + (w == 0 ? L::kQOff : L::kdOOff);   // 32 KiB each, free by now
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t a[32];
+        if (T > 0) {
+          tmem_ld32(tAcc + c * 32, a);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) a[k] = 0u;
+        }
+        uint8_t* line = stage + (c >> 1) * L::kKBlock + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 v;
+          v.x = pack2<kBf16>(__uint_as_float(a[8 * q4 + 0]) * f, __uint_as_float(a[8 * q4 + 1]) * f);
+          v.y = pack2<kBf16>(__uint_as_float(a[8 * q4 + 2]) * f, __uint_as_float(a[8 * q4 + 3]) * f);
+          v.z = pack2<kBf16>(__uint_as_float(a[8 * q4 + 4]) * f, __uint_as_float(a[8 * q4 + 5]) * f);
+          v.w = pack2<kBf16>(__uint_as_float(a[8 * q4 + 6]) * f, __uint_as_float(a[8 * q4 + 7]) * f);
+          const int chunk = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(line + ((chunk ^ (r & 7)) << 4)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+    }
+    named_bar_sync(1 + w, 128);
+    if (ok && r == 0 && !*abort_flag) {
+      tma_store_5d(w == 0 ? &tmdK : &tmdV, w == 0 ? sQ : sdO, 0, n * kBK, 2 * half, hk, b);
+      tma_store_commit();
+      tma_store_wait_read0();
+    }
+    if (!ok && r == 0) atomicOr(p.status, 128);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <bool kBf16, bool kCausal, bool kFeat>
+static cudaError_t launch256_main(const BwdLaunch& a, cudaStream_t stream) {
+  using L = BSmem256;
+  auto kern = bwd256_main_kernel<kBf16, kCausal, kFeat>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  if (e != cudaSuccess) return e;
+  const long long nblocks = 2LL * a.kp.n_kvblk * a.kp.B * a.kp.Hkv;
+  kern<<<static_cast<unsigned>(nblocks), kThreads256, L::kDynamicBytes, stream>>>(
+      a.tmQ, a.tmK, a.tmV, a.tmdO, a.tmdK, a.tmdV, a.delta, a.kp);
+  return cudaGetLastError();
+}
+
+template <bool kBf16>
+static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
+  const BwdKernelParams& kp = a.kp;
+  const int nQ128 = (kp.Sq + 127) / 128, nQ64 = (kp.Sq + kBQ - 1) / kBQ;
+  auto mark = [&](int i) {
+    if (a.stage_events[i]) cudaEventRecord(a.stage_events[i], stream);
+  };
+  unsigned* absmax = const_cast<unsigned*>(kp.do_absmax_bits);
+  if (!kBf16) {
+    const cudaError_t em = cudaMemsetAsync(absmax, 0, sizeof(unsigned), stream);
+    if (em != cudaSuccess) return em;
+  }
+  mark(0);
+  bwd_pre_kernel<kD, kBf16><<<dim3(nQ128, kp.B * kp.Hq), 128, 0, stream>>>(
+      static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
+      a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
+      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  mark(1);
+  const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);
+  switch (key) {
+    case 0: e = launch256_main<kBf16, false, false>(a, stream); break;
+    case 1: e = launch256_main<kBf16, false, true>(a, stream); break;
+    case 2: e = launch256_main<kBf16, true, false>(a, stream); break;
+    default: e = launch256_main<kBf16, true, true>(a, stream); break;
+  }
+  if (e != cudaSuccess) return e;
+  mark(2);
+  bwd256_dq_convert<kBf16><<<dim3(nQ64, kp.B * kp.Hq), 256, 0, stream>>>(
+      kp.dq_acc, static_cast<uint16_t*>(a.dq), a.dq_strides[0], a.dq_strides[1], a.dq_strides[2],
+      kp.Sq, kp.Hq, nQ64, kp.scale, kBf16 ? nullptr : kp.do_absmax_bits);
+  mark(3);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd256(const BwdLaunch& a, cudaStream_t stream) {
+  return a.bf16 ? launch256_all<true>(a, stream) : launch256_all<false>(a, stream);
+}
+
+}  // namespace fa2

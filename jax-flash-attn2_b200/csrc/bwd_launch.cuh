@@ -25,4 +25,7 @@ struct BwdLaunch {
 // Runs the three kernels of the backward pass on `stream`.
 cudaError_t launch_bwd(const BwdLaunch& a, cudaStream_t stream);
 
+// Head dim 256 variant (64-query steps, one half of the head dim per CTA); called by launch_bwd.
+cudaError_t launch_bwd256(const BwdLaunch& a, cudaStream_t stream);
+
 }  // namespace fa2

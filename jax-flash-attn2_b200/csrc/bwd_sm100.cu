@@ -18,6 +18,7 @@
 //                         dK / dV accumulate in tensor memory over the whole group, so there is
 //                         no per-query-head temporary and no second reduction.
 //   3. bwd_dq_convert   : fp32 dq accumulator (tiled layout) * scale -> dq in the input dtype.
+#include "bwd_common.cuh"
 #include "bwd_launch.cuh"
 #include "ptx_sm100.cuh"
 
@@ -25,15 +26,12 @@ namespace fa2 {
 
 namespace {
 
-constexpr int kBM = 128;   // query rows per step
 constexpr int kBN = 128;   // keys per CTA
 constexpr int kThreads = 512;
 // Registers per thread after setmaxnreg: each scheduler holds 2 P/dS warps, 1 drain warp and 1
 // warp of the last warpgroup; 2 * 128 + 152 + 104 = 4 * 128 (the launch allocation).
 constexpr int kRegsDrain = 152;
 constexpr int kRegsOther = 104;
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kMaxDynSmem = 232448;
 
 template <int D>
 struct BwdSmem {
@@ -56,21 +54,6 @@ struct BwdSmem {
   static_assert(kTotal <= kMaxDynSmem, "shared memory budget exceeded");
 };
 
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
-                                             uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
-      : "memory");
-}
-
-// dst[0 .. bytes) += src[0 .. bytes) as float32, done by the TMA unit (asynchronous).
-__device__ __forceinline__ void bulk_reduce_add_f32(float* dst, uint32_t src_smem, uint32_t bytes) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst),
-               "r"(src_smem), "r"(bytes)
-               : "memory");
-}
-
 #ifdef FA2_TRACE
 // Development aid (not compiled by default): per-role time stamps of CTA 0.
 __device__ long long g_trace[48 * 4096];
@@ -79,97 +62,7 @@ __device__ long long g_trace[48 * 4096];
 #define FA2_T(role, idx) do { } while (0)
 #endif
 
-// Power of two that brings max|dO| to [1, 2): fp16 inputs only. With a loss like mean(out) the
-// cotangent is ~1e-6 and dS = P (dP - delta) would sit in fp16's subnormal range; scaling dS by
-// this factor (and dK, dQ back by its inverse) keeps the 16-bit operand of the dK / dQ MMAs in
-// the normal range. Exact: powers of two do not round.
-__device__ __forceinline__ float do_scale_from_bits(const unsigned* bits) {
-  if (bits == nullptr) return 1.f;
-  const float mx = __uint_as_float(__ldg(bits));
-  if (!(mx > 0.f) || !(mx < INFINITY)) return 1.f;
-  const int e = static_cast<int>(floorf(log2f(mx)));
-  return exp2f(static_cast<float>(-max(-60, min(60, e))));
-}
-
-template <bool kBf16>
-__device__ __forceinline__ float load_term(const ScoreTermDev& t, long long idx) {
-  if (t.is_f32) return __ldg(static_cast<const float*>(t.ptr) + idx);
-  return to_float16bit<kBf16>(__ldg(static_cast<const uint16_t*>(t.ptr) + idx));
-}
-
 }  // namespace
-
-// ---------------------------------------------------------------------------------------------
-// 1. pre-pass
-// ---------------------------------------------------------------------------------------------
-// stats layout: [B, Hq, nQ, 2, 128] float: (-lse * log2e | -inf for rows that take no gradient,
-// delta). dq_acc layout: [B, Hq, nQ, D/4, 128, 4] float.
-template <int D, bool kBf16>
-__global__ void __launch_bounds__(128)
-bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
-               long long o_sb, long long o_ss, long long o_sh, long long do_sb, long long do_ss,
-               long long do_sh, const float* __restrict__ lse, long long lse_sb, long long lse_sh,
-               float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ,
-               unsigned* __restrict__ do_absmax_bits) {
-  const int i = blockIdx.x;
-  const int bh = blockIdx.y;
-  const int b = bh / Hq, h = bh - b * Hq;
-  const int tid = threadIdx.x;
-  constexpr int kLanesPerRow = D / 8;            // 16-byte loads
-  constexpr int kRowsPerPass = 128 / kLanesPerRow;
-  const int sub = tid % kLanesPerRow;
-  const long long tile = (static_cast<long long>(bh) * nQ + i);
-  float* st = stats + tile * 256;
-  float amax = 0.f;
-  for (int r0 = 0; r0 < kBM; r0 += kRowsPerPass) {
-    const int r = r0 + tid / kLanesPerRow;
-    const int row = i * kBM + r;
-    float acc = 0.f;
-    if (row < Sq) {
-      const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + b * o_sb + row * o_ss + h * o_sh) + sub);
-      const uint4 g = __ldg(reinterpret_cast<const uint4*>(d_o + b * do_sb + row * do_ss + h * do_sh) + sub);
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        acc = fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(aw[k] & 0xffff)),
-                   to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] & 0xffff)), acc);
-        acc = fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(aw[k] >> 16)),
-                   to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] >> 16)), acc);
-        if constexpr (!kBf16) {
-          const float g0 = fabsf(to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] & 0xffff)));
-          const float g1 = fabsf(to_float16bit<kBf16>(static_cast<uint16_t>(gw[k] >> 16)));
-          if (g0 < INFINITY) amax = fmaxf(amax, g0);
-          if (g1 < INFINITY) amax = fmaxf(amax, g1);
-        }
-      }
-    }
-#pragma unroll
-    for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
-      acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (sub == 0) {
-      float l2 = -INFINITY;      // -lse*log2(e); -inf makes every weight of the row exp2(-inf) = 0
-      if (row < Sq) {
-        const float l = lse[b * lse_sb + h * lse_sh + row];
-        if (l > -INFINITY && l < INFINITY) l2 = -l * kLog2e;
-      }
-      st[r] = l2;
-      st[128 + r] = (row < Sq) ? acc : 0.f;
-    }
-  }
-  float4* acc4 = reinterpret_cast<float4*>(dq_acc + tile * (kBM * D));
-  for (int k = tid; k < kBM * D / 4; k += 128) acc4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-  if constexpr (!kBf16) {
-    // block maximum of |dO| -> one atomic per block (non-negative floats order like their bits)
-    __shared__ float warp_max[4];
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    if ((tid & 31) == 0) warp_max[tid >> 5] = amax;
-    __syncthreads();
-    if (tid == 0 && do_absmax_bits != nullptr)
-      atomicMax(do_absmax_bits, __float_as_uint(fmaxf(fmaxf(warp_max[0], warp_max[1]),
-                                                      fmaxf(warp_max[2], warp_max[3]))));
-  }
-}
 
 // ---------------------------------------------------------------------------------------------
 // 3. dq conversion
@@ -786,6 +679,7 @@ extern "C" int fa2_trace_read_bwd(long long* host, int n) {
 cudaError_t launch_bwd(const BwdLaunch& a, cudaStream_t stream) {
   if (a.head_dim == 64) return a.bf16 ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);
   if (a.head_dim == 128) return a.bf16 ? launch_all<128, true>(a, stream) : launch_all<128, false>(a, stream);
+  if (a.head_dim == 256) return launch_bwd256(a, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -122,3 +122,24 @@ def test_full_size_config2_properties():
     gd = dense.attention_grads(dos, qs, ks, vs, causal=True)
     for mine, ref in zip(g, gd):
         assert rel_l2(mine.cpu(), ref) <= 1e-2
+
+
+def test_config5_slice_properties_head_dim_256():
+    """Config 5 shape family (fp16, D=256, causal) at reduced batch/heads but full sequence length
+    for one head: causal prefix property and dense-oracle check of a slice."""
+    import jax_flash_attn2 as J
+    q, k, v, do = W.make_qkv(1, 8192, 8192, 2, 2, 256, torch.float16, 1.0 / 16)
+    qc, kc, vc, doc = (x.cuda() for x in (q, k, v, do))
+    out, lse = J.fwd_attention_kernel_call(qc, kc, vc, None, None, None, 0.0, True, None)
+    o_pre, l_pre = J.fwd_attention_kernel_call(qc[:, :768], kc[:, :768], vc[:, :768], None, None, None, 0.0, True, None)
+    assert torch.equal(o_pre, out[:, :768]) and torch.equal(l_pre, lse[:, :, :768])
+    od, ld = dense.attention(q[:, :768, :1], k[:, :768, :1], v[:, :768, :1], causal=True)
+    assert (out[:, :768, :1].cpu().double() - od).abs().max().item() <= 5e-3
+    dq, dk, dv = J.bwd_attention_kernel_call(doc, qc, kc, vc, None, None, out, lse, 0.0, True, None, None)
+    for g in (dq, dk, dv):
+        assert torch.isfinite(g.float()).all()
+    g = J.bwd_attention_kernel_call(doc[:, :768], qc[:, :768], kc[:, :768], vc[:, :768], None, None, o_pre, l_pre,
+                                    0.0, True, None, None)
+    gd = dense.attention_grads(do[:, :768], q[:, :768], k[:, :768], v[:, :768], causal=True)
+    for mine, ref in zip(g, gd):
+        assert rel_l2(mine.cpu(), ref) <= 1e-2
