@@ -42,7 +42,12 @@ WORKLOADS = {
     "llama3_8b_causal_bf16_b2": (2, 4096, 4096, 32, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
     "readme_gqa_causal_fp16": (2, 512, 512, 16, 4, 64, torch.float16, True, 1.0),
     "long_context_causal_bf16": (1, 32768, 32768, 64, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
+    "mha_bias_mask_dropout_bf16": (4, 2048, 2048, 16, 16, 64, torch.bfloat16, False, 1.0),
+    "head_dim_256_causal_fp16": (4, 8192, 8192, 8, 8, 256, torch.float16, True, 1.0 / 16),
 }
+# additive bias 1/(1+|i-j|), key-padding mask (valid length U[S/2, S] per batch element, finfo.min
+# beyond it), dropout 0.1 with seed 42
+WORKLOAD_EXTRAS = {"mha_bias_mask_dropout_bf16": {"bias": True, "mask": True, "dropout": 0.1, "seed": 42}}
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward main kernel at the
 # default workload, from the ncu capture summarised under profiles/ (None until captured).
 BWD_MAIN_DRAM_TRAFFIC_BYTES = None
@@ -230,9 +235,23 @@ def main():
     q, k, v, do = (x.cuda(non_blocking=True) for x in (hq, hk, hv, hdo))
     torch.cuda.synchronize()
 
-    fwd = lambda: J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, causal, None)
+    extras = WORKLOAD_EXTRAS.get(args.workload, {})
+    bias = mask = None
+    p_drop, seed = float(extras.get("dropout", 0.0)), extras.get("seed")
+    if extras.get("bias"):
+        idx = torch.arange(Sq)
+        bias = (1.0 / (1.0 + (idx[:, None] - idx[None, :Sk]).abs().float())).to(dtype)
+        bias = bias[None, None].expand(B, 1, Sq, Sk).contiguous().cuda()
+    if extras.get("mask"):
+        lengths = torch.randint(Sk // 2, Sk + 1, (B,), generator=torch.Generator().manual_seed(4))
+        mask = torch.zeros(B, 1, Sq, Sk, dtype=dtype)
+        for bi in range(B):
+            mask[bi, :, :, int(lengths[bi]):] = torch.finfo(dtype).min
+        mask = mask.cuda()
+
+    fwd = lambda: J.fwd_attention_kernel_call(q, k, v, mask, bias, None, p_drop, causal, seed)
     def bwd(o, lse):
-        return J.bwd_attention_kernel_call(do, q, k, v, None, None, o, lse, 0.0, causal, None, None)
+        return J.bwd_attention_kernel_call(do, q, k, v, bias, mask, o, lse, p_drop, causal, None, seed)
 
     def barrier():
         if dist is not None:
@@ -352,7 +371,8 @@ def main():
             "shape_per_gpu": f"B={B} Sq={Sq} Sk={Sk} Hq={Hq} Hkv={Hkv} D={D} causal={causal}",
             "global_batch": B * world,
             "parallelism": f"{world} x independent (batch, kv-head) shards, no collective",
-            "l2": "inputs (640 MiB per step) exceed the 126 MB L2; no explicit flush",
+            "extras": extras,
+            "l2": f"inputs ({(h2d) // (1 << 20)} MiB per step) vs the 126 MB L2; no explicit flush",
             "flops": "fwd 4*B*Hq*Sq*Sk*D (x0.5 causal), bwd 2.5x fwd",
         },
         "per_gpu": {

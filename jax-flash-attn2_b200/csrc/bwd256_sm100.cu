@@ -374,18 +374,16 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           if (p.drop.enabled) {
             const uint32_t bh_glob =
                 static_cast<uint32_t>((p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
-            uint32_t bits = 0u;
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              uint32_t rnd[4];
-              philox4x32_10(static_cast<uint32_t>(kv >> 2), static_cast<uint32_t>(q_first + c),
-                            bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
-              const uint32_t sel = (kv & 3) == 0 ? rnd[0] : (kv & 3) == 1 ? rnd[1]
-                                   : (kv & 3) == 2 ? rnd[2] : rnd[3];
-              if (sel >= p.drop.threshold) bits |= (1u << c);
-            }
-            keep = bits;
+            uint32_t bits[1];
+            dropout_keep_bits_transposed<32>(p.drop, bh_glob, kv, q_first, lane, bits);
+            keep = bits[0];
           }
+        }
+        if constexpr (kFeat) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) s[c] = __float_as_uint(__uint_as_float(s[c]) * p.scale_log2);
+          add_term_column<kBf16, 32>(p.bias, b, h, q_first, kv, p.Sq, p.Sk, s);
+          add_term_column<kBf16, 32>(p.mask, b, h, q_first, kv, p.Sq, p.Sk, s);
         }
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
@@ -396,23 +394,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const int c = 4 * c4 + 2 * k2;
             float x0 = __uint_as_float(s[c]), x1 = __uint_as_float(s[c + 1]);
             if constexpr (kFeat) {
-              x0 *= p.scale_log2;
-              x1 *= p.scale_log2;
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int qi = q_first + c + e;
-                float add = 0.f;
-                if (qi < p.Sq && kv < p.Sk) {
-                  if (p.bias.ptr)
-                    add += load_term<kBf16>(p.bias, b * p.bias.sb + h * p.bias.sh +
-                                                        static_cast<long long>(qi) * p.bias.sq + kv);
-                  if (p.mask.ptr)
-                    add += load_term<kBf16>(p.mask, b * p.mask.sb + h * p.mask.sh +
-                                                        static_cast<long long>(qi) * p.mask.sq + kv);
-                }
-                (e == 0 ? x0 : x1) = fmaf(add, kLog2e, e == 0 ? x0 : x1);
-              }
-              x0 += nlv[2 * k2];
+              x0 += nlv[2 * k2];      // already scaled, bias and mask added (below the loads)
               x1 += nlv[2 * k2 + 1];
             } else {
               fma2(x0, x1, x0, x1, p.scale_log2, p.scale_log2, nlv[2 * k2], nlv[2 * k2 + 1]);

@@ -37,10 +37,70 @@ __device__ __forceinline__ float do_scale_from_bits(const unsigned* bits) {
   return exp2f(static_cast<float>(-max(-60, min(60, e))));
 }
 
-template <bool kBf16>
-__device__ __forceinline__ float load_term(const ScoreTermDev& t, long long idx) {
-  if (t.is_f32) return __ldg(static_cast<const float*>(t.ptr) + idx);
-  return to_float16bit<kBf16>(__ldg(static_cast<const uint16_t*>(t.ptr) + idx));
+// Dropout keep bits of one key row (this thread) for kCols consecutive query columns, in the
+// backward's transposed layout. The Philox counter covers four adjacent keys of one query
+// (counter = (key/4, query, batch*Hq+head, 0), draw = output[key%4]), which suits the forward
+// (one thread owns a query row) but would make every backward thread throw away three of its
+// four draws. Instead the four lanes that share key/4 each draw for a different query of a group
+// of four and exchange the resulting bits with warp votes. All 32 lanes must call this together;
+// the key index of lane l must be a multiple of 4 plus (l % 4).
+template <int kCols>
+__device__ __forceinline__ void dropout_keep_bits_transposed(const DropoutDev& d, uint32_t bh_glob,
+                                                             int kv, int q_first, int lane,
+                                                             uint32_t (&bits)[kCols / 32]) {
+  const int member = lane & 3;
+#pragma unroll
+  for (int w = 0; w < kCols / 32; ++w) bits[w] = 0u;
+#pragma unroll
+  for (int m = 0; m < kCols / 4; ++m) {
+    uint32_t rnd[4];
+    philox4x32_10(static_cast<uint32_t>(kv >> 2), static_cast<uint32_t>(q_first + 4 * m + member),
+                  bh_glob, 0u, d.seed_lo, d.seed_hi, rnd);
+    // vote[k]: bit l says whether key (4*(l/4) + k) keeps query 4m + (l%4)
+    uint32_t vote[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) vote[k] = __ballot_sync(0xffffffffu, rnd[k] >= d.threshold);
+    const uint32_t mine = member == 0 ? vote[0] : member == 1 ? vote[1] : member == 2 ? vote[2] : vote[3];
+    const uint32_t four = (mine >> (lane & ~3)) & 0xfu;     // queries 4m .. 4m+3 for this key
+    bits[(4 * m) >> 5] |= four << ((4 * m) & 31);
+  }
+}
+
+// x[c] += log2(e) * term[b, h, q_first + c, kv] for kCols consecutive queries of this thread's key
+// row (x holds float bits). The loads of 16 columns are issued back to back, without branches in
+// between, so that their latencies overlap; indices are clamped instead of predicated (entries
+// outside the problem are masked or clipped later anyway).
+template <bool kBf16, int kCols>
+__device__ __forceinline__ void add_term_column(const ScoreTermDev& t, int b, int h, int q_first,
+                                                int kv, int Sq, int Sk, uint32_t (&x)[kCols]) {
+  if (t.ptr == nullptr) return;
+  const long long base = static_cast<long long>(b) * t.sb + static_cast<long long>(h) * t.sh +
+                         min(kv, Sk - 1);
+  if (t.is_f32) {
+    const float* ptr = static_cast<const float*>(t.ptr) + base;
+#pragma unroll
+    for (int c0 = 0; c0 < kCols; c0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        v[k] = __ldg(ptr + static_cast<long long>(min(q_first + c0 + k, Sq - 1)) * t.sq);
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        x[c0 + k] = __float_as_uint(fmaf(v[k], kLog2e, __uint_as_float(x[c0 + k])));
+    }
+  } else {
+    const uint16_t* ptr = static_cast<const uint16_t*>(t.ptr) + base;
+#pragma unroll
+    for (int c0 = 0; c0 < kCols; c0 += 16) {
+      uint16_t v[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        v[k] = __ldg(ptr + static_cast<long long>(min(q_first + c0 + k, Sq - 1)) * t.sq);
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        x[c0 + k] = __float_as_uint(fmaf(to_float16bit<kBf16>(v[k]), kLog2e, __uint_as_float(x[c0 + k])));
+    }
+  }
 }
 
 
