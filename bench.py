@@ -49,8 +49,8 @@ WORKLOADS = {
 # beyond it), dropout 0.1 with seed 42
 WORKLOAD_EXTRAS = {"mha_bias_mask_dropout_bf16": {"bias": True, "mask": True, "dropout": 0.1, "seed": 42}}
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward main kernel at the
-# default workload, from the ncu capture summarised under profiles/ (None until captured).
-BWD_MAIN_DRAM_TRAFFIC_BYTES = None
+# default workload, from the ncu capture summarised under profiles/ (B=2 capture: 307.0 MB read + 128.0 MB written, x4 for B=8).
+BWD_MAIN_DRAM_TRAFFIC_BYTES = 1.74e9
 
 
 def load_peaks():
@@ -395,7 +395,7 @@ def main():
             "frac": main_tflops / peak_burst,
             "frac_of_sustained_peak": main_tflops / peak_sust,
             "peak_source": f"{peak_kind}: cuBLAS bf16 burst {peak_burst}, sustained {peak_sust}",
-            "traffic": BWD_MAIN_DRAM_TRAFFIC_BYTES,
+            "traffic": BWD_MAIN_DRAM_TRAFFIC_BYTES if args.workload == "llama3_8b_causal_bf16" else None,
         },
         "e2e": {
             "value": f_step * world / (ms_e2e * 1e-3) / 1e12,
