@@ -28,8 +28,9 @@ struct Smem256 {
   static constexpr int kKOff = kQOff + kQTileBytes;
   static constexpr int kVOff = kKOff + kKVTileBytes;
   static constexpr int kBarOff = kVOff + kKVTileBytes;
-  // barriers: q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2], pv_done, o_full
-  static constexpr int kNumBars = 11;
+  // barriers: q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2 buffers][2 halves],
+  // pv_done, o_full
+  static constexpr int kNumBars = 13;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;
@@ -51,8 +52,8 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t bar_q_full = bars, bar_k_full = bars + 8, bar_k_empty = bars + 16;
   const uint32_t bar_v_full = bars + 24, bar_v_empty = bars + 32;
   auto bar_s_full = [&](int s) { return bars + 8u * (5 + s); };
-  auto bar_p_full = [&](int s) { return bars + 8u * (7 + s); };
-  const uint32_t bar_pv_done = bars + 8u * 9, bar_o_full = bars + 8u * 10;
+  auto bar_p_full = [&](int s, int half) { return bars + 8u * (7 + 2 * s + half); };
+  const uint32_t bar_pv_done = bars + 8u * 11, bar_o_full = bars + 8u * 12;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
@@ -88,7 +89,8 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     mbar_init(bar_v_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_s_full(s), 1);
-      mbar_init(bar_p_full(s), kBM);
+      mbar_init(bar_p_full(s, 0), kBM);
+      mbar_init(bar_p_full(s, 1), kBM);
     }
     mbar_init(bar_pv_done, 1);
     mbar_init(bar_o_full, 1);
@@ -163,14 +165,18 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           issue_s(buf ^ 1);
         }
         ok = mbar_wait(bar_v_full, j & 1, abort_flag);
-        if (ok) ok = mbar_wait(bar_p_full(buf), (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < kBN / 16; ++k) {
-          mma_ts(tmem_base + kColO, tmem_base + kColS + buf * kBN + k * 8,
-                 sdesc_advance(dV, k * 2048), idesc_o, (j == 0 && k == 0) ? 0u : 1u);
+        for (int half = 0; half < 2; ++half) {
+          if (ok) ok = mbar_wait(bar_p_full(buf, half), (j >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = half * (kBN / 32); k < (half + 1) * (kBN / 32); ++k) {
+            mma_ts(tmem_base + kColO, tmem_base + kColS + buf * kBN + k * 8,
+                   sdesc_advance(dV, k * 2048), idesc_o, (j == 0 && k == 0) ? 0u : 1u);
+          }
         }
+        if (!ok) break;
         mma_commit(bar_v_empty);
         mma_commit(bar_pv_done);
         if (j + 1 == nt) mma_commit(bar_o_full);
@@ -199,8 +205,8 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag)) ok = false;
         tc_fence_after();
       };
-      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv);
-      mbar_arrive(bar_p_full(buf));
+      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv,
+                                         [&](int half) { mbar_arrive(bar_p_full(buf, half)); });
       if (!ok) break;
     }
 

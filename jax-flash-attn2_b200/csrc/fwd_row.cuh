@@ -73,14 +73,16 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 //   S (tensor memory, 128 fp32 columns at tS) -> scores in the log2 domain (+ bias / mask),
 //   causal / padding mask, running maximum with lazy rescaling of O (D columns at tO, only if
 //   `have_o`), P = exp2(.) summed into l, dropout, P written back over S as 16-bit pairs.
-// Ends with the fences after which the caller may signal the MMA warp.
 // `before_o_rescale()` is called (by the whole warp) just before O is touched, so that a kernel
 // whose P.V MMA may still be running can wait for it there.
-template <int D, bool kBf16, bool kFeat, class BeforeRescale>
+// `after_half(h)` is called after half h (keys [64h, 64h+64)) of P has been stored and fenced: the
+// caller signals the MMA warp there.
+template <int D, bool kBf16, bool kFeat, class BeforeRescale, class AfterHalf>
 __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j, bool have_o,
                                                  const FwdKernelParams& p, int b, int h, int qi,
                                                  int row_lim, float sc, float& m, float& l,
-                                                 BeforeRescale before_o_rescale) {
+                                                 BeforeRescale before_o_rescale,
+                                                 AfterHalf after_half) {
   tc_fence_after();
   float x[kBN];
   {
@@ -138,51 +140,55 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
   }
   const float m_use = (m == -INFINITY) ? 0.f : m;
   const float neg_ms = -m_use * sc;
+  // P is produced and handed over in two halves of 64 keys: the P.V MMAs of the first half run
+  // while the exponentials of the second half are still being computed.
   float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-  for (int c = 0; c < kBN; c += 4) {
-    fma2(x[c], x[c + 1], x[c], x[c + 1], sc, sc, neg_ms, neg_ms);
-    fma2(x[c + 2], x[c + 3], x[c + 2], x[c + 3], sc, sc, neg_ms, neg_ms);
-    if (((c >> 1) & 7) < kPolyPer8) {
-      ex2_poly2(x[c], x[c + 1]);
-    } else {
-      x[c] = ex2_approx(x[c]);
-      x[c + 1] = ex2_approx(x[c + 1]);
-    }
-    if ((((c >> 1) + 1) & 7) < kPolyPer8) {
-      ex2_poly2(x[c + 2], x[c + 3]);
-    } else {
-      x[c + 2] = ex2_approx(x[c + 2]);
-      x[c + 3] = ex2_approx(x[c + 3]);
-    }
-    add2(l0, l1, l0, l1, x[c], x[c + 1]);
-    add2(l2, l3, l2, l3, x[c + 2], x[c + 3]);
-  }
-  l += (l0 + l1) + (l2 + l3);
-  if constexpr (kFeat) {
-    if (p.drop.enabled) {
-      const uint32_t bh_glob = static_cast<uint32_t>(
-          (p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
+  for (int half = 0; half < 2; ++half) {
 #pragma unroll
-      for (int c = 0; c < kBN; c += 4) {
-        uint32_t rnd[4];
-        philox4x32_10(static_cast<uint32_t>((kv0 + c) >> 2), static_cast<uint32_t>(qi),
-                      bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
+    for (int c = half * (kBN / 2); c < (half + 1) * (kBN / 2); c += 4) {
+      fma2(x[c], x[c + 1], x[c], x[c + 1], sc, sc, neg_ms, neg_ms);
+      fma2(x[c + 2], x[c + 3], x[c + 2], x[c + 3], sc, sc, neg_ms, neg_ms);
+      if (((c >> 1) & 7) < kPolyPer8) {
+        ex2_poly2(x[c], x[c + 1]);
+      } else {
+        x[c] = ex2_approx(x[c]);
+        x[c + 1] = ex2_approx(x[c + 1]);
+      }
+      if ((((c >> 1) + 1) & 7) < kPolyPer8) {
+        ex2_poly2(x[c + 2], x[c + 3]);
+      } else {
+        x[c + 2] = ex2_approx(x[c + 2]);
+        x[c + 3] = ex2_approx(x[c + 3]);
+      }
+      add2(l0, l1, l0, l1, x[c], x[c + 1]);
+      add2(l2, l3, l2, l3, x[c + 2], x[c + 3]);
+    }
+    if constexpr (kFeat) {
+      if (p.drop.enabled) {
+        const uint32_t bh_glob = static_cast<uint32_t>(
+            (p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          if (rnd[k] < p.drop.threshold) x[c + k] = 0.f;
+        for (int c = half * (kBN / 2); c < (half + 1) * (kBN / 2); c += 4) {
+          uint32_t rnd[4];
+          philox4x32_10(static_cast<uint32_t>((kv0 + c) >> 2), static_cast<uint32_t>(qi),
+                        bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (rnd[k] < p.drop.threshold) x[c + k] = 0.f;
+        }
       }
     }
-  }
-  {
-    uint32_t pk[kBN / 2];
+    uint32_t pk[kBN / 4];
 #pragma unroll
-    for (int c = 0; c < kBN / 2; ++c) pk[c] = pack2<kBf16>(x[2 * c], x[2 * c + 1]);
-    tmem_st32(tS, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
-    tmem_st32(tS + 32, reinterpret_cast<const uint32_t(&)[32]>(pk[32]));
+    for (int c = 0; c < kBN / 4; ++c)
+      pk[c] = pack2<kBf16>(x[half * (kBN / 2) + 2 * c], x[half * (kBN / 2) + 2 * c + 1]);
+    tmem_st32(tS + 32 * half, pk);
+    tc_wait_st();
+    tc_fence_before();
+    after_half(half);
   }
-  tc_wait_st();
-  tc_fence_before();
+  l += (l0 + l1) + (l2 + l3);
 }
 
 // Final scaling of this thread's output row: O / l (and 1/(1-p)) -> 16 bit -> 128-byte-swizzled

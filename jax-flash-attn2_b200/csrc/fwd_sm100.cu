@@ -24,6 +24,14 @@ namespace fa2 {
 
 namespace {
 
+#ifdef FA2_TRACE
+// Development aid (not compiled by default): per-role time stamps of one CTA.
+__device__ long long g_trace_fwd[40 * 1024];
+#define FA2_TF(role, idx) do { if (blockIdx.x == FA2_TRACE_CTA && (idx) < 1024) g_trace_fwd[(role) * 1024 + (idx)] = clock64(); } while (0)
+#else
+#define FA2_TF(role, idx) do { } while (0)
+#endif
+
 constexpr int kTilesPerCta = 2;
 constexpr int kThreads = 384;
 constexpr int kRegsSoftmax = 208;   // per scheduler: 2 softmax warps + 1 other warp share the 3 * 168 registers of the launch
@@ -38,8 +46,8 @@ struct FwdSmem {
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = kQOff + kTilesPerCta * kQTileBytes;
   static constexpr int kBarOff = kKVOff + kStages * kKVTileBytes;
-  // barriers: q_full[2], kv_full[S], kv_empty[S], s_full[2], p_full[2], o_full[2]
-  static constexpr int kNumBars = 2 + 2 * kStages + 6;
+  // barriers: q_full[2], kv_full[S], kv_empty[S], s_full[2], p_full[2 tiles][2 halves], o_full[2]
+  static constexpr int kNumBars = 2 + 2 * kStages + 8;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;  // room to align the base to 1024 B
@@ -64,14 +72,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   auto bar_kv_full = [&](int s) { return bars + 8u * (2 + s); };
   auto bar_kv_empty = [&](int s) { return bars + 8u * (2 + L::kStages + s); };
   auto bar_s_full = [&](int t) { return bars + 8u * (2 + 2 * L::kStages + t); };
-  auto bar_p_full = [&](int t) { return bars + 8u * (4 + 2 * L::kStages + t); };
-  auto bar_o_full = [&](int t) { return bars + 8u * (6 + 2 * L::kStages + t); };
+  auto bar_p_full = [&](int t, int half) { return bars + 8u * (4 + 2 * L::kStages + 2 * t + half); };
+  auto bar_o_full = [&](int t) { return bars + 8u * (8 + 2 * L::kStages + t); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  if (tid == 0) FA2_TF(32, 0);
 
   // ---- work item ----------------------------------------------------------------------------
   const int nbh = p.B * p.Hq;
@@ -106,7 +115,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_q_full(t), 1);
       mbar_init(bar_s_full(t), 1);
-      mbar_init(bar_p_full(t), kBM);
+      mbar_init(bar_p_full(t, 0), kBM);
+      mbar_init(bar_p_full(t, 1), kBM);
       mbar_init(bar_o_full(t), 1);
     }
     for (int s = 0; s < L::kStages; ++s) {
@@ -182,10 +192,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         mma_commit(bar_s_full(t));
       };
-      auto issue_o = [&](int t, int slot, bool first) {
+      auto issue_o = [&](int t, int slot, bool first, int half) {
         const uint64_t b0 = sdesc_advance(dKV_mn0, slot * L::kKVTileBytes);
 #pragma unroll
-        for (int k = 0; k < kBN / 16; ++k) {
+        for (int k = half * (kBN / 32); k < (half + 1) * (kBN / 32); ++k) {
           mma_ts(tmem_base + kColO + t * D, tmem_base + kColS + t * kBN + k * 8,
                  sdesc_advance(b0, k * 2048), idesc_o, (first && k == 0) ? 0u : 1u);
         }
@@ -215,10 +225,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
           for (int t = 0; t < kTilesPerCta; ++t) {
             if (j < n_tiles[t]) {
-              ok = mbar_wait(bar_p_full(t), j & 1, abort_flag);
+              ok = mbar_wait(bar_p_full(t, 0), j & 1, abort_flag);
+              if (!ok) break;
+              FA2_TF(t, j);
+              tc_fence_after();
+              issue_o(t, slot_v, j == 0, 0);
+              ok = mbar_wait(bar_p_full(t, 1), j & 1, abort_flag);
               if (!ok) break;
               tc_fence_after();
-              issue_o(t, slot_v, j == 0);
+              issue_o(t, slot_v, j == 0, 1);
               if (j + 1 < n_tiles[t]) {
                 issue_s(t, slot_k);
               } else {
@@ -256,9 +271,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int j = 0; j < nt; ++j) {
       ok = mbar_wait(bar_s_full(t), j & 1, abort_flag);
       if (!ok) break;
-      softmax_tile_row<D, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {});
-      mbar_arrive(bar_p_full(t));
+      if (lane == 0) FA2_TF(8 + warp, j);
+      softmax_tile_row<D, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
+                                        [&](int half) { mbar_arrive(bar_p_full(t, half)); });
+      if (lane == 0) FA2_TF(16 + warp, j);
     }
+    if (lane == 0) FA2_TF(24 + warp, 0);
 
     // ---- epilogue: O / l -> 16 bit -> swizzled shared memory -> TMA store; LSE ---------------
     if (ok && tile_valid) {
@@ -278,6 +296,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (!ok && r == 0) atomicOr(p.status, 4);
   }
 
+  if (tid == 0) FA2_TF(33, 0);
   // ---- teardown -------------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -319,6 +338,12 @@ static cudaError_t launch_d(const FwdLaunch& a, cudaStream_t stream) {
     default: return launch_one<D, true, true, true>(a, stream);
   }
 }
+
+#ifdef FA2_TRACE
+extern "C" int fa2_trace_read_fwd(long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace_fwd, sizeof(long long) * n));
+}
+#endif
 
 cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream) {
   switch (a.head_dim) {
