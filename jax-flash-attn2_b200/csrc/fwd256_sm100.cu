@@ -30,7 +30,7 @@ struct Smem256 {
   static constexpr int kBarOff = kVOff + kKVTileBytes;
   // barriers: q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2 buffers][2 halves],
   // pv_done, o_full
-  static constexpr int kNumBars = 13;
+  static constexpr int kNumBars = 9 + 2 * kPSplit;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;
@@ -52,8 +52,8 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t bar_q_full = bars, bar_k_full = bars + 8, bar_k_empty = bars + 16;
   const uint32_t bar_v_full = bars + 24, bar_v_empty = bars + 32;
   auto bar_s_full = [&](int s) { return bars + 8u * (5 + s); };
-  auto bar_p_full = [&](int s, int half) { return bars + 8u * (7 + 2 * s + half); };
-  const uint32_t bar_pv_done = bars + 8u * 11, bar_o_full = bars + 8u * 12;
+  auto bar_p_full = [&](int s, int half) { return bars + 8u * (7 + kPSplit * s + half); };
+  const uint32_t bar_pv_done = bars + 8u * (7 + 2 * kPSplit), bar_o_full = bars + 8u * (8 + 2 * kPSplit);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
@@ -89,8 +89,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     mbar_init(bar_v_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_s_full(s), 1);
-      mbar_init(bar_p_full(s, 0), kBM);
-      mbar_init(bar_p_full(s, 1), kBM);
+      for (int hh = 0; hh < kPSplit; ++hh) mbar_init(bar_p_full(s, hh), kBM);
     }
     mbar_init(bar_pv_done, 1);
     mbar_init(bar_o_full, 1);
@@ -166,12 +165,12 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         ok = mbar_wait(bar_v_full, j & 1, abort_flag);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < kPSplit; ++half) {
           if (ok) ok = mbar_wait(bar_p_full(buf, half), (j >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
-          for (int k = half * (kBN / 32); k < (half + 1) * (kBN / 32); ++k) {
+          for (int k = half * (kPCols / 16); k < (half + 1) * (kPCols / 16); ++k) {
             mma_ts(tmem_base + kColO, tmem_base + kColS + buf * kBN + k * 8,
                    sdesc_advance(dV, k * 2048), idesc_o, (j == 0 && k == 0) ? 0u : 1u);
           }

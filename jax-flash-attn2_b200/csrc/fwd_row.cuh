@@ -21,6 +21,12 @@ constexpr float kRescaleThreshold = 8.0f;   // in log2 units: P stays below 2^8
 #define FA2_FWD_POLY_PER8 0
 #endif
 constexpr int kPolyPer8 = FA2_FWD_POLY_PER8;
+// P of one K/V tile is handed to the MMA warp in this many pieces (2 or 4).
+#ifndef FA2_FWD_P_SPLIT
+#define FA2_FWD_P_SPLIT 2
+#endif
+constexpr int kPSplit = FA2_FWD_P_SPLIT;
+constexpr int kPCols = kBN / kPSplit;   // keys per piece
 
 template <bool kBf16>
 __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermDev& t, int b,
@@ -75,8 +81,8 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 //   `have_o`), P = exp2(.) summed into l, dropout, P written back over S as 16-bit pairs.
 // `before_o_rescale()` is called (by the whole warp) just before O is touched, so that a kernel
 // whose P.V MMA may still be running can wait for it there.
-// `after_half(h)` is called after half h (keys [64h, 64h+64)) of P has been stored and fenced: the
-// caller signals the MMA warp there.
+// `after_half(h)` is called after piece h (keys [kPCols h, kPCols (h+1))) of P has been stored and
+// fenced: the caller signals the MMA warp there.
 template <int D, bool kBf16, bool kFeat, class BeforeRescale, class AfterHalf>
 __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j, bool have_o,
                                                  const FwdKernelParams& p, int b, int h, int qi,
@@ -144,9 +150,9 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
   // while the exponentials of the second half are still being computed.
   float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
+  for (int half = 0; half < kPSplit; ++half) {
 #pragma unroll
-    for (int c = half * (kBN / 2); c < (half + 1) * (kBN / 2); c += 4) {
+    for (int c = half * kPCols; c < (half + 1) * kPCols; c += 4) {
       fma2(x[c], x[c + 1], x[c], x[c + 1], sc, sc, neg_ms, neg_ms);
       fma2(x[c + 2], x[c + 3], x[c + 2], x[c + 3], sc, sc, neg_ms, neg_ms);
       if (((c >> 1) & 7) < kPolyPer8) {
@@ -169,7 +175,7 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
         const uint32_t bh_glob = static_cast<uint32_t>(
             (p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
 #pragma unroll
-        for (int c = half * (kBN / 2); c < (half + 1) * (kBN / 2); c += 4) {
+        for (int c = half * kPCols; c < (half + 1) * kPCols; c += 4) {
           uint32_t rnd[4];
           philox4x32_10(static_cast<uint32_t>((kv0 + c) >> 2), static_cast<uint32_t>(qi),
                         bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
@@ -179,11 +185,15 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
         }
       }
     }
-    uint32_t pk[kBN / 4];
+    uint32_t pk[kPCols / 2];
 #pragma unroll
-    for (int c = 0; c < kBN / 4; ++c)
-      pk[c] = pack2<kBf16>(x[half * (kBN / 2) + 2 * c], x[half * (kBN / 2) + 2 * c + 1]);
-    tmem_st32(tS + 32 * half, pk);
+    for (int c = 0; c < kPCols / 2; ++c)
+      pk[c] = pack2<kBf16>(x[half * kPCols + 2 * c], x[half * kPCols + 2 * c + 1]);
+    if constexpr (kPSplit == 2) {
+      tmem_st32(tS + 32 * half, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
+    } else {
+      tmem_st16(tS + 16 * half, pk);
+    }
     tc_wait_st();
     tc_fence_before();
     after_half(half);

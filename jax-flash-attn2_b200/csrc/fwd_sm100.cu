@@ -47,7 +47,7 @@ struct FwdSmem {
   static constexpr int kKVOff = kQOff + kTilesPerCta * kQTileBytes;
   static constexpr int kBarOff = kKVOff + kStages * kKVTileBytes;
   // barriers: q_full[2], kv_full[S], kv_empty[S], s_full[2], p_full[2 tiles][2 halves], o_full[2]
-  static constexpr int kNumBars = 2 + 2 * kStages + 8;
+  static constexpr int kNumBars = 2 + 2 * kStages + 4 + 2 * kPSplit;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;  // room to align the base to 1024 B
@@ -72,8 +72,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   auto bar_kv_full = [&](int s) { return bars + 8u * (2 + s); };
   auto bar_kv_empty = [&](int s) { return bars + 8u * (2 + L::kStages + s); };
   auto bar_s_full = [&](int t) { return bars + 8u * (2 + 2 * L::kStages + t); };
-  auto bar_p_full = [&](int t, int half) { return bars + 8u * (4 + 2 * L::kStages + 2 * t + half); };
-  auto bar_o_full = [&](int t) { return bars + 8u * (8 + 2 * L::kStages + t); };
+  auto bar_p_full = [&](int t, int half) { return bars + 8u * (4 + 2 * L::kStages + kPSplit * t + half); };
+  auto bar_o_full = [&](int t) { return bars + 8u * (4 + 2 * L::kStages + 2 * kPSplit + t); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
@@ -115,8 +115,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_q_full(t), 1);
       mbar_init(bar_s_full(t), 1);
-      mbar_init(bar_p_full(t, 0), kBM);
-      mbar_init(bar_p_full(t, 1), kBM);
+      for (int hh = 0; hh < kPSplit; ++hh) mbar_init(bar_p_full(t, hh), kBM);
       mbar_init(bar_o_full(t), 1);
     }
     for (int s = 0; s < L::kStages; ++s) {
@@ -195,7 +194,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       auto issue_o = [&](int t, int slot, bool first, int half) {
         const uint64_t b0 = sdesc_advance(dKV_mn0, slot * L::kKVTileBytes);
 #pragma unroll
-        for (int k = half * (kBN / 32); k < (half + 1) * (kBN / 32); ++k) {
+        for (int k = half * (kPCols / 16); k < (half + 1) * (kPCols / 16); ++k) {
           mma_ts(tmem_base + kColO + t * D, tmem_base + kColS + t * kBN + k * 8,
                  sdesc_advance(b0, k * 2048), idesc_o, (first && k == 0) ? 0u : 1u);
         }
@@ -225,15 +224,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
           for (int t = 0; t < kTilesPerCta; ++t) {
             if (j < n_tiles[t]) {
-              ok = mbar_wait(bar_p_full(t, 0), j & 1, abort_flag);
+#pragma unroll
+              for (int hh = 0; hh < kPSplit; ++hh) {
+                ok = mbar_wait(bar_p_full(t, hh), j & 1, abort_flag);
+                if (!ok) break;
+                if (hh == 0) FA2_TF(t, j);
+                tc_fence_after();
+                issue_o(t, slot_v, j == 0, hh);
+              }
               if (!ok) break;
-              FA2_TF(t, j);
-              tc_fence_after();
-              issue_o(t, slot_v, j == 0, 0);
-              ok = mbar_wait(bar_p_full(t, 1), j & 1, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              issue_o(t, slot_v, j == 0, 1);
               if (j + 1 < n_tiles[t]) {
                 issue_s(t, slot_k);
               } else {
