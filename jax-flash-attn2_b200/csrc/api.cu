@@ -210,7 +210,8 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->q_strides, 128, "q")) ||
       (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->k_strides, 128, "k")) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->v_strides, 128, "v")) ||
-      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->o_strides, 128, "o")))
+      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->o_strides, 128, "o")) ||
+      (rc = make_tmap(&L.tmO1, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->o_strides, 128, "o", 1)))
     return rc;
 
   FwdKernelParams& kp = L.kp;

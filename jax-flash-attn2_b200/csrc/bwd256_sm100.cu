@@ -203,7 +203,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __syncwarp();
   } else if (warp == 12) {
     // =========================== MMA issuer ==================================================
-    if (lane == 0 && T > 0) {
+    if (true && T > 0) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, 128, kBQ, false, false);
       constexpr uint32_t idesc_dkv = make_idesc(kBf16, 128, 128, false, true);
       constexpr uint32_t idesc_dq = make_idesc(kBf16, 128, kBQ, true, true);
@@ -223,7 +223,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int k = 0; k < kD / 16; ++k) {
           const uint32_t offa = (k >> 2) * L::kKBlock + (k & 3) * 32;
           const uint32_t offb = (k >> 2) * L::kQBlock + (k & 3) * 32;
-          mma_ss(tmem_base + d_col, sdesc_advance(a_desc, offa), sdesc_advance(b_desc, offb),
+          mma_ss_e(tmem_base + d_col, sdesc_advance(a_desc, offa), sdesc_advance(b_desc, offb),
                  idesc_s, k > 0 ? 1u : 0u);
         }
       };
@@ -233,66 +233,66 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           // P^T for queries [16k, 16k+16): 8 packed columns; queries [0,32) were written by
           // warpgroup 0 at column 0, queries [32,64) by warpgroup 1 at column 32
           const uint32_t a_col = kColS + (k < 2 ? 8 * k : 32 + 8 * (k - 2));
-          mma_ts(tmem_base + kColdV, tmem_base + a_col, sdesc_advance(ddO_mn, k * 2048), idesc_dkv,
+          mma_ts_e(tmem_base + kColdV, tmem_base + a_col, sdesc_advance(ddO_mn, k * 2048), idesc_dkv,
                  (first && k == 0) ? 0u : 1u);
         }
       };
       auto issue_dk = [&](bool first) {
 #pragma unroll
         for (int k = 0; k < kBQ / 16; ++k)
-          mma_ss(tmem_base + kColdK, sdesc_advance(ddS_k, k * 32), sdesc_advance(dQ_mn, k * 2048),
+          mma_ss_e(tmem_base + kColdK, sdesc_advance(ddS_k, k * 32), sdesc_advance(dQ_mn, k * 2048),
                  idesc_dkv, (first && k == 0) ? 0u : 1u);
       };
       auto issue_dq = [&]() {
 #pragma unroll
         for (int k = 0; k < kBK / 16; ++k)
-          mma_ss(tmem_base + kColdQ, sdesc_advance(dKh_mn, k * 2048), sdesc_advance(ddS_mn, k * 2048),
+          mma_ss_e(tmem_base + kColdQ, sdesc_advance(dKh_mn, k * 2048), sdesc_advance(ddS_mn, k * 2048),
                  idesc_dq, k > 0 ? 1u : 0u);
       };
 
-      ok = mbar_wait(bar_kv_full, 0, abort_flag);
-      if (ok) ok = mbar_wait(bar_q_full, 0, abort_flag);
+      ok = mbar_wait_warp(bar_kv_full, 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar_q_full, 0, abort_flag);
       if (ok) {
         tc_fence_after();
         issue_kd(kColS, dK_k, dQ_k);
-        mma_commit(bar_s_full);
-        ok = mbar_wait(bar_do_full, 0, abort_flag);
+        mma_commit_e(bar_s_full);
+        ok = mbar_wait_warp(bar_do_full, 0, abort_flag);
       }
       if (ok) {
         tc_fence_after();
         issue_kd(kColdP, dV_k, ddO_k);
-        mma_commit(bar_dp_full);
+        mma_commit_e(bar_dp_full);
       }
       for (int it = 0; it < T && ok; ++it) {
         const uint32_t par = it & 1;
-        ok = mbar_wait(bar_p_full, par, abort_flag);
+        ok = mbar_wait_warp(bar_p_full, par, abort_flag);
         if (!ok) break;
         tc_fence_after();
         issue_dv(it == 0);
-        mma_commit(bar_do_empty);
-        ok = mbar_wait(bar_ds_full, par, abort_flag);
-        if (ok && it > 0) ok = mbar_wait(bar_dq_drained, (it - 1) & 1, abort_flag);
+        mma_commit_e(bar_do_empty);
+        ok = mbar_wait_warp(bar_ds_full, par, abort_flag);
+        if (ok && it > 0) ok = mbar_wait_warp(bar_dq_drained, (it - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         issue_dq();
-        mma_commit(bar_dq_full);
+        mma_commit_e(bar_dq_full);
         issue_dk(it == 0);
-        mma_commit(bar_q_empty);
+        mma_commit_e(bar_q_empty);
         if (it + 1 < T) {
-          ok = mbar_wait(bar_q_full, (it + 1) & 1, abort_flag);
+          ok = mbar_wait_warp(bar_q_full, (it + 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           issue_kd(kColS, dK_k, dQ_k);
-          mma_commit(bar_s_full);
-          ok = mbar_wait(bar_do_full, (it + 1) & 1, abort_flag);
+          mma_commit_e(bar_s_full);
+          ok = mbar_wait_warp(bar_do_full, (it + 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           issue_kd(kColdP, dV_k, ddO_k);
-          mma_commit(bar_dp_full);
+          mma_commit_e(bar_dp_full);
         }
       }
-      if (ok) mma_commit(bar_dkv_full);
-      if (!ok) atomicOr(p.status, 16);
+      if (ok) mma_commit_e(bar_dkv_full);
+      if (!ok && lane == 0) atomicOr(p.status, 16);
     }
     __syncwarp();
   } else if (warp >= 8) {

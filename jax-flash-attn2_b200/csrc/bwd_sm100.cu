@@ -237,7 +237,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else if (warp == 12) {
     // =========================== MMA issuer ==================================================
-    if (lane == 0 && T > 0) {
+    if (true && T > 0) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, 128, 128, false, false);
       constexpr uint32_t idesc_dv = make_idesc(kBf16, 128, D, false, true);
       constexpr uint32_t idesc_dk = make_idesc(kBf16, 128, D, false, true);
@@ -258,7 +258,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
-          mma_ss(tmem_base + d_col, sdesc_advance(a_desc, off), sdesc_advance(b_desc, off), idesc_s,
+          mma_ss_e(tmem_base + d_col, sdesc_advance(a_desc, off), sdesc_advance(b_desc, off), idesc_s,
                  k > 0 ? 1u : 0u);
         }
       };
@@ -268,7 +268,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // P^T for queries [16k, 16k+16): 8 packed columns; the two 64-query halves were written
           // by different warpgroups at columns 0 and 64 of the S region.
           const uint32_t a_col = kColS + (k < 4 ? 8 * k : 64 + 8 * (k - 4));
-          mma_ts(tmem_base + kColdV, tmem_base + a_col, sdesc_advance(ddO_mn, k * 2048), idesc_dv,
+          mma_ts_e(tmem_base + kColdV, tmem_base + a_col, sdesc_advance(ddO_mn, k * 2048), idesc_dv,
                  (first && k == 0) ? 0u : 1u);
         }
       };
@@ -276,7 +276,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int k = 0; k < kBM / 16; ++k) {
           const uint32_t a_off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
-          mma_ss(tmem_base + kColdK, sdesc_advance(ddS_k, a_off), sdesc_advance(q_mn, k * 2048),
+          mma_ss_e(tmem_base + kColdK, sdesc_advance(ddS_k, a_off), sdesc_advance(q_mn, k * 2048),
                  idesc_dk, (first && k == 0) ? 0u : 1u);
         }
       };
@@ -284,66 +284,66 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int k = 0; k < kBN / 16; ++k) {
           // A = dS (M = query, contiguous in the dS^T rows; K = key rows), B = K tile, both MN-major
-          mma_ss(tmem_base + kColdQ, sdesc_advance(ddS_mn, k * 2048), sdesc_advance(dK_mn, k * 2048),
+          mma_ss_e(tmem_base + kColdQ, sdesc_advance(ddS_mn, k * 2048), sdesc_advance(dK_mn, k * 2048),
                  idesc_dq, k > 0 ? 1u : 0u);
         }
       };
 
-      ok = mbar_wait(bar_kv_full, 0, abort_flag);
-      if (ok) ok = mbar_wait(bar_q_full(0), 0, abort_flag);
+      ok = mbar_wait_warp(bar_kv_full, 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar_q_full(0), 0, abort_flag);
       if (ok) {
         tc_fence_after();
         issue_kd(kColS, dK_k, dQ_k0);
-        mma_commit(bar_s_full);
-        ok = mbar_wait(bar_do_full, 0, abort_flag);
+        mma_commit_e(bar_s_full);
+        ok = mbar_wait_warp(bar_do_full, 0, abort_flag);
       }
       if (ok) {
         tc_fence_after();
         issue_kd(kColdP, dV_k, ddO_k);
-        mma_commit(bar_dp_full);
+        mma_commit_e(bar_dp_full);
       }
       for (int it = 0; it < T && ok; ++it) {
         const int st = it & 1, nx = st ^ 1;
         const uint32_t par = it & 1;
         const uint32_t par_next = ((it + 1) >> 1) & 1;
         const bool has_next = it + 1 < T;
-        ok = mbar_wait(bar_p_full, par, abort_flag);
+        ok = mbar_wait_warp(bar_p_full, par, abort_flag);
         if (!ok) break;
         FA2_T(0, it);
         tc_fence_after();
         issue_dv(it == 0);
-        mma_commit(bar_do_empty);          // the single dO buffer can be refilled
+        mma_commit_e(bar_do_empty);          // the single dO buffer can be refilled
         if (has_next) {
           FA2_T(40, it);
-          ok = mbar_wait(bar_q_full(nx), par_next, abort_flag);
+          ok = mbar_wait_warp(bar_q_full(nx), par_next, abort_flag);
           if (!ok) break;
           FA2_T(41, it);
           tc_fence_after();
           issue_kd(kColS, dK_k, sdesc_advance(dQ_k0, nx * L::kTileBytes));
-          mma_commit(bar_s_full);
+          mma_commit_e(bar_s_full);
         }
         FA2_T(1, it);
-        ok = mbar_wait(bar_ds_full, par, abort_flag);
+        ok = mbar_wait_warp(bar_ds_full, par, abort_flag);
         if (!ok) break;
         FA2_T(2, it);
         tc_fence_after();
         issue_dq();
-        mma_commit(bar_dq_full);
+        mma_commit_e(bar_dq_full);
         issue_dk(sdesc_advance(dQ_mn0, st * L::kTileBytes), it == 0);
-        mma_commit(bar_q_empty(st));
+        mma_commit_e(bar_q_empty(st));
         if (has_next) {
           FA2_T(3, it);
-          ok = mbar_wait(bar_dq_drained, par, abort_flag);
-          if (ok) ok = mbar_wait(bar_do_full, (it + 1) & 1, abort_flag);
+          ok = mbar_wait_warp(bar_dq_drained, par, abort_flag);
+          if (ok) ok = mbar_wait_warp(bar_do_full, (it + 1) & 1, abort_flag);
           if (!ok) break;
           FA2_T(4, it);
           tc_fence_after();
           issue_kd(kColdP, dV_k, ddO_k);
-          mma_commit(bar_dp_full);
+          mma_commit_e(bar_dp_full);
         }
       }
-      if (ok) mma_commit(bar_dkv_full);
-      if (!ok) atomicOr(p.status, 16);
+      if (ok) mma_commit_e(bar_dkv_full);
+      if (!ok && lane == 0) atomicOr(p.status, 16);
     }
     __syncwarp();
   } else if (warp >= 8) {

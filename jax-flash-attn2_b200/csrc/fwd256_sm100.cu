@@ -132,7 +132,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     __syncwarp();
   } else if (warp == 4) {
     // =========================== MMA issuer ==================================================
-    if (lane == 0 && nt > 0) {
+    if (true && nt > 0) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, kBM, kBN, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, kBM, kD, false, true);
       const uint64_t dQ = make_sdesc(sQ, 16, 1024);
@@ -143,14 +143,14 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
           const uint32_t off = (k >> 2) * kBlockBytes + (k & 3) * 32;
-          mma_ss(tmem_base + kColS + buf * kBN, sdesc_advance(dQ, off), sdesc_advance(dK, off),
+          mma_ss_e(tmem_base + kColS + buf * kBN, sdesc_advance(dQ, off), sdesc_advance(dK, off),
                  idesc_s, k > 0 ? 1u : 0u);
         }
-        mma_commit(bar_s_full(buf));
-        mma_commit(bar_k_empty);
+        mma_commit_e(bar_s_full(buf));
+        mma_commit_e(bar_k_empty);
       };
-      ok = mbar_wait(bar_q_full, 0, abort_flag);
-      if (ok) ok = mbar_wait(bar_k_full, 0, abort_flag);
+      ok = mbar_wait_warp(bar_q_full, 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar_k_full, 0, abort_flag);
       if (ok) {
         tc_fence_after();
         issue_s(0);
@@ -158,29 +158,29 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int j = 0; j < nt && ok; ++j) {
         const int buf = j & 1;
         if (j + 1 < nt) {
-          ok = mbar_wait(bar_k_full, (j + 1) & 1, abort_flag);
+          ok = mbar_wait_warp(bar_k_full, (j + 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           issue_s(buf ^ 1);
         }
-        ok = mbar_wait(bar_v_full, j & 1, abort_flag);
+        ok = mbar_wait_warp(bar_v_full, j & 1, abort_flag);
 #pragma unroll
         for (int half = 0; half < kPSplit; ++half) {
-          if (ok) ok = mbar_wait(bar_p_full(buf, half), (j >> 1) & 1, abort_flag);
+          if (ok) ok = mbar_wait_warp(bar_p_full(buf, half), (j >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
           for (int k = half * (kPCols / 16); k < (half + 1) * (kPCols / 16); ++k) {
-            mma_ts(tmem_base + kColO, tmem_base + kColS + buf * kBN + k * 8,
+            mma_ts_e(tmem_base + kColO, tmem_base + kColS + buf * kBN + k * 8,
                    sdesc_advance(dV, k * 2048), idesc_o, (j == 0 && k == 0) ? 0u : 1u);
           }
         }
         if (!ok) break;
-        mma_commit(bar_v_empty);
-        mma_commit(bar_pv_done);
-        if (j + 1 == nt) mma_commit(bar_o_full);
+        mma_commit_e(bar_v_empty);
+        mma_commit_e(bar_pv_done);
+        if (j + 1 == nt) mma_commit_e(bar_o_full);
       }
-      if (!ok) atomicOr(p.status, 2);
+      if (!ok && lane == 0) atomicOr(p.status, 2);
     }
     __syncwarp();
   } else {

@@ -9,6 +9,7 @@ namespace fa2 {
 
 struct FwdLaunch {
   CUtensorMap tmQ, tmK, tmV, tmO;
+  CUtensorMap tmO1;   // o with a box of one 64-column block (head dim 64 / 128 kernel)
   FwdKernelParams kp;
   int head_dim;
   bool bf16, causal, feat;

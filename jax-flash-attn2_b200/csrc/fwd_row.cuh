@@ -239,4 +239,32 @@ __device__ __forceinline__ void epilogue_row(uint32_t tO, bool has_acc, uint8_t*
   fence_proxy_async_smem();
 }
 
+// The same in pieces, for a kernel that stages one 64-column block at a time:
+// epilogue_stats stores the log-sum-exp and returns the factor the O row is multiplied with;
+// epilogue_block converts 64 accumulator values (two 32-column groups) and writes them as the
+// row's 128-byte line of a swizzled [128][64] block.
+template <bool kFeat>
+__device__ __forceinline__ float epilogue_stats(const FwdKernelParams& p, int b, int h, int qi,
+                                                float sc, float m, float l) {
+  const float inv = (l > 0.f) ? (kFeat ? p.drop.inv_keep : 1.f) / l : 0.f;
+  const float lse = (l > 0.f) ? (m * sc + lg2_approx(l)) * kLn2 : -INFINITY;
+  if (qi < p.Sq)
+    p.lse[static_cast<long long>(b) * p.lse_sb + static_cast<long long>(h) * p.lse_sh + qi] = lse;
+  return inv;
+}
+template <bool kBf16>
+__device__ __forceinline__ void epilogue_block(const uint32_t (&o64)[64], uint8_t* block_gen, int r,
+                                               float inv) {
+  uint8_t* line = block_gen + r * 128;
+#pragma unroll
+  for (int chunk = 0; chunk < 8; ++chunk) {
+    uint4 v;
+    v.x = pack2<kBf16>(__uint_as_float(o64[8 * chunk + 0]) * inv, __uint_as_float(o64[8 * chunk + 1]) * inv);
+    v.y = pack2<kBf16>(__uint_as_float(o64[8 * chunk + 2]) * inv, __uint_as_float(o64[8 * chunk + 3]) * inv);
+    v.z = pack2<kBf16>(__uint_as_float(o64[8 * chunk + 4]) * inv, __uint_as_float(o64[8 * chunk + 5]) * inv);
+    v.w = pack2<kBf16>(__uint_as_float(o64[8 * chunk + 6]) * inv, __uint_as_float(o64[8 * chunk + 7]) * inv);
+    *reinterpret_cast<uint4*>(line + ((chunk ^ (r & 7)) << 4)) = v;
+  }
+}
+
 }  // namespace fa2

@@ -1,21 +1,24 @@
-// Forward attention kernel for sm_100a.
+// Forward attention kernel for sm_100a (head dim 64 and 128).
 //
 // Replaces the Triton kernel _attn_fwd / _attn_fwd_inner of the reference
 // (jax_flash_attn2/flash_attention_triton/_forward_triton.py:60-164, 213-459).
 //
-// One CTA owns 256 query rows of one (batch, query head): two 128-row tiles that share one
-// stream of K/V tiles. Roles (12 warps; registers are moved from the last warpgroup to the
-// softmax warpgroups with setmaxnreg):
-//   warps 0-3  : softmax of query tile 0, one thread per row (TMEM lane == row)
-//   warps 4-7  : softmax of query tile 1
+// Persistent kernel: one CTA per SM walks over work items. A work item is 256 query rows of one
+// (batch, query head): two 128-row tiles that share one stream of K/V tiles. Items are ordered
+// longest first (causal) and dealt round-robin to the CTAs. Roles (12 warps; registers are moved
+// from the last warpgroup to the softmax warpgroups with setmaxnreg):
+//   warps 0-3  : softmax + epilogue of query tile 0, one thread per row (TMEM lane == row)
+//   warps 4-7  : softmax + epilogue of query tile 1
 //   warp  8    : tcgen05.mma issuer (one elected thread)
-//   warp  9    : TMA producer (Q once, then K_j, V_j into a ring of shared-memory slots)
+//   warp  9    : TMA producer (Q tiles per item, K_j / V_j through a ring of shared-memory slots)
 //   warps 10-11: idle (they complete the warpgroup that gives up its registers)
 // Tensor memory (columns): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
 // P (16-bit, two values per column) overwrites the first 64 columns of its S tile and is the
 // A operand of the P.V MMA, read straight from tensor memory.
 // The two query tiles ping-pong: while the softmax warps of one tile work on S_j, the tensor
-// core runs the MMAs of the other tile.
+// core runs the MMAs of the other tile. Across items the roles run ahead of each other: the
+// producer refills a Q tile as soon as its last S MMA has completed and the K/V ring never drains,
+// so the next item's first MMAs overlap the epilogue (O -> shared memory -> TMA store) of this one.
 #include "fwd_launch.cuh"
 #include "fwd_row.cuh"
 #include "ptx_sm100.cuh"
@@ -26,7 +29,7 @@ namespace {
 
 #ifdef FA2_TRACE
 // Development aid (not compiled by default): per-role time stamps of one CTA.
-__device__ long long g_trace_fwd[40 * 1024];
+__device__ long long g_trace_fwd[56 * 1024];
 #define FA2_TF(role, idx) do { if (blockIdx.x == FA2_TRACE_CTA && (idx) < 1024) g_trace_fwd[(role) * 1024 + (idx)] = clock64(); } while (0)
 #else
 #define FA2_TF(role, idx) do { } while (0)
@@ -44,21 +47,58 @@ struct FwdSmem {
   static constexpr int kStages = (D == 64) ? 8 : 4;
   static constexpr int kBlockBytes = kBM * 128;       // one [128 rows][64 elements] block
   static constexpr int kQOff = 0;
-  static constexpr int kKVOff = kQOff + kTilesPerCta * kQTileBytes;
+  static constexpr int kOOff = kQOff + kTilesPerCta * kQTileBytes;     // O staging: one 64-column block per tile
+  static constexpr int kKVOff = kOOff + kTilesPerCta * kBlockBytes;
   static constexpr int kBarOff = kKVOff + kStages * kKVTileBytes;
-  // barriers: q_full[2], kv_full[S], kv_empty[S], s_full[2], p_full[2 tiles][2 halves], o_full[2]
-  static constexpr int kNumBars = 2 + 2 * kStages + 4 + 2 * kPSplit;
+  // barriers: q_full[2], q_free[2], kv_full[S], kv_empty[S], s_full[2], p_full[2][kPSplit],
+  // o_full[2], o_free[2]
+  static constexpr int kNumBars = 4 + 2 * kStages + 2 + 2 * kPSplit + 4;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;  // room to align the base to 1024 B
+  static_assert(kDynamicBytes <= 232448, "shared memory budget exceeded");
 };
+
+// One work item as every role sees it.
+struct FwdItem {
+  int b, h, hk, q0;
+  int n_tiles[kTilesPerCta];
+  int n_max;
+};
+
+template <bool kCausal>
+__device__ __forceinline__ void decode_item(const FwdKernelParams& p, int w, FwdItem& it) {
+  const int nbh = p.B * p.Hq;
+  const int qb_rank = w / nbh;
+  const int bh = w - qb_rank * nbh;
+  // causal: the longest blocks come first
+  const int qblk = kCausal ? (p.n_qblk - 1 - qb_rank) : qb_rank;
+  it.b = bh / p.Hq;
+  it.h = bh - it.b * p.Hq;
+  it.hk = it.h / p.G;
+  it.q0 = qblk * (kBM * kTilesPerCta);
+#pragma unroll
+  for (int t = 0; t < kTilesPerCta; ++t) {
+    const int row_first = it.q0 + t * kBM;
+    if (row_first >= p.Sq) {
+      it.n_tiles[t] = 0;
+    } else if (kCausal) {
+      const int row_last = min(row_first + kBM - 1, p.Sq - 1);
+      const int last_col = min(p.Sk - 1, row_last + p.causal_off);
+      it.n_tiles[t] = last_col >= 0 ? last_col / kBN + 1 : 0;
+    } else {
+      it.n_tiles[t] = (p.Sk + kBN - 1) / kBN;
+    }
+  }
+  it.n_max = max(it.n_tiles[0], it.n_tiles[1]);
+}
 
 }  // namespace
 
 template <int D, bool kBf16, bool kCausal, bool kFeat>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO1,
            const FwdKernelParams p) {
   using L = FwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -66,57 +106,36 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const uint32_t sQ = smem_base + L::kQOff;
+  const uint32_t sO = smem_base + L::kOOff;
   const uint32_t sKV = smem_base + L::kKVOff;
   const uint32_t bars = smem_base + L::kBarOff;
   auto bar_q_full = [&](int t) { return bars + 8u * t; };
-  auto bar_kv_full = [&](int s) { return bars + 8u * (2 + s); };
-  auto bar_kv_empty = [&](int s) { return bars + 8u * (2 + L::kStages + s); };
-  auto bar_s_full = [&](int t) { return bars + 8u * (2 + 2 * L::kStages + t); };
-  auto bar_p_full = [&](int t, int half) { return bars + 8u * (4 + 2 * L::kStages + kPSplit * t + half); };
-  auto bar_o_full = [&](int t) { return bars + 8u * (4 + 2 * L::kStages + 2 * kPSplit + t); };
+  auto bar_q_free = [&](int t) { return bars + 8u * (2 + t); };
+  auto bar_kv_full = [&](int s) { return bars + 8u * (4 + s); };
+  auto bar_kv_empty = [&](int s) { return bars + 8u * (4 + L::kStages + s); };
+  auto bar_s_full = [&](int t) { return bars + 8u * (4 + 2 * L::kStages + t); };
+  auto bar_p_full = [&](int t, int hh) { return bars + 8u * (6 + 2 * L::kStages + kPSplit * t + hh); };
+  auto bar_o_full = [&](int t) { return bars + 8u * (6 + 2 * L::kStages + 2 * kPSplit + t); };
+  auto bar_o_free = [&](int t) { return bars + 8u * (8 + 2 * L::kStages + 2 * kPSplit + t); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  const int total_items = p.n_qblk * p.B * p.Hq;
   if (tid == 0) FA2_TF(32, 0);
-
-  // ---- work item ----------------------------------------------------------------------------
-  const int nbh = p.B * p.Hq;
-  const int qb_rank = blockIdx.x / nbh;
-  const int bh = blockIdx.x - qb_rank * nbh;
-  // causal: the longest blocks are scheduled first
-  const int qblk = kCausal ? (p.n_qblk - 1 - qb_rank) : qb_rank;
-  const int b = bh / p.Hq;
-  const int h = bh - b * p.Hq;
-  const int hk = h / p.G;
-  const int q0 = qblk * (kBM * kTilesPerCta);
-
-  int n_tiles[kTilesPerCta];
-#pragma unroll
-  for (int t = 0; t < kTilesPerCta; ++t) {
-    const int row_first = q0 + t * kBM;
-    if (row_first >= p.Sq) {
-      n_tiles[t] = 0;
-    } else if (kCausal) {
-      const int row_last = min(row_first + kBM - 1, p.Sq - 1);
-      const int last_col = min(p.Sk - 1, row_last + p.causal_off);
-      n_tiles[t] = last_col >= 0 ? last_col / kBN + 1 : 0;
-    } else {
-      n_tiles[t] = (p.Sk + kBN - 1) / kBN;
-    }
-  }
-  const int n_max = max(n_tiles[0], n_tiles[1]);
 
   // ---- set-up ---------------------------------------------------------------------------------
   if (tid == 0) {
     *abort_flag = 0;
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_q_full(t), 1);
+      mbar_init(bar_q_free(t), 1);
       mbar_init(bar_s_full(t), 1);
       for (int hh = 0; hh < kPSplit; ++hh) mbar_init(bar_p_full(t, hh), kBM);
       mbar_init(bar_o_full(t), 1);
+      mbar_init(bar_o_free(t), kBM);
     }
     for (int s = 0; s < L::kStages; ++s) {
       mbar_init(bar_kv_full(s), 1);
@@ -128,7 +147,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
-    tma_prefetch_desc(&tmO);
+    tma_prefetch_desc(&tmO1);
   }
   if (warp == 0) {
     __syncwarp();
@@ -140,7 +159,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const uint32_t tmem_base = *tmem_slot;
   constexpr uint32_t kColS = 0, kColO = 256;
 
-
   if (warp >= 8) {
     // One warpgroup, one instruction: all four warps release their registers here.
     setmaxnreg_dec<kRegsOther>();
@@ -150,32 +168,39 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   } else if (warp == 9) {
     // =========================== TMA producer ================================================
     if (lane == 0) {
-#pragma unroll
-      for (int t = 0; t < kTilesPerCta; ++t) {
-        mbar_arrive_expect_tx(bar_q_full(t), L::kQTileBytes);
-        tma_load_5d(sQ + t * L::kQTileBytes, &tmQ, bar_q_full(t), 0, q0 + t * kBM, 0, h, b);
-      }
       bool ok = true;
-      for (int i = 0; i < 2 * n_max && ok; ++i) {
-        const int slot = i % L::kStages;
-        const uint32_t round = static_cast<uint32_t>(i / L::kStages);
-        ok = mbar_wait(bar_kv_empty(slot), (round & 1u) ^ 1u, abort_flag);
-        if (!ok) break;
-        const int j = i >> 1;
-        mbar_arrive_expect_tx(bar_kv_full(slot), L::kKVTileBytes);
-        tma_load_5d(sKV + slot * L::kKVTileBytes, (i & 1) ? &tmV : &tmK, bar_kv_full(slot), 0,
-                    j * kBN, 0, hk, b);
+      uint32_t kv_count = 0;     // K/V tiles loaded so far (over all items)
+      uint32_t item_idx = 0;
+      for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x, ++item_idx) {
+        FwdItem it;
+        decode_item<kCausal>(p, w, it);
+#pragma unroll
+        for (int t = 0; t < kTilesPerCta; ++t) {
+          // the last S MMA of the previous item that read this Q tile has completed
+          ok = ok && mbar_wait(bar_q_free(t), (item_idx & 1u) ^ 1u, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_q_full(t), L::kQTileBytes);
+          tma_load_5d(sQ + t * L::kQTileBytes, &tmQ, bar_q_full(t), 0, it.q0 + t * kBM, 0, it.h, it.b);
+        }
+        for (int i = 0; i < 2 * it.n_max && ok; ++i, ++kv_count) {
+          const int slot = kv_count % L::kStages;
+          const uint32_t round = kv_count / L::kStages;
+          ok = mbar_wait(bar_kv_empty(slot), (round & 1u) ^ 1u, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_kv_full(slot), L::kKVTileBytes);
+          tma_load_5d(sKV + slot * L::kKVTileBytes, (i & 1) ? &tmV : &tmK, bar_kv_full(slot), 0,
+                      (i >> 1) * kBN, 0, it.hk, it.b);
+        }
       }
       if (!ok) atomicOr(p.status, 1);
     }
     __syncwarp();
   } else if (warp == 8) {
     // =========================== MMA issuer ==================================================
-    if (lane == 0) {
+    if (true) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, kBM, kBN, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, kBM, D, false, true);
       bool ok = true;
-
       // Descriptors are built once; each MMA adds a constant to the start address.
       const uint64_t dQ0 = make_sdesc(sQ, 16, 1024);
       const uint64_t dKV_k0 = make_sdesc(sKV, 16, 1024);                 // K tile, K-major
@@ -186,66 +211,106 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
-          mma_ss(tmem_base + kColS + t * kBN, sdesc_advance(a0, off), sdesc_advance(b0, off), idesc_s,
+          mma_ss_e(tmem_base + kColS + t * kBN, sdesc_advance(a0, off), sdesc_advance(b0, off), idesc_s,
                  k > 0 ? 1u : 0u);
         }
-        mma_commit(bar_s_full(t));
+        mma_commit_e(bar_s_full(t));
       };
-      auto issue_o = [&](int t, int slot, bool first, int half) {
+      auto issue_o = [&](int t, int slot, bool first, int hh) {
         const uint64_t b0 = sdesc_advance(dKV_mn0, slot * L::kKVTileBytes);
 #pragma unroll
-        for (int k = half * (kPCols / 16); k < (half + 1) * (kPCols / 16); ++k) {
-          mma_ts(tmem_base + kColO + t * D, tmem_base + kColS + t * kBN + k * 8,
+        for (int k = hh * (kPCols / 16); k < (hh + 1) * (kPCols / 16); ++k) {
+          mma_ts_e(tmem_base + kColO + t * D, tmem_base + kColS + t * kBN + k * 8,
                  sdesc_advance(b0, k * 2048), idesc_o, (first && k == 0) ? 0u : 1u);
         }
       };
 
-      if (n_max > 0) {
-        for (int t = 0; t < kTilesPerCta && ok; ++t)
-          if (n_tiles[t] > 0) ok = mbar_wait(bar_q_full(t), 0, abort_flag);
-        if (ok) ok = mbar_wait(bar_kv_full(0), 0, abort_flag);
-        if (ok) {
+      uint32_t kv_count = 0;                 // K/V tiles consumed so far (over all items)
+      uint32_t it_cnt[kTilesPerCta] = {0, 0};   // tile-iterations so far: phase of s_full / p_full
+      uint32_t item_idx = 0;
+      for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x, ++item_idx) {
+        FwdItem it;
+        decode_item<kCausal>(p, w, it);
+        FA2_TF(34, item_idx);
+        // Q tiles of this item have landed (also for tiles without work: their buffer is handed
+        // back at once so that the producer's next load into it is ordered after this one)
+#pragma unroll
+        for (int t = 0; t < kTilesPerCta; ++t) {
+          ok = ok && mbar_wait_warp(bar_q_full(t), item_idx & 1u, abort_flag);
+          if (ok && it.n_tiles[t] == 0) {
+            mma_commit_e(bar_q_free(t));
+            // Keep the o_free / o_full hand-shake in step for tiles without work, so that neither
+            // side ever gets two phases ahead of the other.
+            ok = mbar_wait_warp(bar_o_free(t), (item_idx & 1u) ^ 1u, abort_flag);
+            if (ok) mma_commit_e(bar_o_full(t));
+          }
+        }
+        if (!ok || it.n_max == 0) continue;
+        FA2_TF(35, item_idx);
+        {
+          const int slot = kv_count % L::kStages;
+          ok = mbar_wait_warp(bar_kv_full(slot), (kv_count / L::kStages) & 1u, abort_flag);
+          if (!ok) break;
+          FA2_TF(36, item_idx);
           tc_fence_after();
 #pragma unroll
-          for (int t = 0; t < kTilesPerCta; ++t)
-            if (n_tiles[t] > 0) issue_s(t, 0);
-          mma_commit(bar_kv_empty(0));
+          for (int t = 0; t < kTilesPerCta; ++t) {
+            if (it.n_tiles[t] > 0) {
+              issue_s(t, slot);
+              if (it.n_tiles[t] == 1) mma_commit_e(bar_q_free(t));   // that was the last S of tile t
+            }
+          }
+          mma_commit_e(bar_kv_empty(slot));
+          ++kv_count;
         }
-        for (int j = 0; j < n_max && ok; ++j) {
-          const int iv = 2 * j + 1, ik = 2 * j + 2;
-          const int slot_v = iv % L::kStages, slot_k = ik % L::kStages;
-          ok = mbar_wait(bar_kv_full(slot_v), (iv / L::kStages) & 1, abort_flag);
+        for (int j = 0; j < it.n_max && ok; ++j) {
+          const bool has_next = (j + 1 < it.n_max);
+          const int slot_v = kv_count % L::kStages;
+          const int slot_k = (kv_count + 1) % L::kStages;
+          ok = mbar_wait_warp(bar_kv_full(slot_v), (kv_count / L::kStages) & 1u, abort_flag);
           if (!ok) break;
-          const bool has_next = (j + 1 < n_max);
           if (has_next) {
-            ok = mbar_wait(bar_kv_full(slot_k), (ik / L::kStages) & 1, abort_flag);
+            ok = mbar_wait_warp(bar_kv_full(slot_k), ((kv_count + 1) / L::kStages) & 1u, abort_flag);
             if (!ok) break;
           }
+          FA2_TF(43, it_cnt[1]);
 #pragma unroll
           for (int t = 0; t < kTilesPerCta; ++t) {
-            if (j < n_tiles[t]) {
+            if (j < it.n_tiles[t]) {
+              if (j == 0) {
+                // the epilogue of the previous item has read O_t out of tensor memory
+                ok = mbar_wait_warp(bar_o_free(t), (item_idx & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+              }
 #pragma unroll
               for (int hh = 0; hh < kPSplit; ++hh) {
-                ok = mbar_wait(bar_p_full(t, hh), j & 1, abort_flag);
+                ok = mbar_wait_warp(bar_p_full(t, hh), it_cnt[t] & 1u, abort_flag);
                 if (!ok) break;
-                if (hh == 0) FA2_TF(t, j);
+                if (hh == 0) FA2_TF(t, it_cnt[t]);
+                if (hh == kPSplit - 1) FA2_TF(44 + t, it_cnt[t]);
                 tc_fence_after();
                 issue_o(t, slot_v, j == 0, hh);
+                if (hh == 0) FA2_TF(48 + t, it_cnt[t]);
               }
               if (!ok) break;
-              if (j + 1 < n_tiles[t]) {
+              FA2_TF(50 + t, it_cnt[t]);
+              ++it_cnt[t];
+              if (j + 1 < it.n_tiles[t]) {
                 issue_s(t, slot_k);
+                FA2_TF(46 + t, it_cnt[t] - 1);
+                if (j + 2 == it.n_tiles[t]) mma_commit_e(bar_q_free(t));   // last S of tile t issued
               } else {
-                mma_commit(bar_o_full(t));
+                mma_commit_e(bar_o_full(t));
               }
             }
           }
           if (!ok) break;
-          mma_commit(bar_kv_empty(slot_v));
-          if (has_next) mma_commit(bar_kv_empty(slot_k));
+          mma_commit_e(bar_kv_empty(slot_v));
+          if (has_next) mma_commit_e(bar_kv_empty(slot_k));
+          kv_count += has_next ? 2 : 1;
         }
       }
-      if (!ok) atomicOr(p.status, 2);
+      if (!ok && lane == 0) atomicOr(p.status, 2);
     }
     __syncwarp();
   } else if (warp < 8) {
@@ -253,45 +318,80 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     setmaxnreg_inc<kRegsSoftmax>();
     const int t = warp >> 2;                   // query tile of this warpgroup
     const int r = tid & (kBM - 1);             // row inside the tile == TMEM lane
-    const int qi = q0 + t * kBM + r;           // global query row
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + kColS + t * kBN;
     const uint32_t tO = tmem_base + lane_base + kColO + t * D;
-    const int nt = n_tiles[t];
-    const bool tile_valid = (q0 + t * kBM) < p.Sq;
-    // last visible key of this row
-    const int row_lim = kCausal ? min(p.Sk - 1, qi + p.causal_off) : p.Sk - 1;
     const float sc = kFeat ? 1.0f : p.scale_log2;   // multiplies the values held in x[]
-
-    float m = -INFINITY;   // running (possibly stale) row maximum, in the units of x[]
-    float l = 0.f;         // running row sum of exp2(x*sc - m*sc)
+    uint32_t it_cnt = 0;       // tile-iterations so far: phase of s_full / p_full
+    uint32_t o_cnt = 0;        // items so far: phase of o_full
     bool ok = true;
 
-    for (int j = 0; j < nt; ++j) {
-      ok = mbar_wait(bar_s_full(t), j & 1, abort_flag);
-      if (!ok) break;
-      if (lane == 0) FA2_TF(8 + warp, j);
-      softmax_tile_row<D, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
-                                        [&](int half) { mbar_arrive(bar_p_full(t, half)); });
-      if (lane == 0) FA2_TF(16 + warp, j);
-    }
-    if (lane == 0) FA2_TF(24 + warp, 0);
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
+      FwdItem it;
+      decode_item<kCausal>(p, w, it);
+      const int b = it.b, h = it.h;
+      const int qi = it.q0 + t * kBM + r;      // global query row
+      const int nt = it.n_tiles[t];
+      const bool tile_valid = (it.q0 + t * kBM) < p.Sq;
+      // last visible key of this row
+      const int row_lim = kCausal ? min(p.Sk - 1, qi + p.causal_off) : p.Sk - 1;
+      float m = -INFINITY;   // running (possibly stale) row maximum, in the units of x[]
+      float l = 0.f;         // running row sum of exp2(x*sc - m*sc)
 
-    // ---- epilogue: O / l -> 16 bit -> swizzled shared memory -> TMA store; LSE ---------------
-    if (ok && tile_valid) {
-      ok = mbar_wait(bar_q_full(t), 0, abort_flag);   // Q tile landed: its slot is reused below
-      if (ok && nt > 0) ok = mbar_wait(bar_o_full(t), 0, abort_flag);
+      for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
+        ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
+        if (!ok) break;
+        if (lane == 0) FA2_TF(8 + warp, it_cnt);
+        softmax_tile_row<D, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
+                                          [&](int hh) { mbar_arrive(bar_p_full(t, hh)); });
+        if (lane == 0) FA2_TF(16 + warp, it_cnt);
+      }
+
+      // ---- epilogue: O / l -> 16 bit -> swizzled shared memory -> TMA store; LSE -------------
+      if (tid == 0) FA2_TF(37, o_cnt);
+      if (tid == 128) FA2_TF(40, o_cnt);
+      if (ok) ok = mbar_wait(bar_o_full(t), o_cnt & 1u, abort_flag);   // once per item, work or not
+      if (tid == 0) FA2_TF(38, o_cnt);
+      if (tid == 128) FA2_TF(41, o_cnt);
+      ++o_cnt;
+      // One 64-column block at a time through this tile's 16 KiB staging block. O_t is handed
+      // back to the MMA warp as soon as its last columns have been read out of tensor memory.
+      const float inv = (ok && tile_valid) ? epilogue_stats<kFeat>(p, b, h, qi, sc, m, l) : 0.f;
+      uint8_t* stage_gen = smem_gen + L::kOOff + t * L::kBlockBytes;
+      tc_fence_after();
+#pragma unroll
+      for (int blk = 0; blk < D / 64; ++blk) {
+        // the previous TMA store out of the staging block has finished reading it
+        if (r == 0) tma_store_wait_read0();
+        named_bar_sync(1 + t, kBM);
+        uint32_t o[64];
+        if (nt > 0) {
+          tmem_ld32(tO + blk * 64, reinterpret_cast<uint32_t(&)[32]>(o[0]));
+          tmem_ld32(tO + blk * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(o[32]));
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) o[c] = 0u;
+        }
+        if (blk == D / 64 - 1) {
+          tc_fence_before();
+          mbar_arrive(bar_o_free(t));
+        }
+        if (ok && tile_valid) {
+          epilogue_block<kBf16>(o, stage_gen, r, inv);
+          fence_proxy_async_smem();
+        }
+        named_bar_sync(1 + t, kBM);
+        if (ok && tile_valid && r == 0 && !*abort_flag) {
+          tma_store_5d(&tmO1, sO + t * L::kBlockBytes, 0, it.q0 + t * kBM, blk, h, b);
+          tma_store_commit();
+        }
+      }
+      if (tid == 0) FA2_TF(39, o_cnt - 1);
+      if (tid == 128) FA2_TF(42, o_cnt - 1);
+      if (!ok) break;
     }
-    if (ok && tile_valid) {
-      epilogue_row<D, kBf16, kFeat>(tO, nt > 0, smem_gen + L::kQOff + t * L::kQTileBytes, r, p, b, h, qi, sc, m, l);
-    }
-    // All 128 threads of the warpgroup reach this barrier, whatever happened above.
-    named_bar_sync(1 + t, kBM);
-    if (ok && tile_valid && r == 0 && !*abort_flag) {
-      tma_store_5d(&tmO, sQ + t * L::kQTileBytes, 0, q0 + t * kBM, 0, h, b);
-      tma_store_commit();
-      tma_store_wait_read0();
-    }
+    if (r == 0) tma_store_wait_read0();
     if (!ok && r == 0) atomicOr(p.status, 4);
   }
 
@@ -308,6 +408,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 // ---------------------------------------------------------------------------------------------
 // launcher
 // ---------------------------------------------------------------------------------------------
+static int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <int D, bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch_one(const FwdLaunch& a, cudaStream_t stream) {
   using L = FwdSmem<D>;
@@ -315,11 +427,10 @@ static cudaError_t launch_one(const FwdLaunch& a, cudaStream_t stream) {
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   if (e != cudaSuccess) return e;
-  const long long nblocks =
-      static_cast<long long>(a.kp.n_qblk) * a.kp.B * a.kp.Hq;
-  if (nblocks <= 0) return cudaSuccess;
-  kern<<<static_cast<unsigned>(nblocks), kThreads, L::kDynamicBytes, stream>>>(a.tmQ, a.tmK, a.tmV,
-                                                                               a.tmO, a.kp);
+  const long long items = static_cast<long long>(a.kp.n_qblk) * a.kp.B * a.kp.Hq;
+  if (items <= 0) return cudaSuccess;
+  const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
+  kern<<<grid, kThreads, L::kDynamicBytes, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmO1, a.kp);
   return cudaGetLastError();
 }
 
