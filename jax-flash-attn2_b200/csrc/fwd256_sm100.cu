@@ -205,7 +205,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         tc_fence_after();
       };
       softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv,
-                                         [&](int half) { mbar_arrive(bar_p_full(buf, half)); });
+                                         [&](int half) { return mbar_arrive_zero(bar_p_full(buf, half)); });
       if (!ok) break;
     }
 

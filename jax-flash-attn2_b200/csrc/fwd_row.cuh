@@ -82,7 +82,7 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 // `before_o_rescale()` is called (by the whole warp) just before O is touched, so that a kernel
 // whose P.V MMA may still be running can wait for it there.
 // `after_half(h)` is called after piece h (keys [kPCols h, kPCols (h+1))) of P has been stored and
-// fenced: the caller signals the MMA warp there.
+// fenced: the caller signals the MMA warp there (mbar_arrive_zero) and returns that call's value.
 template <int D, bool kBf16, bool kFeat, class BeforeRescale, class AfterHalf>
 __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j, bool have_o,
                                                  const FwdKernelParams& p, int b, int h, int qi,
@@ -145,7 +145,7 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
     }
   }
   const float m_use = (m == -INFINITY) ? 0.f : m;
-  const float neg_ms = -m_use * sc;
+  float neg_ms = -m_use * sc;
   // P is produced and handed over in two halves of 64 keys: the P.V MMAs of the first half run
   // while the exponentials of the second half are still being computed.
   float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
@@ -196,7 +196,10 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
     }
     tc_wait_st();
     tc_fence_before();
-    after_half(half);
+    // `after_half` arrives on the barrier and returns a zero the compiler cannot see through;
+    // folding it into the next piece's FMA offset keeps the assembler from scheduling that
+    // piece's exponentials ahead of this hand-over.
+    neg_ms += after_half(half);
   }
   l += (l0 + l1) + (l2 + l3);
 }

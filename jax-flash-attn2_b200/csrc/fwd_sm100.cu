@@ -29,7 +29,7 @@ namespace {
 
 #ifdef FA2_TRACE
 // Development aid (not compiled by default): per-role time stamps of one CTA.
-__device__ long long g_trace_fwd[56 * 1024];
+__device__ long long g_trace_fwd[64 * 1024];
 #define FA2_TF(role, idx) do { if (blockIdx.x == FA2_TRACE_CTA && (idx) < 1024) g_trace_fwd[(role) * 1024 + (idx)] = clock64(); } while (0)
 #else
 #define FA2_TF(role, idx) do { } while (0)
@@ -343,7 +343,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (!ok) break;
         if (lane == 0) FA2_TF(8 + warp, it_cnt);
         softmax_tile_row<D, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
-                                          [&](int hh) { mbar_arrive(bar_p_full(t, hh)); });
+                                          [&](int hh) {
+                                            if (hh == 0 && lane == 0) FA2_TF(52 + warp, it_cnt);
+                                            return mbar_arrive_zero(bar_p_full(t, hh));
+                                          });
         if (lane == 0) FA2_TF(16 + warp, it_cnt);
       }
 
