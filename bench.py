@@ -316,25 +316,54 @@ def main():
     ms_main = max_over_ranks(statistics.mean(main_ms))
 
     # ---- end to end: host buffers in, host buffers out, every step -----------------------------
+    # Every step copies its inputs from pinned host memory and its results (o, dq, dk, dv) back to
+    # pinned host memory inside the timed region. The three stages run on three streams over two
+    # sets of device input buffers, so that step i+1's upload and step i-1's download overlap step
+    # i's kernels (PCIe is full duplex); nothing is skipped or cached.
     ho = torch.empty_like(hq).pin_memory()
     hdq = torch.empty_like(hq).pin_memory()
     hdk = torch.empty_like(hk).pin_memory()
     hdv = torch.empty_like(hv).pin_memory()
-    dq_, dk_, dv_ = (torch.empty_like(x) for x in (q, k, v))
-    def e2e_step():
-        q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True)
-        v.copy_(hv, non_blocking=True); do.copy_(hdo, non_blocking=True)
-        o_, lse_ = fwd()
-        g_ = bwd(o_, lse_)
-        ho.copy_(o_, non_blocking=True); hdq.copy_(g_[0], non_blocking=True)
-        hdk.copy_(g_[1], non_blocking=True); hdv.copy_(g_[2], non_blocking=True)
+    in_sets = [(q, k, v, do), tuple(torch.empty_like(x) for x in (q, k, v, do))]
+    s_in, s_comp, s_out = (torch.cuda.Stream() for _ in range(3))
+    def e2e_run(n_steps):
+        ev_in = [None, None]
+        ev_free = [None, None]      # compute of the step that last used input set b has finished
+        ev_out = None
+        keep = []
+        for i in range(n_steps):
+            bset = i & 1
+            dq_, dk_, dv_, ddo_ = in_sets[bset]
+            with torch.cuda.stream(s_in):
+                if ev_free[bset] is not None:
+                    s_in.wait_event(ev_free[bset])
+                dq_.copy_(hq, non_blocking=True); dk_.copy_(hk, non_blocking=True)
+                dv_.copy_(hv, non_blocking=True); ddo_.copy_(hdo, non_blocking=True)
+                ev_in[bset] = torch.cuda.Event(); ev_in[bset].record(s_in)
+            with torch.cuda.stream(s_comp):
+                s_comp.wait_event(ev_in[bset])
+                o_, lse_ = J.fwd_attention_kernel_call(dq_, dk_, dv_, mask, bias, None, p_drop, causal, seed)
+                g_ = J.bwd_attention_kernel_call(ddo_, dq_, dk_, dv_, bias, mask, o_, lse_, p_drop, causal, None, seed)
+                ev_free[bset] = torch.cuda.Event(); ev_free[bset].record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_free[bset])
+                for t_ in (o_, *g_):
+                    t_.record_stream(s_out)
+                ho.copy_(o_, non_blocking=True); hdq.copy_(g_[0], non_blocking=True)
+                hdk.copy_(g_[1], non_blocking=True); hdv.copy_(g_[2], non_blocking=True)
+            keep.append((o_, lse_, g_))
+            if len(keep) > 2:
+                keep.pop(0)
+        for st_ in (s_in, s_comp, s_out):
+            torch.cuda.current_stream().wait_stream(st_)
     e2e_steps = max(3, min(args.steps, 10))
-    e2e_step()
+    e2e_run(2)
     barrier()
     e0, e1 = ev(), ev()
     e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    for st_ in (s_in, s_comp, s_out):
+        st_.wait_event(e0)
+    e2e_run(e2e_steps)
     e1.record()
     barrier()
     ms_e2e = max_over_ranks(e0.elapsed_time(e1) / e2e_steps)
