@@ -26,6 +26,11 @@ constexpr int kPolyPer8 = FA2_FWD_POLY_PER8;
 #define FA2_FWD_P_SPLIT 2
 #endif
 constexpr int kPSplit = FA2_FWD_P_SPLIT;
+// 1: the next piece's arithmetic is made to depend on the hand-over arrive (strict ordering);
+// 0: the assembler may overlap it with the hand-over.
+#ifndef FA2_FWD_ORDERED_HANDOVER
+#define FA2_FWD_ORDERED_HANDOVER 0
+#endif
 constexpr int kPCols = kBN / kPSplit;   // keys per piece
 
 template <bool kBf16>
@@ -199,7 +204,11 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
     // `after_half` arrives on the barrier and returns a zero the compiler cannot see through;
     // folding it into the next piece's FMA offset keeps the assembler from scheduling that
     // piece's exponentials ahead of this hand-over.
+#if FA2_FWD_ORDERED_HANDOVER
     neg_ms += after_half(half);
+#else
+    (void)after_half(half);
+#endif
   }
   l += (l0 + l1) + (l2 + l3);
 }
