@@ -27,11 +27,29 @@ namespace fa2 {
 namespace {
 
 constexpr int kBN = 128;   // keys per CTA
-constexpr int kThreads = 512;
-// Registers per thread after setmaxnreg: each scheduler holds 2 P/dS warps, 1 drain warp and 1
-// warp of the last warpgroup; 2 * 128 + 152 + 104 = 4 * 128 (the launch allocation).
-constexpr int kRegsDrain = 152;
-constexpr int kRegsOther = 104;
+// Warpgroups that compute P and dS: each owns 128 / kPW query columns of every step, and they come
+// first in the block, followed by the dQ drain warpgroup and the MMA / TMA warpgroup. The kernel
+// is bound by shared-memory bandwidth at D = 128 (the operands of the 128x128x16 MMAs alone take
+// all of it), where two warpgroups measured a little faster than four; at D = 64 the element-wise
+// phases weigh more and four warpgroups hide more of their latencies.
+// Registers per thread after setmaxnreg (the pool is the launch allocation):
+//   kPW = 2: launch 128: 2 * 128 + 152 + 104 = 4 * 128
+//   kPW = 4: launch  80, nobody trades: the MMA / TMA warps spill below 80 and the drain, which
+//            then takes a D = 128 tile in two halves, fits in 80
+template <int D>
+struct BwdRoles {
+#ifdef FA2_BWD_PWG
+  static constexpr int kPW = FA2_BWD_PWG;
+#else
+  static constexpr int kPW = (D == 64) ? 4 : 2;
+#endif
+  static_assert(kPW == 2 || kPW == 4, "2 or 4 P/dS warpgroups");
+  static constexpr int kCW = 128 / kPW;                 // query columns per P/dS warpgroup
+  static constexpr int kThreads = (kPW + 2) * 128;
+  static constexpr int kRegsDrain = kPW == 2 ? 152 : 80;
+  static constexpr int kRegsOther = kPW == 2 ? 104 : 80;
+  static constexpr int kWarpDrain = 4 * kPW, kWarpMma = 4 * kPW + 4, kWarpTma = 4 * kPW + 5;
+};
 
 template <int D>
 struct BwdSmem {
@@ -53,6 +71,9 @@ struct BwdSmem {
   static constexpr int kDynamicBytes = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
   static_assert(kTotal <= kMaxDynSmem, "shared memory budget exceeded");
 };
+
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&x)[32]) { tmem_st32(taddr, x); }
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&x)[16]) { tmem_st16(taddr, x); }
 
 #ifdef FA2_TRACE
 // Development aid (not compiled by default): per-role time stamps of CTA 0.
@@ -115,12 +136,15 @@ bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long
 // 2. main kernel
 // ---------------------------------------------------------------------------------------------
 template <int D, bool kBf16, bool kCausal, bool kFeat>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(BwdRoles<D>::kThreads, 1)
 bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
                 const float* __restrict__ stats, const BwdKernelParams p) {
   using L = BwdSmem<D>;
+  using R = BwdRoles<D>;
+  constexpr int kPW = R::kPW, kCW = R::kCW;
+  constexpr int kWarpDrain = R::kWarpDrain, kWarpMma = R::kWarpMma, kWarpTma = R::kWarpTma;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t pad = smem_base - smem_u32(smem_raw);
@@ -174,15 +198,15 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar_do_full, 1);
     mbar_init(bar_do_empty, 1);
     mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, 256);
+    mbar_init(bar_p_full, 128 * kPW);
     mbar_init(bar_dp_full, 1);
-    mbar_init(bar_ds_full, 256);
+    mbar_init(bar_ds_full, 128 * kPW);
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_drained, 128);
     mbar_init(bar_dkv_full, 1);
     fence_mbar_init();
   }
-  if (warp == 13 && lane == 0) {
+  if (warp == kWarpTma && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -205,10 +229,12 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     h = hk * p.G + g;
   };
 
-  if (warp >= 12) setmaxnreg_dec<kRegsOther>();   // one site for the whole warpgroup
-  if (warp >= 14) {
+  if constexpr (kPW == 2) {
+    if (warp >= kWarpMma) setmaxnreg_dec<R::kRegsOther>();   // one site for the whole warpgroup
+  }
+  if (warp >= kWarpTma + 1) {
     // idle: these two warps only complete the warpgroup that gives up registers
-  } else if (warp == 13) {
+  } else if (warp == kWarpTma) {
     // =========================== TMA producer ================================================
     if (lane == 0 && T > 0) {
       mbar_arrive_expect_tx(bar_kv_full, 2 * L::kTileBytes);
@@ -235,7 +261,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) atomicOr(p.status, 8);
     }
     __syncwarp();
-  } else if (warp == 12) {
+  } else if (warp == kWarpMma) {
     // =========================== MMA issuer ==================================================
     if (true && T > 0) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, 128, 128, false, false);
@@ -265,9 +291,9 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto issue_dv = [&](bool first) {
 #pragma unroll
         for (int k = 0; k < kBM / 16; ++k) {
-          // P^T for queries [16k, 16k+16): 8 packed columns; the two 64-query halves were written
-          // by different warpgroups at columns 0 and 64 of the S region.
-          const uint32_t a_col = kColS + (k < 4 ? 8 * k : 64 + 8 * (k - 4));
+          // P^T for queries [16k, 16k+16): 8 packed columns; every P/dS warpgroup wrote its kCW
+          // queries at the start of the S columns it had read (column kCW * g).
+          const uint32_t a_col = kColS + kCW * (k / (kCW / 16)) + 8 * (k % (kCW / 16));
           mma_ts_e(tmem_base + kColdV, tmem_base + a_col, sdesc_advance(ddO_mn, k * 2048), idesc_dv,
                  (first && k == 0) ? 0u : 1u);
         }
@@ -346,10 +372,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok && lane == 0) atomicOr(p.status, 16);
     }
     __syncwarp();
-  } else if (warp >= 8) {
+  } else if (warp >= kWarpDrain) {
     // =========================== dQ drain ====================================================
-    setmaxnreg_inc<kRegsDrain>();
-    const int r = tid - 256;   // query row inside the tile == TMEM lane
+    if constexpr (kPW == 2) setmaxnreg_inc<R::kRegsDrain>();
+    const int r = tid - 128 * kPW;   // query row inside the tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tdQ = tmem_base + lane_base + kColdQ;
     bool ok = true;
@@ -360,41 +386,50 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok) break;
       if (r == 0) FA2_T(5, it);
       tc_fence_after();
-      // Pull the whole tile into registers first so that the tensor-memory columns are handed
-      // back at once; the reductions (slow: they queue in the memory pipe) then overlap with the
-      // MMAs of the next step.
-      uint32_t v[D];
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c)
-        tmem_ld32(tdQ + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
-      tc_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar_dq_drained);
-      if (r == 0) FA2_T(6, it);
-      // Hand the tile to the TMA unit in four chunks of D/4 columns through two staging
-      // buffers: cp.reduce.async.bulk adds each chunk to the global fp32 accumulator while the
-      // next chunk is written. (Reductions issued from registers would queue in the memory
-      // pipe in front of the tensor-memory traffic of the other warps.)
+      // Pull the tile into registers first so that the tensor-memory columns are handed back
+      // early; the reductions (slow: they queue in the memory pipe) then overlap with the MMAs of
+      // the next step. With four P/dS warpgroups the register file only leaves room for half a
+      // D = 128 tile here, so the tile is taken in two parts and handed back after the second load.
+      // Each part leaves through the TMA unit in chunks of D/4 columns through two staging
+      // buffers: cp.reduce.async.bulk adds a chunk to the global fp32 accumulator while the next
+      // one is written. (Reductions issued from registers would queue in the memory pipe in front
+      // of the tensor-memory traffic of the other warps.)
+      constexpr int kParts = (kPW == 4 && D == 128) ? 2 : 1;
+      constexpr int kPartCols = D / kParts;
       float* dst_tile = p.dq_acc + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * (kBM * D);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int buf = c & 1;
-        // at most one reduction may still be reading: the one from the other buffer
-        if (r == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        named_bar_sync(3, 128);
-        uint8_t* stage = smem_gen + L::kStageOff + buf * L::kChunkBytes;
+      for (int part = 0; part < kParts; ++part) {
+        uint32_t v[kPartCols];
 #pragma unroll
-        for (int c4 = 0; c4 < D / 16; ++c4) {
-          const int cc = c * (D / 16) + c4;
-          *reinterpret_cast<uint4*>(stage + (c4 * 128 + r) * 16) =
-              make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
+        for (int c = 0; c < kPartCols / 32; ++c)
+          tmem_ld32(tdQ + part * kPartCols + c * 32, reinterpret_cast<uint32_t(&)[32]>(v[c * 32]));
+        tc_wait_ld();
+        if (part == kParts - 1) {
+          tc_fence_before();
+          mbar_arrive(bar_dq_drained);
+          if (r == 0) FA2_T(6, it);
         }
-        fence_proxy_async_smem();
-        named_bar_sync(3, 128);
-        if (r == 0) {
-          bulk_reduce_add_f32(dst_tile + c * (kBM * D / 4), smem_base + L::kStageOff + buf * L::kChunkBytes,
-                              L::kChunkBytes);
-          tma_store_commit();
+#pragma unroll
+        for (int cl = 0; cl < 4 / kParts; ++cl) {
+          const int c = part * (4 / kParts) + cl;
+          const int buf = c & 1;
+          // at most one reduction may still be reading: the one from the other buffer
+          if (r == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          named_bar_sync(3, 128);
+          uint8_t* stage = smem_gen + L::kStageOff + buf * L::kChunkBytes;
+#pragma unroll
+          for (int c4 = 0; c4 < D / 16; ++c4) {
+            const int cc = cl * (D / 16) + c4;
+            *reinterpret_cast<uint4*>(stage + (c4 * 128 + r) * 16) =
+                make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(3, 128);
+          if (r == 0) {
+            bulk_reduce_add_f32(dst_tile + c * (kBM * D / 4),
+                                smem_base + L::kStageOff + buf * L::kChunkBytes, L::kChunkBytes);
+            tma_store_commit();
+          }
         }
       }
     }
@@ -402,14 +437,16 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (!ok && r == 0) atomicOr(p.status, 32);
   } else {
     // =========================== P / dS warps + dK, dV epilogue ==============================
-    const int w = warp >> 2;            // 0: queries [0,64) of each tile, dK; 1: [64,128), dV
+    const int w = warp >> 2;            // warpgroup: queries [kCW*w, kCW*w + kCW) of each tile
     const int r = tid & 127;            // key row inside the tile == TMEM lane
     const int kv = n * kBN + r;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem_base + lane_base + kColS + 64 * w;
-    const uint32_t tdP = tmem_base + lane_base + kColdP + 64 * w;
+    const uint32_t tS = tmem_base + lane_base + kColS + kCW * w;
+    const uint32_t tdP = tmem_base + lane_base + kColdP + kCW * w;
     const float* stats_s = reinterpret_cast<const float*>(smem_gen + L::kStatsOff);
-    uint8_t* ds_row = smem_gen + L::kdSOff + w * L::kBlockBytes + r * 128;
+    // dS^T row r: queries [kCW*w, +kCW) are chunks [chunk0, chunk0 + kCW/8) of one 128-byte line
+    uint8_t* ds_row = smem_gen + L::kdSOff + ((kCW * w) >> 6) * L::kBlockBytes + r * 128;
+    const int chunk0 = ((kCW * w) & 63) >> 3;
     const float do_scale = kBf16 ? 1.f : do_scale_from_bits(p.do_absmax_bits);
     bool ok = true;
 
@@ -418,46 +455,46 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       int h, i;
       step_coords(it, h, i);
       // per query column of this warpgroup: -lse*log2(e) (or -inf) and delta
-      const float4* nlse4 = reinterpret_cast<const float4*>(stats_s + st * 256 + 64 * w);
+      const float4* nlse4 = reinterpret_cast<const float4*>(stats_s + st * 256 + kCW * w);
       const float4* delta4 = nlse4 + 32;
-      const int q_first = i * kBM + 64 * w;
+      const int q_first = i * kBM + kCW * w;
       ok = mbar_wait(bar_q_full(st), (it >> 1) & 1, abort_flag);
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
       if (tid == 0) FA2_T(7, it);
-      if (lane == 0) FA2_T(32 + warp, it);
+      if (lane == 0 && warp < 8) FA2_T(32 + warp, it);
       tc_fence_after();
       // some (query, key) pairs of this step are above the causal diagonal
       const bool diag = kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off);
       const int q_lim = kv - p.causal_off;     // masked iff query index < q_lim
 
-      // ---- P^T = exp2(S^T * scale*log2e - lse*log2e): 64 query columns of this key row -------
-      uint32_t pk[32];                          // P as 16-bit pairs; also the input of dS below
-      uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;
+      // ---- P^T = exp2(S^T * scale*log2e - lse*log2e): kCW query columns of this key row ------
+      uint32_t pk[kCW / 2];                     // P as 16-bit pairs; also the input of dS below
+      uint32_t keep[kCW / 32];
+#pragma unroll
+      for (int k = 0; k < kCW / 32; ++k) keep[k] = 0xffffffffu;
       {
-        uint32_t s[64];
-        tmem_ld32(tS, reinterpret_cast<uint32_t(&)[32]>(s[0]));
-        tmem_ld32(tS + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+        uint32_t s[kCW];
+#pragma unroll
+        for (int c = 0; c < kCW / 32; ++c)
+          tmem_ld32(tS + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
         tc_wait_ld();
         if (tid == 0) FA2_T(11, it);
         if constexpr (kFeat) {
           if (p.drop.enabled) {
             const uint32_t bh_glob =
                 static_cast<uint32_t>((p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
-            uint32_t bits[2];
-            dropout_keep_bits_transposed<64>(p.drop, bh_glob, kv, q_first, lane, bits);
-            keep_lo = bits[0];
-            keep_hi = bits[1];
+            dropout_keep_bits_transposed<kCW>(p.drop, bh_glob, kv, q_first, lane, keep);
           }
         }
         if constexpr (kFeat) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) s[c] = __float_as_uint(__uint_as_float(s[c]) * p.scale_log2);
-          add_term_column<kBf16, 64>(p.bias, b, h, q_first, kv, p.Sq, p.Sk, s);
-          add_term_column<kBf16, 64>(p.mask, b, h, q_first, kv, p.Sq, p.Sk, s);
+          for (int c = 0; c < kCW; ++c) s[c] = __float_as_uint(__uint_as_float(s[c]) * p.scale_log2);
+          add_term_column<kBf16, kCW>(p.bias, b, h, q_first, kv, p.Sq, p.Sk, s);
+          add_term_column<kBf16, kCW>(p.mask, b, h, q_first, kv, p.Sq, p.Sk, s);
         }
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
+        for (int c4 = 0; c4 < kCW / 4; ++c4) {
           const float4 nl = nlse4[c4];
           const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
 #pragma unroll
@@ -479,31 +516,32 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
+      auto store_p = [&](const uint32_t (&x)[kCW / 2]) { tmem_st_cols(tS, x); };
       if constexpr (kFeat) {
         if (p.drop.enabled) {
           // the weights that reach dV carry the dropout mask and its 1/(1-p)
-          uint32_t pd[32];
+          uint32_t pd[kCW / 2];
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const uint32_t bits = (c < 16) ? keep_lo : keep_hi;
+          for (int c = 0; c < kCW / 2; ++c) {
+            const uint32_t bits = keep[(2 * c) >> 5];
             const int sh = (2 * c) & 31;
             float a0 = ((bits >> sh) & 1u) ? unpack_lo<kBf16>(pk[c]) * p.drop.inv_keep : 0.f;
             float a1 = ((bits >> (sh + 1)) & 1u) ? unpack_hi<kBf16>(pk[c]) * p.drop.inv_keep : 0.f;
             pd[c] = pack2<kBf16>(a0, a1);
           }
-          tmem_st32(tS, pd);
+          store_p(pd);
         } else {
-          tmem_st32(tS, pk);
+          store_p(pk);
         }
       } else {
-        tmem_st32(tS, pk);
+        store_p(pk);
       }
       if (tid == 0) FA2_T(14, it);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);
       if (tid == 0) FA2_T(8, it);
-      if (lane == 0) FA2_T(16 + warp, it);
+      if (lane == 0 && warp < 8) FA2_T(16 + warp, it);
 
       // ---- dS^T = P^T * (dP^T * keep/(1-p) - delta) -> shared memory, 16 bit ------------------
       ok = mbar_wait(bar_dp_full, it & 1, abort_flag);
@@ -511,13 +549,14 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (tid == 0) FA2_T(9, it);
       tc_fence_after();
       {
-        uint32_t dp[64];
-        tmem_ld32(tdP, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
-        tmem_ld32(tdP + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+        uint32_t dp[kCW];
+#pragma unroll
+        for (int c = 0; c < kCW / 32; ++c)
+          tmem_ld32(tdP + 32 * c, reinterpret_cast<uint32_t(&)[32]>(dp[32 * c]));
         tc_wait_ld();
         if (tid == 0) FA2_T(12, it);
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
+        for (int c4 = 0; c4 < kCW / 4; ++c4) {
           const float4 dl = delta4[c4];
           const float dlv[4] = {dl.x, dl.y, dl.z, dl.w};
 #pragma unroll
@@ -525,7 +564,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int c = 4 * c4 + 2 * k2;
             float d0 = __uint_as_float(dp[c]), d1 = __uint_as_float(dp[c + 1]);
             if constexpr (kFeat) {
-              const uint32_t bits = (c < 32) ? keep_lo : keep_hi;
+              const uint32_t bits = keep[c >> 5];
               d0 = ((bits >> (c & 31)) & 1u) ? d0 * p.drop.inv_keep : 0.f;
               d1 = ((bits >> ((c + 1) & 31)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
             }
@@ -533,13 +572,12 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             add2(t0, t1, d0, d1, -dlv[2 * k2], -dlv[2 * k2 + 1]);
             if constexpr (!kBf16) fma2(t0, t1, t0, t1, do_scale, do_scale, 0.f, 0.f);
             const float p0 = unpack_lo<kBf16>(pk[c >> 1]), p1 = unpack_hi<kBf16>(pk[c >> 1]);
-            dp[c >> 1] = pack2<kBf16>(p0 * t0, p1 * t1);     // reuse dp[0..31] for the packed dS
+            dp[c >> 1] = pack2<kBf16>(p0 * t0, p1 * t1);     // reuse dp[0..kCW/2) for the packed dS
           }
         }
-        // dS^T row r, queries [64w, 64w + 64): the eight 16-byte chunks of one 128-byte line
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          *reinterpret_cast<uint4*>(ds_row + ((q4 ^ (r & 7)) << 4)) =
+        for (int q4 = 0; q4 < kCW / 8; ++q4) {
+          *reinterpret_cast<uint4*>(ds_row + (((chunk0 + q4) ^ (r & 7)) << 4)) =
               make_uint4(dp[4 * q4], dp[4 * q4 + 1], dp[4 * q4 + 2], dp[4 * q4 + 3]);
         }
       }
@@ -547,18 +585,23 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       fence_proxy_async_smem();
       mbar_arrive(bar_ds_full);
       if (tid == 0) FA2_T(10, it);
-      if (lane == 0) FA2_T(24 + warp, it);
+      if (lane == 0 && warp < 8) FA2_T(24 + warp, it);
     }
 
-    // ---- epilogue: warpgroup 0 writes dK (scaled), warpgroup 1 writes dV ---------------------
+    // ---- epilogue: the first half of the warpgroups writes dK (scaled), the second half dV ----
+    constexpr int kWgPerAcc = kPW / 2;                 // warpgroups that share one accumulator
+    constexpr int kUnits = D / 32 / kWgPerAcc;         // 32-column units per warpgroup
+    const int acc = w / kWgPerAcc;                     // 0: dK, 1: dV
+    const int part = w % kWgPerAcc;
     if (ok && T > 0) ok = mbar_wait(bar_dkv_full, 0, abort_flag);
     if (ok) {
       tc_fence_after();
-      const uint32_t tAcc = tmem_base + lane_base + (w == 0 ? kColdK : kColdV);
-      const float f = (w == 0) ? p.scale / do_scale : 1.f;
-      uint8_t* stage = smem_gen + L::kQOff + w * L::kTileBytes;   // both Q stages are free now
+      const uint32_t tAcc = tmem_base + lane_base + (acc == 0 ? kColdK : kColdV);
+      const float f = (acc == 0) ? p.scale / do_scale : 1.f;
+      uint8_t* stage = smem_gen + L::kQOff + acc * L::kTileBytes;   // both Q stages are free now
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cu = 0; cu < kUnits; ++cu) {
+        const int c = part * kUnits + cu;
         uint32_t a[32];
         if (T > 0) {
           tmem_ld32(tAcc + c * 32, a);
@@ -581,9 +624,9 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       fence_proxy_async_smem();
     }
-    named_bar_sync(1 + w, 128);
-    if (ok && r == 0 && !*abort_flag) {
-      tma_store_5d(w == 0 ? &tmdK : &tmdV, sQ + w * L::kTileBytes, 0, n * kBN, 0, hk, b);
+    named_bar_sync(1 + acc, 128 * kWgPerAcc);
+    if (ok && part == 0 && r == 0 && !*abort_flag) {
+      tma_store_5d(acc == 0 ? &tmdK : &tmdV, sQ + acc * L::kTileBytes, 0, n * kBN, 0, hk, b);
       tma_store_commit();
       tma_store_wait_read0();
     }
@@ -609,7 +652,7 @@ static cudaError_t launch_main(const BwdLaunch& a, cudaStream_t stream) {
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   if (e != cudaSuccess) return e;
   const long long nblocks = static_cast<long long>(a.kp.n_kvblk) * a.kp.B * a.kp.Hkv;
-  kern<<<static_cast<unsigned>(nblocks), kThreads, L::kDynamicBytes, stream>>>(
+  kern<<<static_cast<unsigned>(nblocks), BwdRoles<D>::kThreads, L::kDynamicBytes, stream>>>(
       a.tmQ, a.tmK, a.tmV, a.tmdO, a.tmdK, a.tmdV, a.delta, a.kp);
   return cudaGetLastError();
 }
