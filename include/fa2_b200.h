@@ -56,6 +56,9 @@ typedef struct {
 } fa2_score_term;
 
 typedef struct {
+  /* head_dim: any multiple of 8 up to 64, of 16 up to 128, of 32 up to 256. Head dims other than
+   * 64 / 128 / 256 run on the next larger kernel with zero-padded columns (the reference pads
+   * them too: PADDED_HEADS, _forward_triton.py:337-346); nothing is copied. */
   int32_t batch, seqlen_q, seqlen_k, heads_q, heads_kv, head_dim;
   int32_t dtype;              /* fa2_dtype of q, k, v, o, do, dq, dk, dv                     */
   int32_t causal;             /* bottom-right aligned when seqlen_q != seqlen_k              */
@@ -136,6 +139,7 @@ int fa2_debug_device_status(void* cuda_stream);
  *
  *  - Limit: fa2_bwd_workspace_bytes(problem) must not exceed FA2_BWD_STATIC_SCRATCH_BYTES,
  *    i.e. batch * heads_q * ceil(seqlen_q / 128) * 128 * (head_dim + 2) * 4 bytes <= 32 MiB
+ *    with head_dim rounded up to 64, 128 or 256
  *    (for head_dim 128: 64512 query rows over all batches and heads). Larger problems are
  *    refused with FA2_ERR_WORKSPACE and a message; nothing is launched.
  *  - The call allocates and frees nothing (no cudaMalloc / cudaFree, no allocating library

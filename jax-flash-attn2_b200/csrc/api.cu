@@ -58,12 +58,34 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// The kernels exist for head dims 64, 128 and 256 (1, 2 and 4 blocks of 64 columns). Any other
+// head dim is cut into the same number of equal blocks of D / nblk columns, each padded with zeros
+// to 64: the tensor maps below give the first dimension the extent D / nblk while the box stays 64
+// wide, so the TMA unit zero-fills the padding on loads and clips it on stores. Every operand is
+// cut the same way, so the dot products over the head dim are unchanged, and outputs leave through
+// the same kind of map, which puts their columns back in place. The block stride must be a multiple
+// of 16 bytes, hence D % 8 == 0 up to 64, D % 16 == 0 up to 128, D % 32 == 0 up to 256.
+struct HeadDim {
+  int padded;   // 64, 128 or 256: selects the kernel
+  int nblk;     // padded / 64
+  int blk;      // real columns per block (64 when the head dim is one the kernels are built for)
+};
+bool split_head_dim(int D, HeadDim* hd) {
+  if (D <= 0 || D > 256) return false;
+  hd->padded = D <= 64 ? 64 : D <= 128 ? 128 : 256;
+  hd->nblk = hd->padded / 64;
+  if (D % (8 * hd->nblk) != 0) return false;
+  hd->blk = D / hd->nblk;
+  return true;
+}
+
 // Tensor map of a [B, S, H, D] operand (any strides, unit head-dim stride) viewed as the 5-D
-// tensor (64, S, D/64, H, B); one box is (64, rows, D/64, 1, 1) and lands in shared memory as
-// D/64 consecutive [rows][64] blocks with the 128-byte swizzle the MMA descriptors expect.
-int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, int D,
+// tensor (D/nblk, S, nblk, H, B); one box is (64, rows, nblk, 1, 1) and lands in shared memory as
+// nblk consecutive [rows][64] blocks with the 128-byte swizzle the MMA descriptors expect.
+int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, const HeadDim& hd,
               const fa2_strides& st, int box_rows, const char* what, int box_dblocks = 0) {
-  if (box_dblocks == 0) box_dblocks = D / 64;   // default: the full head dim
+  if (box_dblocks == 0) box_dblocks = hd.nblk;   // default: the full head dim
+  const int D = hd.blk * hd.nblk;
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return fail(FA2_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0)
@@ -72,12 +94,14 @@ int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, 
     return fail(FA2_ERR_UNSUPPORTED, "%s: strides must be multiples of 8 elements", what);
   if (st.s <= 0 || (H > 1 && st.h <= 0) || (B > 1 && st.b <= 0))
     return fail(FA2_ERR_INVALID_ARG, "%s: strides must be positive", what);
-  const cuuint64_t dims[5] = {64, static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(D / 64),
-                              static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+  const cuuint64_t dims[5] = {static_cast<cuuint64_t>(hd.blk), static_cast<cuuint64_t>(S),
+                              static_cast<cuuint64_t>(hd.nblk), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(B)};
   // A dimension of extent 1 still needs a legal (multiple of 16 bytes) stride.
   const cuuint64_t sh = static_cast<cuuint64_t>(st.h > 0 ? st.h : D) * 2;
   const cuuint64_t sb = static_cast<cuuint64_t>(st.b > 0 ? st.b : static_cast<int64_t>(D)) * 2;
-  const cuuint64_t strides[4] = {static_cast<cuuint64_t>(st.s) * 2, 128, sh, sb};
+  const cuuint64_t strides[4] = {static_cast<cuuint64_t>(st.s) * 2,
+                                 static_cast<cuuint64_t>(hd.blk) * 2, sh, sb};
   const cuuint32_t box[5] = {64, static_cast<cuuint32_t>(box_rows),
                              static_cast<cuuint32_t>(box_dblocks), 1, 1};
   const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
@@ -101,8 +125,11 @@ int check_problem(const fa2_problem& p, bool backward = false) {
   if (p.dtype != FA2_FP16 && p.dtype != FA2_BF16)
     return fail(FA2_ERR_UNSUPPORTED, "only fp16 and bf16 inputs are supported");
   (void)backward;
-  if (p.head_dim != 64 && p.head_dim != 128 && p.head_dim != 256)
-    return fail(FA2_ERR_UNSUPPORTED, "head_dim %d is not supported (64, 128 and 256 are)", p.head_dim);
+  HeadDim hd;
+  if (!split_head_dim(p.head_dim, &hd))
+    return fail(FA2_ERR_UNSUPPORTED,
+                "head_dim %d is not supported (multiples of 8 up to 64, of 16 up to 128, of 32 up to 256 are)",
+                p.head_dim);
   if (!(p.dropout_p >= 0.f) || !(p.dropout_p < 1.f))
     return fail(FA2_ERR_INVALID_ARG, "dropout_p must be in [0, 1)");
   if (!std::isfinite(p.softmax_scale))
@@ -159,7 +186,9 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * w.sq_pad;
   w.delta_off = 0;
   w.dq_off = align_up(2 * rows * sizeof(float), 256);   // (lse2, delta) per row
-  w.absmax_off = w.dq_off + align_up(rows * p.head_dim * sizeof(float), 256);
+  HeadDim hd;
+  split_head_dim(p.head_dim, &hd);   // checked by the callers
+  w.absmax_off = w.dq_off + align_up(rows * hd.padded * sizeof(float), 256);
   w.total = w.absmax_off + 256;   // one word: max|dO| of the call (fp16 range guard)
   return w;
 }
@@ -206,12 +235,14 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   FwdLaunch L;
   std::memset(&L, 0, sizeof(L));
   const bool bf16 = p.dtype == FA2_BF16;
-  const int D = p.head_dim;
-  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->q_strides, 128, "q")) ||
-      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->k_strides, 128, "k")) ||
-      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->v_strides, 128, "v")) ||
-      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->o_strides, 128, "o")) ||
-      (rc = make_tmap(&L.tmO1, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->o_strides, 128, "o", 1)))
+  HeadDim hd;
+  split_head_dim(p.head_dim, &hd);
+  const int D = hd.padded;
+  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->q_strides, 128, "q")) ||
+      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k")) ||
+      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v")) ||
+      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->o_strides, 128, "o")) ||
+      (rc = make_tmap(&L.tmO1, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->o_strides, 128, "o", 1)))
     return rc;
 
   FwdKernelParams& kp = L.kp;
@@ -263,16 +294,18 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   BwdLaunch L;
   std::memset(&L, 0, sizeof(L));
   const bool bf16 = p.dtype == FA2_BF16;
-  const int D = p.head_dim;
+  HeadDim hd;
+  split_head_dim(p.head_dim, &hd);
+  const int D = hd.padded;
   // head dim 256: 64-row query tiles, and dk / dv leave in halves of the head dim
   const int q_rows = (D == 256) ? 64 : 128;
   const int dkv_blocks = (D == 256) ? 2 : D / 64;
-  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->q_strides, q_rows, "q")) ||
-      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->k_strides, 128, "k")) ||
-      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->v_strides, 128, "v")) ||
-      (rc = make_tmap(&L.tmdO, a->d_o, bf16, p.batch, p.seqlen_q, p.heads_q, D, a->do_strides, q_rows, "d_o")) ||
-      (rc = make_tmap(&L.tmdK, a->dk, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dk_strides, 128, "dk", dkv_blocks)) ||
-      (rc = make_tmap(&L.tmdV, a->dv, bf16, p.batch, p.seqlen_k, p.heads_kv, D, a->dv_strides, 128, "dv", dkv_blocks)))
+  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->q_strides, q_rows, "q")) ||
+      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k")) ||
+      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v")) ||
+      (rc = make_tmap(&L.tmdO, a->d_o, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->do_strides, q_rows, "d_o")) ||
+      (rc = make_tmap(&L.tmdK, a->dk, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->dk_strides, 128, "dk", dkv_blocks)) ||
+      (rc = make_tmap(&L.tmdV, a->dv, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->dv_strides, 128, "dv", dkv_blocks)))
     return rc;
   if ((a->o_strides.b % 8) || (a->o_strides.s % 8) || (a->o_strides.h % 8) ||
       (a->dq_strides.b % 8) || (a->dq_strides.s % 8) || (a->dq_strides.h % 8) ||
@@ -308,6 +341,8 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   L.dq = a->dq; L.dq_strides[0] = a->dq_strides.b; L.dq_strides[1] = a->dq_strides.s; L.dq_strides[2] = a->dq_strides.h;
   L.delta = reinterpret_cast<float*>(ws + w.delta_off);
   L.dq_acc_bytes = w.absmax_off - w.dq_off;
+  L.head_dim_real = p.head_dim;
+  L.head_blk = hd.blk;
 
   for (int i = 0; i < 4; ++i) {
     L.stage_events[i] = g_bwd_events[i];

@@ -58,7 +58,7 @@ template <bool kBf16>
 __global__ void __launch_bounds__(256)
 bwd256_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long long sb,
                   long long ss, long long sh, int Sq, int Hq, int nQ64, float scale_in,
-                  const unsigned* __restrict__ do_absmax_bits) {
+                  const unsigned* __restrict__ do_absmax_bits, int blk_real) {
   const float scale = scale_in / (kBf16 ? 1.f : do_scale_from_bits(do_absmax_bits));
   const int i = blockIdx.x;
   const int bh = blockIdx.y;
@@ -75,11 +75,15 @@ bwd256_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, l
     const float4 x = src[slab * 128 + 2 * dpair];
     const float4 y = src[slab * 128 + 2 * dpair + 1];
     const float xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
+    // a padded head dim keeps blk_real real columns at the start of every 64-column block
+    const int col = half * 128 + 2 * dpair;          // column in the padded head dim
+    const int blk = col >> 6, x_in = col & 63;
+    const int pair_real = (blk * blk_real + x_in) >> 1;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int row = i * kBQ + c4 * 4 + e;
-      if (row < Sq)
-        reinterpret_cast<uint32_t*>(dq + b * sb + row * ss + h * sh)[half * 64 + dpair] =
+      if (row < Sq && x_in < blk_real)
+        reinterpret_cast<uint32_t*>(dq + b * sb + row * ss + h * sh)[pair_real] =
             pack2<kBf16>(xs[e] * scale, ys[e] * scale);
     }
   }
@@ -543,7 +547,8 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
   bwd_pre_kernel<kD, kBf16><<<dim3(nQ128, kp.B * kp.Hq), 128, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
-      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax);
+      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax,
+      a.head_dim_real);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   mark(1);
@@ -558,7 +563,7 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
   mark(2);
   bwd256_dq_convert<kBf16><<<dim3(nQ64, kp.B * kp.Hq), 256, 0, stream>>>(
       kp.dq_acc, static_cast<uint16_t*>(a.dq), a.dq_strides[0], a.dq_strides[1], a.dq_strides[2],
-      kp.Sq, kp.Hq, nQ64, kp.scale, kBf16 ? nullptr : kp.do_absmax_bits);
+      kp.Sq, kp.Hq, nQ64, kp.scale, kBf16 ? nullptr : kp.do_absmax_bits, a.head_blk);
   mark(3);
   return cudaGetLastError();
 }

@@ -115,7 +115,7 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                long long o_sb, long long o_ss, long long o_sh, long long do_sb, long long do_ss,
                long long do_sh, const float* __restrict__ lse, long long lse_sb, long long lse_sh,
                float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ,
-               unsigned* __restrict__ do_absmax_bits) {
+               unsigned* __restrict__ do_absmax_bits, int d_real) {
   const int i = blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / Hq, h = bh - b * Hq;
@@ -130,7 +130,7 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
     const int r = r0 + tid / kLanesPerRow;
     const int row = i * kBM + r;
     float acc = 0.f;
-    if (row < Sq) {
+    if (row < Sq && 8 * sub < d_real) {   // d_real < D: the head dim is padded, rows are d_real wide
       const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + b * o_sb + row * o_ss + h * o_sh) + sub);
       const uint4 g = __ldg(reinterpret_cast<const uint4*>(d_o + b * do_sb + row * do_ss + h * do_sh) + sub);
       const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};

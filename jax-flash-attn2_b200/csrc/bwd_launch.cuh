@@ -10,7 +10,9 @@ namespace fa2 {
 struct BwdLaunch {
   CUtensorMap tmQ, tmK, tmV, tmdO, tmdK, tmdV;
   BwdKernelParams kp;
-  int head_dim;
+  int head_dim;        // 64, 128 or 256: the kernel's (padded) head dim
+  int head_dim_real;   // the operands' head dim
+  int head_blk;        // real columns in each 64-column block of the padded head dim
   bool bf16, causal, feat;
   const void* o;   long long o_strides[3];    // (batch, sequence, head) element strides
   const void* d_o; long long do_strides[3];

@@ -95,7 +95,7 @@ template <int D, bool kBf16>
 __global__ void __launch_bounds__(256)
 bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long long sb,
                long long ss, long long sh, int Sq, int Hq, int nQ, float scale_in,
-               const unsigned* __restrict__ do_absmax_bits) {
+               const unsigned* __restrict__ do_absmax_bits, int blk_real) {
   const float scale = scale_in / (kBf16 ? 1.f : do_scale_from_bits(do_absmax_bits));
   constexpr int kPitch = 129;                       // float4 per column chunk: 128 rows + 1 pad
   __shared__ float4 tile[16 * kPitch];              // 16 chunks of 4 columns = 64 columns
@@ -118,7 +118,8 @@ bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long
     for (int pass = 0; pass < 4; ++pass) {
       const int r = pass * 32 + (tid >> 3);
       const int row = i * kBM + r;
-      if (row < Sq) {
+      // a padded head dim keeps blk_real real columns at the start of every 64-column block
+      if (row < Sq && 8 * j < blk_real) {
         const float4 x = tile[(2 * j) * kPitch + r];
         const float4 y = tile[(2 * j + 1) * kPitch + r];
         uint4 v;
@@ -126,7 +127,7 @@ bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long
         v.y = pack2<kBf16>(x.z * scale, x.w * scale);
         v.z = pack2<kBf16>(y.x * scale, y.y * scale);
         v.w = pack2<kBf16>(y.z * scale, y.w * scale);
-        reinterpret_cast<uint4*>(dq + b * sb + row * ss + h * sh)[part * 8 + j] = v;
+        reinterpret_cast<uint4*>(dq + b * sb + row * ss + h * sh)[part * (blk_real >> 3) + j] = v;
       }
     }
   }
@@ -674,7 +675,8 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   bwd_pre_kernel<D, kBf16><<<grid, 128, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
-      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ, kBf16 ? nullptr : absmax);
+      kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ, kBf16 ? nullptr : absmax,
+      a.head_dim_real);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);
@@ -690,7 +692,7 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   bwd_dq_convert<D, kBf16><<<grid, 256, 0, stream>>>(kp.dq_acc, static_cast<uint16_t*>(a.dq),
                                                      a.dq_strides[0], a.dq_strides[1],
                                                      a.dq_strides[2], kp.Sq, kp.Hq, nQ, kp.scale,
-                                                     kBf16 ? nullptr : kp.do_absmax_bits);
+                                                     kBf16 ? nullptr : kp.do_absmax_bits, a.head_blk);
   mark(3);
   return cudaGetLastError();
 }

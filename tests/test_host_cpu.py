@@ -35,8 +35,13 @@ def test_validation_errors_come_before_any_launch():
     assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_INVALID_ARG
     assert b"divisible" in lib.fa2_last_error()
     a.p.heads_q = 4
-    a.p.head_dim = 96
-    assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_UNSUPPORTED
+    for d in (72, 136, 288):       # not a multiple of 16 / of 32 / above 256
+        a.p.head_dim = d
+        assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_UNSUPPORTED
+        assert b"head_dim" in lib.fa2_last_error()
+    a.p.head_dim = 96              # padded to 128 inside: the workspace is sized for 128 columns
+    rows = 1 * 4 * 128
+    assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 128 * 4 + 256
     a.p.head_dim = 128
     a.p.dropout_p = 1.0
     assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_INVALID_ARG

@@ -104,6 +104,23 @@ def test_head_dim_256_with_bias_mask_dropout():
     run_case(1, 200, 200, 4, 2, 256, torch.float16, True, scale=1.0 / 16, bias_heads=4, p=0.1)
 
 
+@pytest.mark.parametrize("D,dtype,causal", [
+    (8, torch.float16, False), (32, torch.bfloat16, True), (40, torch.float16, True),
+    (56, torch.bfloat16, False), (80, torch.bfloat16, True), (96, torch.float16, False),
+    (112, torch.bfloat16, True), (160, torch.float16, True), (192, torch.bfloat16, False),
+    (224, torch.bfloat16, True),
+])
+def test_head_dims_between_the_kernel_sizes(D, dtype, causal):
+    """Head dims other than 64 / 128 / 256 (the reference pads them: PADDED_HEADS,
+    _forward_triton.py:337-346): the tensor maps cut the head dim into equal zero-padded blocks."""
+    run_case(2, 200, 328, 4, 2, D, dtype, causal, scale=D ** -0.25)
+
+
+def test_padded_head_dim_with_bias_mask_dropout():
+    run_case(1, 256, 320, 2, 2, 96, torch.bfloat16, False, scale=0.3, bias_heads=1, mask_kind="pad", p=0.2)
+    run_case(1, 200, 200, 4, 2, 192, torch.float16, True, scale=0.25, bias_heads=4, p=0.1)
+
+
 @pytest.mark.parametrize("G", [1, 2, 4, 8])
 def test_gqa_groups(G):
     run_case(1, 256, 256, 8, 8 // G, 64, torch.float16, True)
@@ -226,9 +243,10 @@ def test_strided_inputs_bhsd_storage():
 def test_unsupported_arguments_raise_before_launch():
     J = _J()
     from jax_flash_attn2._capi import Fa2Error
-    q = torch.zeros(1, 128, 2, 96, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(Fa2Error, match="head_dim"):
-        J.fwd_attention_kernel_call(q, q, q)
+    for d in (72, 144, 320):     # not a multiple of 16 / of 32 / above 256
+        q = torch.zeros(1, 128, 2, d, dtype=torch.bfloat16, device="cuda")
+        with pytest.raises(Fa2Error, match="head_dim"):
+            J.fwd_attention_kernel_call(q, q, q)
     q = torch.zeros(1, 128, 2, 64, dtype=torch.float32, device="cuda")
     with pytest.raises(AssertionError, match="fp16 and bf16"):
         J.fwd_attention_kernel_call(q, q, q)
