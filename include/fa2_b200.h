@@ -80,6 +80,14 @@ typedef struct {
   int64_t lse_stride_b, lse_stride_h;
   fa2_score_term bias;                         /* added to scale * q.k                        */
   fa2_score_term mask;                         /* added as well; 0 keeps, -inf / finfo.min drops */
+  /* Optional (NULL = absent): int32 [batch] on the device. Batch element b is attended as if
+   * seqlen_q = seqlen_k = seqlens[b] (its first seqlens[b] rows are the real tokens, the rest is
+   * padding): keys past that length are not seen, key tiles past it are not visited, and output
+   * rows past it are written as zeros (their lse as -inf). Requires seqlen_q == seqlen_k. This is
+   * the reference's varlen mode for a [batch, seqlen] padding mask (_forward_triton.py:267-279,
+   * 500-510) without its pack / unpack copies (_utils.py:196-294); values are clamped to
+   * [0, seqlen_q]. */
+  const int32_t* seqlens;
 } fa2_fwd_params;
 
 typedef struct {
@@ -97,6 +105,10 @@ typedef struct {
   void* dv; fa2_strides dv_strides;
   void* workspace;                             /* fa2_bwd_workspace_bytes() bytes, 256-aligned */
   size_t workspace_bytes;
+  /* Optional per-batch lengths: the array that was given to the forward call.
+   * Rows of dq, dk and dv past a batch element's length are written as zeros and its d_o rows
+   * past it are never read (_backward_triton.py:973-1025, 1163-1171). */
+  const int32_t* seqlens;
 } fa2_bwd_params;
 
 /* Forward: o = softmax(scale q k^T + bias + mask [causal]) v with dropout on the weights, and

@@ -200,7 +200,7 @@ using namespace fa2;
 
 extern "C" {
 
-int fa2_version(void) { return 1000; }
+int fa2_version(void) { return 1001; }
 
 const char* fa2_last_error(void) { return g_err; }
 
@@ -255,6 +255,11 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
       (rc = make_score_term(&kp.mask, a->mask, p, "mask")))
     return rc;
   make_dropout(&kp.drop, p);
+  if (a->seqlens && p.seqlen_q != p.seqlen_k)
+    return fail(FA2_ERR_INVALID_ARG, "seqlens requires seqlen_q == seqlen_k");
+  if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
+    return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
+  kp.seqlens = a->seqlens;
   kp.n_qblk = (p.seqlen_q + 255) / 256;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
@@ -328,6 +333,11 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
       (rc = make_score_term(&kp.mask, a->mask, p, "mask")))
     return rc;
   make_dropout(&kp.drop, p);
+  if (a->seqlens && p.seqlen_q != p.seqlen_k)
+    return fail(FA2_ERR_INVALID_ARG, "seqlens requires seqlen_q == seqlen_k");
+  if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
+    return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
+  kp.seqlens = a->seqlens;
   kp.n_kvblk = (p.seqlen_k + 127) / 128;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");

@@ -127,16 +127,24 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int bhk = rest / p.n_kvblk;
   const int b = bhk / p.Hkv;
   const int hk = bhk - b * p.Hkv;
-  const int nQ64 = (p.Sq + kBQ - 1) / kBQ;
+  const int nQ64 = (p.Sq + kBQ - 1) / kBQ;      // tiles in the accumulator layout
   const int nQ128 = (p.Sq + 127) / 128;
+  // rows of this batch element that take part: the problem's, or its seqlens entry
+  int sq_b = p.Sq, sk_b = p.Sk;
+  if (p.seqlens != nullptr) {
+    sq_b = max(0, min(__ldg(p.seqlens + b), p.Sq));
+    sk_b = min(sq_b, p.Sk);
+  }
+  const int nQ64_b = (sq_b + kBQ - 1) / kBQ;
   int i_start = 0;
   if (kCausal) {
     const int first_row = n * kBK - p.causal_off;   // first query row that sees key n*128
     i_start = first_row > 0 ? first_row / kBQ : 0;
-    if (i_start > nQ64) i_start = nQ64;
   }
-  const int nI = nQ64 - i_start;
-  const int T = nI * p.G;
+  if (i_start > nQ64_b) i_start = nQ64_b;
+  const int nI = nQ64_b - i_start;
+  const int T = (n * kBK < sk_b) ? nI * p.G : 0;    // steps of this CTA (none: dK = dV = 0)
+  const bool dead_keys = n * kBK + kBK > sk_b;      // some key rows lie past the end
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -365,8 +373,9 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const bool diag = kCausal && (n * kBK + kBK - 1 > i * kBQ + p.causal_off);
-      const int q_lim = kv - p.causal_off;     // masked iff query index < q_lim
+      const bool diag = (kCausal && (n * kBK + kBK - 1 > i * kBQ + p.causal_off)) || dead_keys;
+      // masked iff query index < q_lim: every query for a key past the end
+      const int q_lim = kv >= sk_b ? 0x7fffffff : (kCausal ? kv - p.causal_off : -0x7fffffff - 1);
 
       uint32_t pk[16];
       uint32_t keep = 0xffffffffu;
@@ -548,7 +557,7 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax,
-      a.head_dim_real);
+      a.head_dim_real, kp.seqlens);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   mark(1);

@@ -115,10 +115,13 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                long long o_sb, long long o_ss, long long o_sh, long long do_sb, long long do_ss,
                long long do_sh, const float* __restrict__ lse, long long lse_sb, long long lse_sh,
                float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ,
-               unsigned* __restrict__ do_absmax_bits, int d_real) {
+               unsigned* __restrict__ do_absmax_bits, int d_real,
+               const int* __restrict__ seqlens) {
   const int i = blockIdx.x;
   const int bh = blockIdx.y;
   const int b = bh / Hq, h = bh - b * Hq;
+  // rows past a batch element's own length take no gradient (and their dO is never read)
+  const int sq_b = seqlens ? max(0, min(__ldg(seqlens + b), Sq)) : Sq;
   const int tid = threadIdx.x;
   constexpr int kLanesPerRow = D / 8;            // 16-byte loads
   constexpr int kRowsPerPass = 128 / kLanesPerRow;
@@ -130,7 +133,7 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
     const int r = r0 + tid / kLanesPerRow;
     const int row = i * kBM + r;
     float acc = 0.f;
-    if (row < Sq && 8 * sub < d_real) {   // d_real < D: the head dim is padded, rows are d_real wide
+    if (row < sq_b && 8 * sub < d_real) {   // d_real < D: the head dim is padded, rows are d_real wide
       const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + b * o_sb + row * o_ss + h * o_sh) + sub);
       const uint4 g = __ldg(reinterpret_cast<const uint4*>(d_o + b * do_sb + row * do_ss + h * do_sh) + sub);
       const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
@@ -153,12 +156,12 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
       acc += __shfl_xor_sync(0xffffffffu, acc, off);
     if (sub == 0) {
       float l2 = -INFINITY;      // -lse*log2(e); -inf makes every weight of the row exp2(-inf) = 0
-      if (row < Sq) {
+      if (row < sq_b) {
         const float l = lse[b * lse_sb + h * lse_sh + row];
         if (l > -INFINITY && l < INFINITY) l2 = -l * kLog2e;
       }
       st[r] = l2;
-      st[128 + r] = (row < Sq) ? acc : 0.f;
+      st[128 + r] = (row < sq_b) ? acc : 0.f;
     }
   }
   float4* acc4 = reinterpret_cast<float4*>(dq_acc + tile * (kBM * D));

@@ -179,15 +179,23 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int bhk = blockIdx.x / p.n_kvblk;
   const int b = bhk / p.Hkv;
   const int hk = bhk - b * p.Hkv;
-  const int nQ = (p.Sq + kBM - 1) / kBM;
+  const int nQ = (p.Sq + kBM - 1) / kBM;   // query tiles in the statistics / accumulator layout
+  // rows of this batch element that take part: the problem's, or its seqlens entry
+  int sq_b = p.Sq, sk_b = p.Sk;
+  if (p.seqlens != nullptr) {
+    sq_b = max(0, min(__ldg(p.seqlens + b), p.Sq));
+    sk_b = min(sq_b, p.Sk);
+  }
+  const int nQ_b = (sq_b + kBM - 1) / kBM;
   int i_start = 0;
   if (kCausal) {
     const int first_row = n * kBN - p.causal_off;   // first query row that sees key n*128
     i_start = first_row > 0 ? first_row / kBM : 0;
-    if (i_start > nQ) i_start = nQ;
   }
-  const int nI = nQ - i_start;          // query tiles per head
-  const int T = nI * p.G;               // steps of this CTA
+  if (i_start > nQ_b) i_start = nQ_b;
+  const int nI = nQ_b - i_start;                     // query tiles per head
+  const int T = (n * kBN < sk_b) ? nI * p.G : 0;     // steps of this CTA (none: dK = dV = 0)
+  const bool dead_keys = n * kBN + kBN > sk_b;       // some key rows lie past the end
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -466,8 +474,9 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0 && warp < 8) FA2_T(32 + warp, it);
       tc_fence_after();
       // some (query, key) pairs of this step are above the causal diagonal
-      const bool diag = kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off);
-      const int q_lim = kv - p.causal_off;     // masked iff query index < q_lim
+      const bool diag = (kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off)) || dead_keys;
+      // masked iff query index < q_lim: every query for a key past the end
+      const int q_lim = kv >= sk_b ? 0x7fffffff : (kCausal ? kv - p.causal_off : -0x7fffffff - 1);
 
       // ---- P^T = exp2(S^T * scale*log2e - lse*log2e): kCW query columns of this key row ------
       uint32_t pk[kCW / 2];                     // P as 16-bit pairs; also the input of dS below
@@ -676,7 +685,7 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ, kBf16 ? nullptr : absmax,
-      a.head_dim_real);
+      a.head_dim_real, kp.seqlens);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);

@@ -71,13 +71,21 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int h = bh - b * p.Hq;
   const int hk = h / p.G;
   const int q0 = qt * kBM;
+  // rows of this batch element that take part: the problem's, or its seqlens entry
+  int sq_b = p.Sq, sk_b = p.Sk;
+  if (p.seqlens != nullptr) {
+    sq_b = max(0, min(__ldg(p.seqlens + b), p.Sq));
+    sk_b = min(sq_b, p.Sk);
+  }
   int nt;
-  if (kCausal) {
-    const int row_last = min(q0 + kBM - 1, p.Sq - 1);
-    const int last_col = min(p.Sk - 1, row_last + p.causal_off);
+  if (q0 >= sq_b) {
+    nt = 0;
+  } else if (kCausal) {
+    const int row_last = min(q0 + kBM - 1, sq_b - 1);
+    const int last_col = min(sk_b - 1, row_last + p.causal_off);
     nt = last_col >= 0 ? last_col / kBN + 1 : 0;
   } else {
-    nt = (p.Sk + kBN - 1) / kBN;
+    nt = (sk_b + kBN - 1) / kBN;
   }
 
   if (tid == 0) {
@@ -189,7 +197,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int qi = q0 + r;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tO = tmem_base + lane_base + kColO;
-    const int row_lim = kCausal ? min(p.Sk - 1, qi + p.causal_off) : p.Sk - 1;
+    const int row_lim = qi < sq_b ? (kCausal ? min(sk_b - 1, qi + p.causal_off) : sk_b - 1) : -1;
     const float sc = kFeat ? 1.0f : p.scale_log2;
     float m = -INFINITY, l = 0.f;
     bool ok = true;

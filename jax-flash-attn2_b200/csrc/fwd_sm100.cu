@@ -62,6 +62,7 @@ struct FwdSmem {
 // One work item as every role sees it.
 struct FwdItem {
   int b, h, hk, q0;
+  int sq, sk;   // rows of this batch element that take part (the problem's, or its seqlens entry)
   int n_tiles[kTilesPerCta];
   int n_max;
 };
@@ -77,17 +78,24 @@ __device__ __forceinline__ void decode_item(const FwdKernelParams& p, int w, Fwd
   it.h = bh - it.b * p.Hq;
   it.hk = it.h / p.G;
   it.q0 = qblk * (kBM * kTilesPerCta);
+  it.sq = p.Sq;
+  it.sk = p.Sk;
+  if (p.seqlens != nullptr) {
+    const int len = max(0, min(__ldg(p.seqlens + it.b), p.Sq));
+    it.sq = len;
+    it.sk = min(len, p.Sk);
+  }
 #pragma unroll
   for (int t = 0; t < kTilesPerCta; ++t) {
     const int row_first = it.q0 + t * kBM;
-    if (row_first >= p.Sq) {
+    if (row_first >= it.sq) {
       it.n_tiles[t] = 0;
     } else if (kCausal) {
-      const int row_last = min(row_first + kBM - 1, p.Sq - 1);
-      const int last_col = min(p.Sk - 1, row_last + p.causal_off);
+      const int row_last = min(row_first + kBM - 1, it.sq - 1);
+      const int last_col = min(it.sk - 1, row_last + p.causal_off);
       it.n_tiles[t] = last_col >= 0 ? last_col / kBN + 1 : 0;
     } else {
-      it.n_tiles[t] = (p.Sk + kBN - 1) / kBN;
+      it.n_tiles[t] = (it.sk + kBN - 1) / kBN;
     }
   }
   it.n_max = max(it.n_tiles[0], it.n_tiles[1]);
@@ -333,8 +341,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const int qi = it.q0 + t * kBM + r;      // global query row
       const int nt = it.n_tiles[t];
       const bool tile_valid = (it.q0 + t * kBM) < p.Sq;
-      // last visible key of this row
-      const int row_lim = kCausal ? min(p.Sk - 1, qi + p.causal_off) : p.Sk - 1;
+      // last visible key of this row (none for rows past the end of the sequence)
+      const int row_lim =
+          qi < it.sq ? (kCausal ? min(it.sk - 1, qi + p.causal_off) : it.sk - 1) : -1;
       float m = -INFINITY;   // running (possibly stale) row maximum, in the units of x[]
       float l = 0.f;         // running row sum of exp2(x*sc - m*sc)
 

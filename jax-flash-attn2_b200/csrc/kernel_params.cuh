@@ -29,6 +29,9 @@ struct FwdKernelParams {
   ScoreTermDev bias, mask;
   DropoutDev drop;
   int n_qblk;           // number of 256-row query blocks
+  // Optional per-batch lengths (Sq == Sk): batch element b is attended as if both sequences had
+  // seqlens[b] rows; output rows at or beyond it are written as zeros.
+  const int* seqlens;
   int* status;          // device status word (bounded-wait time-outs)
 };
 
@@ -45,6 +48,7 @@ struct BwdKernelParams {
   ScoreTermDev bias, mask;
   DropoutDev drop;
   int n_kvblk;          // number of 128-row key blocks
+  const int* seqlens;   // optional per-batch lengths (Sq == Sk), as in the forward
   // fp16 only: bit pattern of max|dO| over the whole call (written by the pre-pass); dS is
   // scaled by a power of two derived from it so that small cotangents do not underflow in fp16.
   const unsigned* do_absmax_bits;

@@ -74,6 +74,7 @@ class FwdParams(C.Structure):
         ("lse_stride_b", C.c_int64), ("lse_stride_h", C.c_int64),
         ("bias", ScoreTerm),
         ("mask", ScoreTerm),
+        ("seqlens", C.c_void_p),
     ]
 
 
@@ -94,6 +95,7 @@ class BwdParams(C.Structure):
         ("dv", C.c_void_p), ("dv_strides", Strides),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
+        ("seqlens", C.c_void_p),
     ]
 
 

@@ -16,6 +16,7 @@ from ._kernel_calls import (
     bwd_attention_kernel_call,
     fwd_attention_kernel_call,
     normalise_attention_mask,
+    seqlens_from_padding_mask,
 )
 
 
@@ -24,7 +25,7 @@ class _FlashAttentionCall(torch.autograd.Function):
     def forward(ctx, q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard):
         out, lse = fwd_attention_kernel_call(
             q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, **shard
-        )
+        )   # `shard` also carries the per-batch lengths, when there are any
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.extras = (attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard)
         return out
@@ -56,14 +57,23 @@ def flash_attention(
     heads_q_global: tp.Optional[int] = None,
 ) -> torch.Tensor:
     """Same signature as the reference's `triton_flash_attention`
-    (flash_attention_triton/_flash_attention.py:125-157). `varlen_mode` is accepted for
-    compatibility: a 2-D padding mask is always honoured (keys masked, padded rows zeroed).
+    (flash_attention_triton/_flash_attention.py:125-157).
+
+    A 2-D [B, S] `attention_mask` is a padding mask. With `varlen_mode=True` (the default, as in
+    the reference) it is read the way the reference's varlen mode reads it: row b has
+    `sum(mask[b])` real tokens and they come first; the kernels then work on per-batch lengths and
+    skip the padding (no packing, no mask tensor). Unlike the reference this also holds for
+    batch 1 (where the reference ignores the mask, _forward_triton.py:475) and a bias may be given
+    as well. With `varlen_mode=False` the mask may have its real tokens anywhere: keys are masked
+    through an additive term and padded rows are zeroed afterwards.
     The three keyword-only arguments place a shard inside the unsharded problem so that dropout
     draws the same bits on every partitioning."""
-    del varlen_mode
     sq, sk = q.shape[1], k.shape[1]
-    add_mask, row_keep = normalise_attention_mask(attention_mask, q.dtype, sq, sk)
     shard = dict(batch_offset=batch_offset, head_offset=head_offset, heads_q_global=heads_q_global)
+    if attention_mask is not None and attention_mask.dim() == 2 and varlen_mode:
+        shard["seqlens"] = seqlens_from_padding_mask(attention_mask, sq, sk)
+        attention_mask = None
+    add_mask, row_keep = normalise_attention_mask(attention_mask, q.dtype, sq, sk)
     out = _FlashAttentionCall.apply(
         q, k, v, add_mask, bias, softmax_scale, float(dropout_prob), bool(causal), dropout_seed, shard
     )

@@ -63,10 +63,10 @@ def normalise_attention_mask(
 
     * 4-D floating mask [B, 1|Hq, Sq, Sk] (0 keeps, finfo.min / -inf drops): used as is.
     * 4-D bool / integer mask (non-zero keeps): converted to 0 / -inf.
-    * 2-D [B, S] padding mask (non-zero = real token): the reference's meaning of
-      `attention_mask` (_forward_triton.py:474-479). Becomes a key-padding term [B,1,1,Sk];
-      the second return value is the [B, Sq] row mask with which the caller zeroes the padded
-      query rows, as the reference's unpacking does.
+    * 2-D [B, S] padding mask (non-zero = real token) with tokens anywhere in the row: becomes a
+      key-padding term [B,1,1,Sk]; the second return value is the [B, Sq] row mask with which the
+      caller zeroes the padded query rows. (The reference's own reading of a 2-D mask, real tokens
+      first, is served by `seqlens_from_padding_mask` and the kernels' per-batch lengths.)
     """
     if attention_mask is None:
         return None, None
@@ -85,6 +85,34 @@ def normalise_attention_mask(
     add = torch.zeros(m.shape, dtype=dtype, device=m.device)
     add.masked_fill_(m == 0, float("-inf"))
     return add, None
+
+
+def seqlens_from_padding_mask(attention_mask: torch.Tensor, sq: int, sk: int) -> torch.Tensor:
+    """Per-batch lengths of a 2-D [B, S] padding mask, the way the reference's varlen mode reads
+    it (_forward_triton.py:500-510; _utils.py:211-221): the number of non-zero entries of a row
+    is the length of that sequence and its real tokens come first. Computed on the device, no
+    host synchronisation."""
+    if attention_mask.dim() != 2:
+        raise ValueError(f"a padding mask must be 2-D, got shape {tuple(attention_mask.shape)}")
+    if sq != sk:
+        raise AssertionError("Attention mask is not supported with QSeq != KSeq")
+    if attention_mask.shape[1] != sq:
+        raise ValueError(f"padding mask must be [batch, {sq}], got {tuple(attention_mask.shape)}")
+    return (attention_mask != 0).sum(dim=1, dtype=torch.int32).contiguous()
+
+
+def _seqlens_ptr(seqlens: tp.Optional[torch.Tensor], q: torch.Tensor, sk: int):
+    if seqlens is None:
+        return None, None
+    batch, sq = q.shape[0], q.shape[1]
+    if sq != sk:
+        raise AssertionError("Attention mask is not supported with QSeq != KSeq")
+    if seqlens.dtype != torch.int32 or seqlens.dim() != 1 or seqlens.shape[0] != batch:
+        raise ValueError(f"seqlens must be int32 of shape [{batch}], got {seqlens.dtype} {tuple(seqlens.shape)}")
+    if seqlens.device != q.device:
+        raise ValueError("seqlens must live on the device of q")
+    seqlens = seqlens.contiguous()
+    return seqlens.data_ptr(), seqlens
 
 
 def _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offset, head_offset, heads_q_global):
@@ -131,10 +159,13 @@ def fwd_attention_kernel_call(
     batch_offset: int = 0,
     head_offset: int = 0,
     heads_q_global: tp.Optional[int] = None,
+    seqlens: tp.Optional[torch.Tensor] = None,
 ) -> tp.Tuple[torch.Tensor, torch.Tensor]:
     """Forward launch. q [B,Sq,Hq,D]; k, v [B,Sk,Hkv,D]; `attention_mask` here is already an
-    additive 4-D term (see normalise_attention_mask). Returns (out [B,Sq,Hq,D] in q.dtype,
-    lse [B,Hq,ceil(Sq/128)*128] float32, natural log; columns >= Sq are not written)."""
+    additive 4-D term (see normalise_attention_mask); `seqlens` (int32 [B], device) gives every
+    batch element its own length, the reference's varlen mode without packing. Returns
+    (out [B,Sq,Hq,D] in q.dtype, lse [B,Hq,ceil(Sq/128)*128] float32, natural log; columns >= Sq
+    are not written)."""
     _check_qkv(q, k, v)
     lib = _capi.load()
     q, k, v = _unit_last(q), _unit_last(k), _unit_last(v)
@@ -153,6 +184,7 @@ def fwd_attention_kernel_call(
     a.lse, a.lse_stride_b, a.lse_stride_h = lse.data_ptr(), lse.stride(0), lse.stride(1)
     a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias")
     a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
+    a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
         _capi.check(lib.fa2_fwd(C.byref(a), C.c_void_p(stream)))
@@ -176,6 +208,7 @@ def bwd_attention_kernel_call(
     batch_offset: int = 0,
     head_offset: int = 0,
     heads_q_global: tp.Optional[int] = None,
+    seqlens: tp.Optional[torch.Tensor] = None,
 ) -> tp.Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Backward launch; `M` is the lse returned by the forward. Returns (dq, dk, dv) in the input
     dtype; dk and dv are already reduced over the query heads of each key/value head."""
@@ -208,6 +241,7 @@ def bwd_attention_kernel_call(
     a.dk, a.dk_strides = dk.data_ptr(), _strides(dk)
     a.dv, a.dv_strides = dv.data_ptr(), _strides(dv)
     a.workspace, a.workspace_bytes = workspace.data_ptr(), nbytes
+    a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
     with torch.cuda.device(q.device):
         stream = torch.cuda.current_stream().cuda_stream
         _capi.check(lib.fa2_bwd(C.byref(a), C.c_void_p(stream)))

@@ -121,6 +121,67 @@ def test_padded_head_dim_with_bias_mask_dropout():
     run_case(1, 200, 200, 4, 2, 192, torch.float16, True, scale=0.25, bias_heads=4, p=0.1)
 
 
+@pytest.mark.parametrize("D,dtype,causal,S,lengths,extras", [
+    (128, torch.bfloat16, True, 512, [512, 300, 128, 1], {}),
+    (128, torch.bfloat16, False, 384, [200, 384, 0], {}),
+    (64, torch.float16, True, 300, [77, 300], {}),
+    (64, torch.bfloat16, False, 320, [129, 255], dict(bias_heads=4, p=0.2)),
+    (256, torch.float16, True, 320, [200, 65, 320], {}),
+    (256, torch.bfloat16, False, 256, [100, 256], dict(bias_heads=1, p=0.1)),
+    (96, torch.bfloat16, True, 256, [256, 130], {}),
+])
+def test_per_batch_lengths(D, dtype, causal, S, lengths, extras):
+    """Per-batch sequence lengths (the reference's varlen mode, _forward_triton.py:267-279): batch
+    element b must come out as the attention over its first lengths[b] rows alone, with zeros
+    behind them in the output and in all three gradients; what sits in the padding (large finite
+    values here) must not matter."""
+    J = _J()
+    B, Hq, Hkv = len(lengths), 4, 2
+    scale = D ** -0.25
+    q, k, v, do = W.make_qkv(B, S, S, Hq, Hkv, D, dtype, scale)
+    for b, n in enumerate(lengths):
+        for x in (q, k, v, do):
+            x[b, n:] = 50.0
+    g = torch.Generator().manual_seed(9)
+    bias_heads, p = extras.get("bias_heads", 0), extras.get("p", 0.0)
+    bias = (0.5 * torch.randn(B, bias_heads, S, S, generator=g)).to(dtype) if bias_heads else None
+    seqlens = torch.tensor(lengths, dtype=torch.int32)
+    dev = lambda x: None if x is None else x.cuda()
+    out, lse = J.fwd_attention_kernel_call(dev(q), dev(k), dev(v), None, dev(bias), None, p, causal, 11,
+                                           seqlens=seqlens.cuda())
+    dq, dk, dv = J.bwd_attention_kernel_call(dev(do), dev(q), dev(k), dev(v), dev(bias), None, out, lse, p,
+                                             causal, None, 11, seqlens=seqlens.cuda())
+    assert J.device_status() == 0
+    out, lse, dq, dk, dv = (x.cpu() for x in (out, lse, dq, dk, dv))
+    blk = BlockAttention()
+    for b, n in enumerate(lengths):
+        assert torch.all(out[b, n:] == 0) and torch.all(dq[b, n:] == 0)
+        assert torch.all(dk[b, n:] == 0) and torch.all(dv[b, n:] == 0)
+        assert torch.all(lse[b, :, n:S] == float("-inf"))
+        if n == 0:
+            continue
+        sl = lambda x: x[b:b + 1, :n]
+        kw = dict(bias=None if bias is None else bias[b:b + 1, :, :n, :n], causal=causal, dropout_p=p,
+                  dropout_seed=11, batch_offset=b)
+        ro, rl = blk.forward(sl(q), sl(k), sl(v), **kw)
+        assert (sl(out).float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
+        assert (lse[b:b + 1, :, :n] - rl).abs().max().item() <= LSE_TOL
+        rq, rk, rv = blk.backward(sl(do), sl(q), sl(k), sl(v), sl(out), lse[b:b + 1, :, :n],
+                                  out_dtype=torch.float32, **kw)
+        for name, mine, ref in (("dq", dq, rq), ("dk", dk, rk), ("dv", dv, rv)):
+            if n == 1 and name != "dv":     # one key: the weight is 1 whatever q and k are
+                assert sl(mine).float().abs().max().item() <= 1e-5 and ref.abs().max().item() <= 1e-5
+                continue
+            assert rel_l2(sl(mine), ref) <= GRAD_TOL, (name, b, rel_l2(sl(mine), ref))
+
+
+def test_seqlens_needs_equal_sequence_lengths():
+    J = _J()
+    q, k, v, _ = W.make_qkv(1, 128, 256, 2, 2, 64, torch.bfloat16)
+    with pytest.raises(AssertionError, match="QSeq != KSeq"):
+        J.fwd_attention_kernel_call(q.cuda(), k.cuda(), v.cuda(), seqlens=torch.tensor([5], dtype=torch.int32).cuda())
+
+
 @pytest.mark.parametrize("G", [1, 2, 4, 8])
 def test_gqa_groups(G):
     run_case(1, 256, 256, 8, 8 // G, 64, torch.float16, True)
