@@ -208,7 +208,7 @@ def main():
         return
 
     import jax_flash_attn2 as J
-    from jax_flash_attn2 import _capi
+    from jax_flash_attn2 import _capi, sharding
     import workloads as W
 
     rank = int(os.environ.get("RANK", "0"))
@@ -259,11 +259,7 @@ def main():
         torch.cuda.synchronize()
 
     def max_over_ranks(x: float) -> float:
-        if dist is None:
-            return x
-        t = torch.tensor([x], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return sharding.max_over_ranks(x, device="cuda")
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     f_fwd = flops_fwd(B, Sq, Sk, Hq, D, causal)

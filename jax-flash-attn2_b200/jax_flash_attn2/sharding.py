@@ -61,3 +61,39 @@ def slice_inputs(shard: Shard, group: int, q, k, v, *rest):
     others = tuple(x[b0:b1, :, h0 * group:h1 * group] for x in rest)
     kwargs = dict(batch_offset=b0, head_offset=h0 * group, heads_q_global=q.shape[2])
     return (qs, ks, vs, *others, kwargs)
+
+
+def max_over_ranks(value: float, device=None) -> float:
+    """Largest `value` over all ranks of the default process group (the timing rule for anything
+    measured on several GPUs); `value` itself when no process group is up."""
+    import torch
+    import torch.distributed as dist
+
+    if not (dist.is_available() and dist.is_initialized()):
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def gather_shards(shard: Shard, group: int, local: tp.Sequence, full_shapes: tp.Sequence[tp.Sequence[int]],
+                  kv_layout: tp.Sequence[bool]):
+    """Collects every rank's slices into full tensors on every rank (test and debugging aid; the
+    product path never needs it: outputs stay where their shard ran). `local[i]` is this rank's
+    slice of a [B, S, H, D] tensor whose full shape is `full_shapes[i]`; `kv_layout[i]` says
+    whether its head axis counts key/value heads (k, v, dk, dv) or query heads."""
+    import torch
+    import torch.distributed as dist
+
+    pieces = [None] * shard.world_size
+    mine = (shard, [x.cpu() for x in local])
+    if shard.world_size > 1:
+        dist.all_gather_object(pieces, mine)
+    else:
+        pieces = [mine]
+    full = [torch.zeros(tuple(shape), dtype=x.dtype) for shape, x in zip(full_shapes, local)]
+    for sh, tensors in pieces:
+        for dst, src, is_kv in zip(full, tensors, kv_layout):
+            g = 1 if is_kv else group
+            dst[sh.batch_start:sh.batch_stop, :, sh.kv_head_start * g:sh.kv_head_stop * g] = src
+    return full
