@@ -1,0 +1,174 @@
+"""JAX side of the XLA FFI binding: drop-in bodies for the reference's two launch functions.
+
+`_fwd_attention_kernel_call` / `_bwd_attention_kernel_call` below take the place of the functions
+of the same name in jax_flash_attn2/flash_attention_triton/_forward_triton.py:462-592 and
+_backward_triton.py:948-1173; `flash_attention_call` repeats the reference's custom_vjp
+(flash_attention_triton/_flash_attention.py:27-122) over them, and `sharded_flash_attention`
+spreads a call over a (batch, kv head) mesh with shard_map.
+
+NOT RUN WHERE THIS LIBRARY IS BUILT AND TESTED: JAX is not installed there. Importing this module
+without JAX raises ImportError at once; nothing else in the package imports it. The call sequence
+it issues is the one the tested torch / ctypes layer issues (jax_flash_attn2/_kernel_calls.py).
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+import math
+import os
+import typing as tp
+
+import jax  # noqa: E402  (ImportError here means: this optional module cannot be used)
+import jax.numpy as jnp
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_core = ctypes.CDLL(os.path.join(_HERE, "..", "libfa2_b200.so"), mode=ctypes.RTLD_GLOBAL)
+_shim = ctypes.CDLL(os.path.join(_HERE, "libfa2_b200_xla.so"))
+for _name in ("fa2_b200_fwd", "fa2_b200_bwd"):
+    jax.ffi.register_ffi_target(_name, jax.ffi.pycapsule(getattr(_shim, _name)), platform="CUDA")
+
+
+class _Problem(ctypes.Structure):   # fa2_problem of include/fa2_b200.h
+    _fields_ = [
+        ("batch", ctypes.c_int32), ("seqlen_q", ctypes.c_int32), ("seqlen_k", ctypes.c_int32),
+        ("heads_q", ctypes.c_int32), ("heads_kv", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("dtype", ctypes.c_int32), ("causal", ctypes.c_int32),
+        ("softmax_scale", ctypes.c_float), ("dropout_p", ctypes.c_float),
+        ("dropout_seed", ctypes.c_uint64),
+        ("batch_offset", ctypes.c_int32), ("head_offset", ctypes.c_int32),
+        ("heads_q_global", ctypes.c_int32),
+    ]
+
+
+_core.fa2_bwd_workspace_bytes.restype = ctypes.c_size_t
+_core.fa2_bwd_workspace_bytes.argtypes = [ctypes.POINTER(_Problem)]
+
+
+def _workspace_bytes(q_shape, k_shape, dtype) -> int:
+    p = _Problem()
+    p.batch, p.seqlen_q, p.heads_q, p.head_dim = (int(x) for x in q_shape)
+    p.seqlen_k, p.heads_kv = int(k_shape[1]), int(k_shape[2])
+    p.dtype = 1 if dtype == jnp.bfloat16 else 0
+    p.softmax_scale = 1.0
+    n = int(_core.fa2_bwd_workspace_bytes(ctypes.byref(p)))
+    if n == 0:
+        raise ValueError("fa2_b200: unsupported problem (head_dim, dtype or shape)")
+    return n
+
+
+def _operands(q, bias, attention_mask):
+    """(bias, additive mask, seqlens) with one-element dummies for what is absent. A 2-D
+    [B, S] attention_mask is a padding mask: it becomes per-batch lengths (real tokens first),
+    the reference's varlen mode without packing (_forward_triton.py:500-510)."""
+    dummy = jnp.zeros((1,), q.dtype)
+    seqlens = dummy
+    mask = dummy
+    if attention_mask is not None:
+        if attention_mask.ndim == 2:
+            seqlens = jnp.sum(attention_mask != 0, axis=1, dtype=jnp.int32)
+        elif jnp.issubdtype(attention_mask.dtype, jnp.floating):
+            mask = attention_mask
+        else:
+            mask = jnp.where(attention_mask != 0, 0.0, -jnp.inf).astype(q.dtype)
+    return (dummy if bias is None else bias), mask, seqlens
+
+
+def _attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, offsets):
+    return dict(
+        softmax_scale=np.float32(1.0 / math.sqrt(q.shape[-1]) if softmax_scale is None else softmax_scale),
+        dropout_p=np.float32(dropout_prob),
+        causal=bool(causal),
+        dropout_seed=np.int64(0 if dropout_seed is None else dropout_seed),
+        batch_offset=np.int32(offsets[0]),
+        head_offset=np.int32(offsets[1]),
+        heads_q_global=np.int32(offsets[2] or q.shape[2]),
+    )
+
+
+def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_scale=None,
+                               dropout_prob=0.0, causal=False, dropout_seed=None, varlen_mode=True,
+                               *, offsets=(0, 0, None)):
+    del varlen_mode
+    assert q.shape[2] % k.shape[2] == 0, f"nheads_q = {q.shape[2]} is not divisible by nheads_kv = {k.shape[2]}"
+    assert q.dtype == k.dtype == v.dtype, "All tensors must have the same type"
+    assert q.dtype in (jnp.float16, jnp.bfloat16), "Only support fp16 and bf16"
+    batch, sq, hq, _ = q.shape
+    bias_, mask_, seqlens = _operands(q, bias, attention_mask)
+    out_types = (
+        jax.ShapeDtypeStruct(q.shape, q.dtype),
+        jax.ShapeDtypeStruct((batch, hq, -(-sq // 128) * 128), jnp.float32),
+    )
+    return jax.ffi.ffi_call("fa2_b200_fwd", out_types)(
+        q, k, v, bias_, mask_, seqlens,
+        **_attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, offsets))
+
+
+def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_prob, causal,
+                               softmax_scale, dropout_seed, varlen_mode=True, *, offsets=(0, 0, None)):
+    del varlen_mode
+    bias_, mask_, seqlens = _operands(q, bias, attention_mask)
+    out_types = (
+        jax.ShapeDtypeStruct(q.shape, q.dtype),
+        jax.ShapeDtypeStruct(k.shape, k.dtype),
+        jax.ShapeDtypeStruct(v.shape, v.dtype),
+        jax.ShapeDtypeStruct((_workspace_bytes(q.shape, k.shape, q.dtype),), jnp.uint8),
+    )
+    dq, dk, dv, _ = jax.ffi.ffi_call("fa2_b200_bwd", out_types)(
+        dO, q, k, v, bias_, mask_, o, M, seqlens,
+        **_attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, offsets))
+    return dq, dk, dv
+
+
+@functools.partial(jax.custom_vjp, nondiff_argnums=(5, 6, 7, 8))
+def flash_attention_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed):
+    return _fwd_attention_kernel_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal,
+                                      dropout_seed)[0]
+
+
+def _vjp_fwd(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed):
+    out, lse = _fwd_attention_kernel_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob,
+                                          causal, dropout_seed)
+    return out, (q, k, v, bias, attention_mask, out, lse)
+
+
+def _vjp_bwd(softmax_scale, dropout_prob, causal, dropout_seed, residuals, dO):
+    q, k, v, bias, attention_mask, out, lse = residuals
+    dq, dk, dv = _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, out, lse, dropout_prob,
+                                            causal, softmax_scale, dropout_seed)
+    return dq, dk, dv, None, None
+
+
+flash_attention_call.defvjp(_vjp_fwd, _vjp_bwd)
+
+
+def sharded_flash_attention(q, k, v, *, causal=False, softmax_scale=None, dropout_prob=0.0,
+                            dropout_seed=None, mesh_shape: tp.Optional[tp.Tuple[int, int]] = None):
+    """One call spread over the local GPUs by (batch, kv head): every device runs the single-GPU
+    kernels on its slice, no collective is issued (the query heads of a kv head are contiguous, so
+    q's head axis shards consistently with k / v). The offsets keep the dropout bits those of the
+    unsharded call."""
+    from jax.experimental.shard_map import shard_map
+    from jax.sharding import Mesh, PartitionSpec as P
+
+    devices = jax.devices()
+    nb, nh = mesh_shape or (math.gcd(q.shape[0], len(devices)), len(devices) // math.gcd(q.shape[0], len(devices)))
+    mesh = Mesh(np.array(devices[: nb * nh]).reshape(nb, nh), ("b", "h"))
+    spec = P("b", None, "h", None)
+    hq_global = q.shape[2]
+    pb, ph = q.shape[0] // nb, q.shape[2] // nh
+
+    def local(q_, k_, v_):
+        # static offsets are needed by the FFI attributes, so every (b, h) position gets its own
+        # trace of the call; the mesh is small (at most the 8 GPUs of a box)
+        ib, ih = jax.lax.axis_index("b"), jax.lax.axis_index("h")
+        branches = [
+            functools.partial(
+                lambda qq, kk, vv, off: _fwd_attention_kernel_call(
+                    qq, kk, vv, None, None, softmax_scale, dropout_prob, causal, dropout_seed, offsets=off)[0],
+                off=(b * pb, h * ph, hq_global))
+            for b in range(nb) for h in range(nh)
+        ]
+        return jax.lax.switch(ib * nh + ih, branches, q_, k_, v_)
+
+    return shard_map(local, mesh, in_specs=(spec, spec, spec), out_specs=spec, check_rep=False)(q, k, v)
