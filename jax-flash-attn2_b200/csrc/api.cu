@@ -306,7 +306,9 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   const int q_rows = (D == 256) ? 64 : 128;
   const int dkv_blocks = (D == 256) ? 2 : D / 64;
   if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->q_strides, q_rows, "q")) ||
-      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k")) ||
+      // head dim 256: K is loaded in halves of the head dim (two 64-column blocks per copy)
+      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k",
+                      D == 256 ? 2 : 0)) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v")) ||
       (rc = make_tmap(&L.tmdO, a->d_o, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->do_strides, q_rows, "d_o")) ||
       (rc = make_tmap(&L.tmdK, a->dk, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->dk_strides, 128, "dk", dkv_blocks)) ||

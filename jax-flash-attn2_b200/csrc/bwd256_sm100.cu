@@ -31,20 +31,24 @@ constexpr int kRegsOther256 = 104;
 
 struct BSmem256 {
   static constexpr int kKVBytes = kBK * kD * 2;     // 64 KiB: 4 blocks of [128][64]
+  static constexpr int kKhBytes = kKVBytes / 2;     // 32 KiB: this CTA's half of K (2 blocks)
   static constexpr int kQBytes = kBQ * kD * 2;      // 32 KiB: 4 blocks of [64][64]
   static constexpr int kKBlock = kBK * 128;         // 16 KiB
   static constexpr int kQBlock = kBQ * 128;         // 8 KiB
   static constexpr int kdSBytes = kBK * kBQ * 2;    // 16 KiB: one [128][64] block
   static constexpr int kChunkBytes = 16 * 128 * 4;  // 16 query columns x 128 dims, fp32
+  // K: only the half of the head dim this CTA produces dQ for stays in shared memory; the other
+  // half (needed for S^T alone) is copied once into tensor memory and read from there as the A
+  // operand, which is what makes room for the second Q stage.
   static constexpr int kKOff = 0;
-  static constexpr int kVOff = kKOff + kKVBytes;
-  static constexpr int kQOff = kVOff + kKVBytes;
-  static constexpr int kdOOff = kQOff + kQBytes;
+  static constexpr int kVOff = kKOff + kKhBytes;
+  static constexpr int kQOff = kVOff + kKVBytes;            // 2 stages
+  static constexpr int kdOOff = kQOff + 2 * kQBytes;        // 1 stage
   static constexpr int kdSOff = kdOOff + kQBytes;
   static constexpr int kStageOff = kdSOff + kdSBytes;
-  static constexpr int kStatsOff = kStageOff + 2 * kChunkBytes;   // -lse*log2e [64], delta [64]
-  static constexpr int kBarOff = kStatsOff + 512;
-  static constexpr int kNumBars = 12;
+  static constexpr int kStatsOff = kStageOff + 2 * kChunkBytes;   // 2 stages x (-lse*log2e [64], delta [64])
+  static constexpr int kBarOff = kStatsOff + 2 * 512;
+  static constexpr int kNumBars = 16;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
@@ -108,7 +112,10 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t sQ = smem_base + L::kQOff, sdO = smem_base + L::kdOOff;
   const uint32_t sdS = smem_base + L::kdSOff, sStats = smem_base + L::kStatsOff;
   const uint32_t bars = smem_base + L::kBarOff;
-  const uint32_t bar_kv_full = bars, bar_q_full = bars + 8, bar_q_empty = bars + 16;
+  const uint32_t bar_kv_full = bars;
+  auto bar_q_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto bar_q_empty = [&](int s) { return bars + 8u * (12 + s); };
+  const uint32_t bar_kx_full = bars + 8u * 14, bar_kx_done = bars + 8u * 15;
   const uint32_t bar_do_full = bars + 24, bar_do_empty = bars + 32;
   const uint32_t bar_s_full = bars + 40, bar_p_full = bars + 48;
   const uint32_t bar_dp_full = bars + 56, bar_ds_full = bars + 64;
@@ -149,8 +156,12 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar_kv_full, 1);
-    mbar_init(bar_q_full, 1);
-    mbar_init(bar_q_empty, 1);
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(bar_q_full(st), 1);
+      mbar_init(bar_q_empty(st), 1);
+    }
+    mbar_init(bar_kx_full, 1);
+    mbar_init(bar_kx_done, 128);
     mbar_init(bar_do_full, 1);
     mbar_init(bar_do_empty, 1);
     mbar_init(bar_s_full, 1);
@@ -176,7 +187,8 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t kColS = 0, kColdP = 64, kColdQ = 128, kColdK = 256, kColdV = 384;
+  // tensor memory: S^T 64 | dP^T 64 | dQ^T 64 | other half of K (16 bit, 128 dims) 64 | dK 128 | dV 128
+  constexpr uint32_t kColS = 0, kColdP = 64, kColdQ = 128, kColKx = 192, kColdK = 256, kColdV = 384;
 
   auto step_coords = [&](int it, int& h, int& i) {
     const int g = it / nI;
@@ -190,21 +202,28 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 13) {
     // =========================== TMA producer ================================================
     if (lane == 0 && T > 0) {
-      mbar_arrive_expect_tx(bar_kv_full, 2 * L::kKVBytes);
-      tma_load_5d(sK, &tmK, bar_kv_full, 0, n * kBK, 0, hk, b);
+      // K arrives in halves of the head dim (the K map's box is two 64-column blocks): this
+      // CTA's half stays in its own buffer, the other half lands in the second Q stage, from
+      // where the P/dS warps move it into tensor memory before that stage is first used.
+      mbar_arrive_expect_tx(bar_kv_full, L::kKhBytes + L::kKVBytes);
+      tma_load_5d(sK, &tmK, bar_kv_full, 0, n * kBK, 2 * half, hk, b);
       tma_load_5d(sV, &tmV, bar_kv_full, 0, n * kBK, 0, hk, b);
+      mbar_arrive_expect_tx(bar_kx_full, L::kKhBytes);
+      tma_load_5d(sQ + L::kQBytes, &tmK, bar_kx_full, 0, n * kBK, 2 * (1 - half), hk, b);
       bool ok = true;
       for (int it = 0; it < T && ok; ++it) {
+        const int stg = it & 1;
         int h, i;
         step_coords(it, h, i);
-        ok = mbar_wait(bar_q_empty, (it & 1) ^ 1, abort_flag);
+        if (it == 1) ok = mbar_wait(bar_kx_done, 0, abort_flag);   // stage 1 no longer holds K
+        if (ok) ok = mbar_wait(bar_q_empty(stg), ((it >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_q_full, L::kQBytes + 512);
-        tma_load_5d(sQ, &tmQ, bar_q_full, 0, i * kBQ, 0, h, b);
+        mbar_arrive_expect_tx(bar_q_full(stg), L::kQBytes + 512);
+        tma_load_5d(sQ + stg * L::kQBytes, &tmQ, bar_q_full(stg), 0, i * kBQ, 0, h, b);
         const float* st =
             stats + ((static_cast<long long>(b) * p.Hq + h) * nQ128 + (i >> 1)) * 256 + (i & 1) * 64;
-        bulk_load_1d(sStats, st, 256, bar_q_full);
-        bulk_load_1d(sStats + 256, st + 128, 256, bar_q_full);
+        bulk_load_1d(sStats + stg * 512, st, 256, bar_q_full(stg));
+        bulk_load_1d(sStats + stg * 512 + 256, st + 128, 256, bar_q_full(stg));
         ok = mbar_wait(bar_do_empty, (it & 1) ^ 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(bar_do_full, L::kQBytes);
@@ -219,13 +238,13 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t idesc_s = make_idesc(kBf16, 128, kBQ, false, false);
       constexpr uint32_t idesc_dkv = make_idesc(kBf16, 128, 128, false, true);
       constexpr uint32_t idesc_dq = make_idesc(kBf16, 128, kBQ, true, true);
-      const uint64_t dK_k = make_sdesc(sK, 16, 1024), dV_k = make_sdesc(sV, 16, 1024);
-      const uint64_t dQ_k = make_sdesc(sQ, 16, 1024), ddO_k = make_sdesc(sdO, 16, 1024);
+      const uint64_t dKh_k = make_sdesc(sK, 16, 1024), dV_k = make_sdesc(sV, 16, 1024);
+      const uint64_t dQ_k0 = make_sdesc(sQ, 16, 1024), ddO_k = make_sdesc(sdO, 16, 1024);
       // halves of Q / dO as MN-major B operands: two 64-dim blocks, L::kQBlock apart
-      const uint64_t dQ_mn = make_sdesc(sQ + 2 * half * L::kQBlock, L::kQBlock, 1024);
+      const uint64_t dQ_mn0 = make_sdesc(sQ + 2 * half * L::kQBlock, L::kQBlock, 1024);
       const uint64_t ddO_mn = make_sdesc(sdO + 2 * half * L::kQBlock, L::kQBlock, 1024);
-      // half of K as MN-major A operand (M = head dim): two 64-dim blocks, L::kKBlock apart
-      const uint64_t dKh_mn = make_sdesc(sK + 2 * half * L::kKBlock, L::kKBlock, 1024);
+      // this CTA's half of K as MN-major A operand (M = head dim): two 64-dim blocks
+      const uint64_t dKh_mn = make_sdesc(sK, L::kKBlock, 1024);
       const uint64_t ddS_k = make_sdesc(sdS, 16, 1024), ddS_mn = make_sdesc(sdS, 16, 1024);
       bool ok = true;
 
@@ -249,10 +268,28 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                  (first && k == 0) ? 0u : 1u);
         }
       };
-      auto issue_dk = [&](bool first) {
+      // S^T[key, query] over the full head dim: this CTA's half of K from shared memory, the
+      // other half from tensor memory (8 columns per 16 dims)
+      auto issue_s = [&](int stg) {
+        const uint64_t q_k = sdesc_advance(dQ_k0, stg * L::kQBytes);
+#pragma unroll
+        for (int k = 0; k < kD / 32; ++k) {
+          const uint32_t offa = (k >> 2) * L::kKBlock + (k & 3) * 32;
+          const uint32_t offb = (2 * half + (k >> 2)) * L::kQBlock + (k & 3) * 32;
+          mma_ss_e(tmem_base + kColS, sdesc_advance(dKh_k, offa), sdesc_advance(q_k, offb), idesc_s,
+                 k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < kD / 32; ++k) {
+          const uint32_t offb = (2 * (1 - half) + (k >> 2)) * L::kQBlock + (k & 3) * 32;
+          mma_ts_e(tmem_base + kColS, tmem_base + kColKx + 8 * k, sdesc_advance(q_k, offb), idesc_s, 1u);
+        }
+      };
+      auto issue_dk = [&](int stg, bool first) {
+        const uint64_t q_mn = sdesc_advance(dQ_mn0, stg * L::kQBytes);
 #pragma unroll
         for (int k = 0; k < kBQ / 16; ++k)
-          mma_ss_e(tmem_base + kColdK, sdesc_advance(ddS_k, k * 32), sdesc_advance(dQ_mn, k * 2048),
+          mma_ss_e(tmem_base + kColdK, sdesc_advance(ddS_k, k * 32), sdesc_advance(q_mn, k * 2048),
                  idesc_dkv, (first && k == 0) ? 0u : 1u);
       };
       auto issue_dq = [&]() {
@@ -263,10 +300,11 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       };
 
       ok = mbar_wait_warp(bar_kv_full, 0, abort_flag);
-      if (ok) ok = mbar_wait_warp(bar_q_full, 0, abort_flag);
+      if (ok) ok = mbar_wait_warp(bar_kx_done, 0, abort_flag);   // the other half of K is in tensor memory
+      if (ok) ok = mbar_wait_warp(bar_q_full(0), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        issue_kd(kColS, dK_k, dQ_k);
+        issue_s(0);
         mma_commit_e(bar_s_full);
         ok = mbar_wait_warp(bar_do_full, 0, abort_flag);
       }
@@ -277,25 +315,31 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       for (int it = 0; it < T && ok; ++it) {
         const uint32_t par = it & 1;
+        const int stg = it & 1, nxt = stg ^ 1;
+        const bool has_next = it + 1 < T;
         ok = mbar_wait_warp(bar_p_full, par, abort_flag);
         if (!ok) break;
         tc_fence_after();
         issue_dv(it == 0);
         mma_commit_e(bar_do_empty);
+        if (has_next) {
+          // S^T of the next step runs while the P/dS warps are still busy with dS of this one; it
+          // is issued behind dV, which is the last reader of the P^T columns it overwrites
+          ok = mbar_wait_warp(bar_q_full(nxt), ((it + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(nxt);
+          mma_commit_e(bar_s_full);
+        }
         ok = mbar_wait_warp(bar_ds_full, par, abort_flag);
         if (ok && it > 0) ok = mbar_wait_warp(bar_dq_drained, (it - 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         issue_dq();
         mma_commit_e(bar_dq_full);
-        issue_dk(it == 0);
-        mma_commit_e(bar_q_empty);
-        if (it + 1 < T) {
-          ok = mbar_wait_warp(bar_q_full, (it + 1) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          issue_kd(kColS, dK_k, dQ_k);
-          mma_commit_e(bar_s_full);
+        issue_dk(stg, it == 0);
+        mma_commit_e(bar_q_empty(stg));
+        if (has_next) {
           ok = mbar_wait_warp(bar_do_full, (it + 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
@@ -359,17 +403,47 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + kColS + 32 * w;
     const uint32_t tdP = tmem_base + lane_base + kColdP + 32 * w;
-    const float4* nlse4 = reinterpret_cast<const float4*>(smem_gen + L::kStatsOff) + 8 * w;
-    const float4* delta4 = nlse4 + 16;
     uint8_t* ds_row = smem_gen + L::kdSOff + r * 128;
     const float do_scale = kBf16 ? 1.f : do_scale_from_bits(p.do_absmax_bits);
     bool ok = true;
 
-    for (int it = 0; it < T; ++it) {
+    if (w == 0 && T > 0) {
+      // One-time: the half of K that landed in the second Q stage goes into tensor memory, one key
+      // row per thread (= lane), two 16-bit values per column in head-dim order: the layout of
+      // a 16-bit A operand (the same one P^T is written in).
+      ok = mbar_wait(bar_kx_full, 0, abort_flag);
+      if (ok) {
+        const uint8_t* src = smem_gen + L::kQOff + L::kQBytes;
+        uint32_t kx[64];
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 v4 = *reinterpret_cast<const uint4*>(src + blk * L::kKBlock + r * 128 +
+                                                             ((j ^ (r & 7)) << 4));
+            kx[blk * 32 + 4 * j + 0] = v4.x;
+            kx[blk * 32 + 4 * j + 1] = v4.y;
+            kx[blk * 32 + 4 * j + 2] = v4.z;
+            kx[blk * 32 + 4 * j + 3] = v4.w;
+          }
+        }
+        const uint32_t tKx = tmem_base + lane_base + kColKx;
+        tmem_st32(tKx, reinterpret_cast<const uint32_t(&)[32]>(kx[0]));
+        tmem_st32(tKx + 32, reinterpret_cast<const uint32_t(&)[32]>(kx[32]));
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_kx_done);
+      }
+    }
+
+    for (int it = 0; it < T && ok; ++it) {
+      const int stg = it & 1;
       int h, i;
       step_coords(it, h, i);
       const int q_first = i * kBQ + 32 * w;
-      ok = mbar_wait(bar_q_full, it & 1, abort_flag);
+      const float4* nlse4 = reinterpret_cast<const float4*>(smem_gen + L::kStatsOff + stg * 512) + 8 * w;
+      const float4* delta4 = nlse4 + 16;
+      ok = mbar_wait(bar_q_full(stg), (it >> 1) & 1, abort_flag);
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
