@@ -63,7 +63,11 @@ typedef struct {
   int32_t dtype;              /* fa2_dtype of q, k, v, o, do, dq, dk, dv                     */
   int32_t causal;             /* bottom-right aligned when seqlen_q != seqlen_k              */
   float softmax_scale;        /* multiplies q.k ; callers default it to 1/sqrt(head_dim)     */
-  float dropout_p;            /* probability of dropping an attention weight, [0, 1)         */
+  float dropout_p;            /* probability of dropping an attention weight, [0, 1),
+                                 realised in steps of 2^-16                                   */
+  /* Philox-4x32-10 key. Counter (key_index / 8, query_index, batch * heads_q_global + head, 0);
+   * output word (key_index % 8) / 2 carries the 16-bit draw of an even key in its low half and of
+   * the following key in its high half; a weight is kept iff draw >= round(dropout_p * 65536). */
   uint64_t dropout_seed;
   /* A sharded caller passes the global position of its slice so that every shard draws the
    * dropout bits the unsharded call would draw. */

@@ -164,8 +164,9 @@ void make_dropout(DropoutDev* d, const fa2_problem& p) {
   d->enabled = p.dropout_p > 0.f;
   d->inv_keep = 1.f;
   if (!d->enabled) return;
-  const double thr = std::floor(static_cast<double>(p.dropout_p) * 4294967296.0 + 0.5);
-  d->threshold = thr >= 4294967295.0 ? 0xffffffffu : static_cast<uint32_t>(thr);
+  // 16-bit draws: the drop probability is realised in steps of 2^-16
+  const double thr = std::floor(static_cast<double>(p.dropout_p) * 65536.0 + 0.5);
+  d->threshold = thr >= 65535.0 ? 65535u : static_cast<uint32_t>(thr);
   d->inv_keep = static_cast<float>(1.0 / (1.0 - static_cast<double>(p.dropout_p)));
   d->seed_lo = static_cast<uint32_t>(p.dropout_seed & 0xffffffffu);
   d->seed_hi = static_cast<uint32_t>(p.dropout_seed >> 32);

@@ -16,6 +16,7 @@
 // dQ staging 2 x 8 KiB.
 #include "bwd_common.cuh"
 #include "bwd_launch.cuh"
+#include "launch_util.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fa2 {
@@ -605,8 +606,8 @@ template <bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch256_main(const BwdLaunch& a, cudaStream_t stream) {
   using L = BSmem256;
   auto kern = bwd256_main_kernel<kBf16, kCausal, kFeat>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  static bool smem_opted_in[64] = {};
+  cudaError_t e = opt_in_dynamic_smem(kern, L::kDynamicBytes, smem_opted_in);
   if (e != cudaSuccess) return e;
   const long long nblocks = 2LL * a.kp.n_kvblk * a.kp.B * a.kp.Hkv;
   kern<<<static_cast<unsigned>(nblocks), kThreads256, L::kDynamicBytes, stream>>>(

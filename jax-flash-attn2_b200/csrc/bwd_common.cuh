@@ -38,31 +38,36 @@ __device__ __forceinline__ float do_scale_from_bits(const unsigned* bits) {
 }
 
 // Dropout keep bits of one key row (this thread) for kCols consecutive query columns, in the
-// backward's transposed layout. The Philox counter covers four adjacent keys of one query
-// (counter = (key/4, query, batch*Hq+head, 0), draw = output[key%4]), which suits the forward
-// (one thread owns a query row) but would make every backward thread throw away three of its
-// four draws. Instead the four lanes that share key/4 each draw for a different query of a group
-// of four and exchange the resulting bits with warp votes. All 32 lanes must call this together;
-// the key index of lane l must be a multiple of 4 plus (l % 4).
+// backward's transposed layout. One Philox call covers eight adjacent keys of one query
+// (counter = (key/8, query, batch*Hq+head, 0); output word (key%8)/2 holds the 16-bit draws of an
+// even key in its low half and of the next key in its high half), which suits the forward (one
+// thread owns a query row) but would make every backward thread throw away seven of its eight
+// draws. Instead the eight lanes that share key/8 each draw for a different query of a group of
+// eight and exchange the resulting bits with warp votes. All 32 lanes must call this together;
+// the key index of lane l must be a multiple of 8 plus (l % 8).
 template <int kCols>
 __device__ __forceinline__ void dropout_keep_bits_transposed(const DropoutDev& d, uint32_t bh_glob,
                                                              int kv, int q_first, int lane,
                                                              uint32_t (&bits)[kCols / 32]) {
-  const int member = lane & 3;
+  const int member = lane & 7;
 #pragma unroll
   for (int w = 0; w < kCols / 32; ++w) bits[w] = 0u;
 #pragma unroll
-  for (int m = 0; m < kCols / 4; ++m) {
+  for (int m = 0; m < kCols / 8; ++m) {
     uint32_t rnd[4];
-    philox4x32_10(static_cast<uint32_t>(kv >> 2), static_cast<uint32_t>(q_first + 4 * m + member),
+    philox4x32_10(static_cast<uint32_t>(kv >> 3), static_cast<uint32_t>(q_first + 8 * m + member),
                   bh_glob, 0u, d.seed_lo, d.seed_hi, rnd);
-    // vote[k]: bit l says whether key (4*(l/4) + k) keeps query 4m + (l%4)
-    uint32_t vote[4];
+    // vote k: bit l says whether key (8*(l/8) + k) keeps query 8m + (l%8); this lane keeps the
+    // vote about its own key
+    uint32_t mine = 0u;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) vote[k] = __ballot_sync(0xffffffffu, rnd[k] >= d.threshold);
-    const uint32_t mine = member == 0 ? vote[0] : member == 1 ? vote[1] : member == 2 ? vote[2] : vote[3];
-    const uint32_t four = (mine >> (lane & ~3)) & 0xfu;     // queries 4m .. 4m+3 for this key
-    bits[(4 * m) >> 5] |= four << ((4 * m) & 31);
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t draw = (k & 1) ? (rnd[k >> 1] >> 16) : (rnd[k >> 1] & 0xffffu);
+      const uint32_t vote = __ballot_sync(0xffffffffu, draw >= d.threshold);
+      if (member == k) mine = vote;
+    }
+    const uint32_t eight = (mine >> (lane & ~7)) & 0xffu;    // queries 8m .. 8m+7 for this key
+    bits[(8 * m) >> 5] |= eight << ((8 * m) & 31);
   }
 }
 

@@ -20,6 +20,7 @@
 //   3. bwd_dq_convert   : fp32 dq accumulator (tiled layout) * scale -> dq in the input dtype.
 #include "bwd_common.cuh"
 #include "bwd_launch.cuh"
+#include "launch_util.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fa2 {
@@ -658,8 +659,8 @@ template <int D, bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch_main(const BwdLaunch& a, cudaStream_t stream) {
   using L = BwdSmem<D>;
   auto kern = bwd_main_kernel<D, kBf16, kCausal, kFeat>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  static bool smem_opted_in[64] = {};
+  cudaError_t e = opt_in_dynamic_smem(kern, L::kDynamicBytes, smem_opted_in);
   if (e != cudaSuccess) return e;
   const long long nblocks = static_cast<long long>(a.kp.n_kvblk) * a.kp.B * a.kp.Hkv;
   kern<<<static_cast<unsigned>(nblocks), BwdRoles<D>::kThreads, L::kDynamicBytes, stream>>>(

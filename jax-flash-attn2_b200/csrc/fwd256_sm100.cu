@@ -12,6 +12,7 @@
 // Shared memory: Q 64 KiB + K slot 64 KiB + V slot 64 KiB.
 #include "fwd_launch.cuh"
 #include "fwd_row.cuh"
+#include "launch_util.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fa2 {
@@ -243,8 +244,8 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 template <bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch256_one(const FwdLaunch& a, cudaStream_t stream) {
   auto kern = fwd256_kernel<kBf16, kCausal, kFeat>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Smem256::kDynamicBytes);
+  static bool smem_opted_in[64] = {};
+  cudaError_t e = opt_in_dynamic_smem(kern, Smem256::kDynamicBytes, smem_opted_in);
   if (e != cudaSuccess) return e;
   const long long nblocks =
       static_cast<long long>((a.kp.Sq + kBM - 1) / kBM) * a.kp.B * a.kp.Hq;

@@ -21,6 +21,7 @@
 // so the next item's first MMAs overlap the epilogue (O -> shared memory -> TMA store) of this one.
 #include "fwd_launch.cuh"
 #include "fwd_row.cuh"
+#include "launch_util.cuh"
 #include "ptx_sm100.cuh"
 
 namespace fa2 {
@@ -436,8 +437,8 @@ template <int D, bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch_one(const FwdLaunch& a, cudaStream_t stream) {
   using L = FwdSmem<D>;
   auto kern = fwd_kernel<D, kBf16, kCausal, kFeat>;
-  cudaError_t e =
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  static bool smem_opted_in[64] = {};
+  cudaError_t e = opt_in_dynamic_smem(kern, L::kDynamicBytes, smem_opted_in);
   if (e != cudaSuccess) return e;
   const long long items = static_cast<long long>(a.kp.n_qblk) * a.kp.B * a.kp.Hq;
   if (items <= 0) return cudaSuccess;

@@ -13,7 +13,7 @@ struct ScoreTermDev {
 };
 
 struct DropoutDev {
-  uint32_t threshold;   // keep an element iff its 32-bit draw >= threshold
+  uint32_t threshold;   // keep an element iff its 16-bit draw >= threshold (0 .. 65535)
   float inv_keep;       // 1 / (1 - p)
   uint32_t seed_lo, seed_hi;
   int b_off, h_off, hq_global;

@@ -20,6 +20,28 @@ from . import _capi
 _DTYPE_CODE = {torch.float16: _capi.FA2_FP16, torch.bfloat16: _capi.FA2_BF16, torch.float32: _capi.FA2_FP32}
 
 
+_raw_stream_fn = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _launch(fn, params, device: torch.device) -> None:
+    """Calls one C-ABI entry point on torch's current stream of `device`. The device is only
+    switched when it is not the current one, and the stream handle is taken through the raw
+    accessor when torch has it: for small problems the host side of a call is what one waits for."""
+    index = device.index
+    current = torch.cuda.current_device()
+    if index is None:
+        index = current
+    if index != current:
+        with torch.cuda.device(index):
+            _launch(fn, params, device)
+        return
+    if _raw_stream_fn is not None:
+        stream = _raw_stream_fn(index)
+    else:
+        stream = torch.cuda.current_stream(index).cuda_stream
+    _capi.check(fn(C.byref(params), C.c_void_p(stream)))
+
+
 def _strides(x: torch.Tensor) -> _capi.Strides:
     """(batch, sequence, head) element strides of a [B, S, H, D] tensor."""
     return _capi.Strides(x.stride(0), x.stride(1), x.stride(2))
@@ -185,9 +207,7 @@ def fwd_attention_kernel_call(
     a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias")
     a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
-    with torch.cuda.device(q.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        _capi.check(lib.fa2_fwd(C.byref(a), C.c_void_p(stream)))
+    _launch(lib.fa2_fwd, a, q.device)
     return out, lse
 
 
@@ -242,9 +262,7 @@ def bwd_attention_kernel_call(
     a.dv, a.dv_strides = dv.data_ptr(), _strides(dv)
     a.workspace, a.workspace_bytes = workspace.data_ptr(), nbytes
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
-    with torch.cuda.device(q.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        _capi.check(lib.fa2_bwd(C.byref(a), C.c_void_p(stream)))
+    _launch(lib.fa2_bwd, a, q.device)
     return dq, dk, dv
 
 

@@ -6,10 +6,14 @@ SC'11), restated in numpy. The reference draws its dropout bits with Triton's `t
 bit-equality with Triton's stream is not a requirement of the build, reproducibility from the
 seed is. The mapping used by the CUDA kernels and restated here:
 
-    counter = (key_index // 4, query_index, batch * heads_q_global + head, 0)
+    counter = (key_index // 8, query_index, batch * heads_q_global + head, 0)
     key     = (seed & 0xffffffff, seed >> 32)
-    draw    = output[key_index % 4]
-    keep    = draw >= round(p * 2**32)
+    word    = output[(key_index % 8) // 2]
+    draw    = word & 0xffff if key_index is even else word >> 16        (16 bits)
+    keep    = draw >= min(round(p * 2**16), 65535)
+
+One call thus serves eight adjacent keys of a query row, and the drop probability is realised in
+steps of 2**-16.
 
 Only tests, the smoke check and the CPU-baseline leg of the benchmark may import this module.
 """
@@ -42,8 +46,8 @@ def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
 
 
 def dropout_threshold(p: float) -> int:
-    thr = int(np.floor(float(np.float32(p)) * 4294967296.0 + 0.5))
-    return min(thr, 0xFFFFFFFF)
+    thr = int(np.floor(float(np.float32(p)) * 65536.0 + 0.5))
+    return min(thr, 0xFFFF)
 
 
 def keep_mask(seed: int, p: float, batch: int, heads: int, sq: int, sk: int,
@@ -52,14 +56,17 @@ def keep_mask(seed: int, p: float, batch: int, heads: int, sq: int, sk: int,
     hq_glob = heads if heads_q_global is None else heads_q_global
     k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
     thr = np.uint32(dropout_threshold(p))
-    n4 = (sk + 3) // 4
-    out = np.empty((batch, heads, sq, n4 * 4), dtype=bool)
-    c0 = np.arange(n4, dtype=np.uint32)[None, :]
+    n8 = (sk + 7) // 8
+    out = np.empty((batch, heads, sq, n8 * 8), dtype=bool)
+    c0 = np.arange(n8, dtype=np.uint32)[None, :]
     c1 = np.arange(sq, dtype=np.uint32)[:, None]
     for b in range(batch):
         for h in range(heads):
             bh = (batch_offset + b) * hq_glob + head_offset + h
             r = philox4x32_10(c0, c1, np.uint32(bh), np.uint32(0), k0, k1)
-            draws = np.stack(r, axis=-1).reshape(sq, n4 * 4)
+            halves = []
+            for word in r:                       # key % 8 = 2 * word index + (0: low, 1: high half)
+                halves += [word & np.uint32(0xFFFF), word >> np.uint32(16)]
+            draws = np.stack(halves, axis=-1).reshape(sq, n8 * 8)
             out[b, h] = draws >= thr
     return out[..., :sk]
