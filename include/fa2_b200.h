@@ -92,6 +92,12 @@ typedef struct {
    * 500-510) without its pack / unpack copies (_utils.py:196-294); values are clamped to
    * [0, seqlen_q]. */
   const int32_t* seqlens;
+  /* Optional (NULL = absent): the 64-bit dropout seed at a device address (8-byte aligned). When
+   * given, the kernels read the seed from there and p.dropout_seed is ignored, so a seed that only
+   * exists on the device (the reference passes it as a traced operand,
+   * flash_attention_triton/_flash_attention.py:91-92; _forward_triton.py:554) needs no host copy and
+   * a new seed never changes the launch. */
+  const uint64_t* dropout_seed_dev;
 } fa2_fwd_params;
 
 typedef struct {
@@ -113,6 +119,7 @@ typedef struct {
    * Rows of dq, dk and dv past a batch element's length are written as zeros and its d_o rows
    * past it are never read (_backward_triton.py:973-1025, 1163-1171). */
   const int32_t* seqlens;
+  const uint64_t* dropout_seed_dev;            /* optional device-resident seed, see above        */
 } fa2_bwd_params;
 
 /* Forward: o = softmax(scale q k^T + bias + mask [causal]) v with dropout on the weights, and

@@ -201,7 +201,7 @@ using namespace fa2;
 
 extern "C" {
 
-int fa2_version(void) { return 1001; }
+int fa2_version(void) { return 1002; }
 
 const char* fa2_last_error(void) { return g_err; }
 
@@ -261,6 +261,9 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
   kp.seqlens = a->seqlens;
+  if (a->dropout_seed_dev && (reinterpret_cast<uintptr_t>(a->dropout_seed_dev) & 7))
+    return fail(FA2_ERR_INVALID_ARG, "dropout_seed_dev must be 8-byte aligned");
+  kp.drop.seed_dev = reinterpret_cast<const unsigned long long*>(a->dropout_seed_dev);
   kp.n_qblk = (p.seqlen_q + 255) / 256;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
@@ -341,6 +344,9 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
   kp.seqlens = a->seqlens;
+  if (a->dropout_seed_dev && (reinterpret_cast<uintptr_t>(a->dropout_seed_dev) & 7))
+    return fail(FA2_ERR_INVALID_ARG, "dropout_seed_dev must be 8-byte aligned");
+  kp.drop.seed_dev = reinterpret_cast<const unsigned long long*>(a->dropout_seed_dev);
   kp.n_kvblk = (p.seqlen_k + 127) / 128;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");

@@ -11,8 +11,12 @@
 //   * a step covers 64 query rows: S^T = K Q^T and dP^T = V dO^T are [128 keys x 64 queries];
 //   * dQ is produced transposed, dQ^T[:, half] = K[:, half]^T dS^T ([128 dims x 64 queries]), so
 //     that every MMA keeps M = 128.
-// Tensor memory: S^T 64 | dP^T 64 | dQ^T 64 | free 64 | dK_half 128 | dV_half 128.
-// Shared memory: K 64 KiB, V 64 KiB, Q 32 KiB, dO 32 KiB (single buffers), dS^T 16 KiB,
+//   * only the CTA's own half of K stays in shared memory (it is the MN-major A operand of
+//     dQ^T); the other half, which S^T alone contracts over, is copied once into tensor memory
+//     and read from there (TS MMAs). That makes room for a second Q stage, so S^T of the next
+//     step overlaps the dS phase of the current one.
+// Tensor memory: S^T 64 | dP^T 64 | dQ^T 64 | other half of K 64 | dK_half 128 | dV_half 128.
+// Shared memory: K half 32 KiB, V 64 KiB, Q 2 x 32 KiB, dO 32 KiB (single buffer), dS^T 16 KiB,
 // dQ staging 2 x 8 KiB.
 #include "bwd_common.cuh"
 #include "bwd_launch.cuh"

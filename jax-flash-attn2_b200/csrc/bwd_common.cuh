@@ -50,13 +50,15 @@ __device__ __forceinline__ void dropout_keep_bits_transposed(const DropoutDev& d
                                                              int kv, int q_first, int lane,
                                                              uint32_t (&bits)[kCols / 32]) {
   const int member = lane & 7;
+  uint32_t key_lo, key_hi;
+  dropout_key(d, key_lo, key_hi);
 #pragma unroll
   for (int w = 0; w < kCols / 32; ++w) bits[w] = 0u;
 #pragma unroll
   for (int m = 0; m < kCols / 8; ++m) {
     uint32_t rnd[4];
     philox4x32_10(static_cast<uint32_t>(kv >> 3), static_cast<uint32_t>(q_first + 8 * m + member),
-                  bh_glob, 0u, d.seed_lo, d.seed_hi, rnd);
+                  bh_glob, 0u, key_lo, key_hi, rnd);
     // vote k: bit l says whether key (8*(l/8) + k) keeps query 8m + (l%8); this lane keeps the
     // vote about its own key
     uint32_t mine = 0u;

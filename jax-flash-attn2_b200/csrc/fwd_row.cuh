@@ -179,13 +179,15 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
       if (p.drop.enabled) {
         const uint32_t bh_glob = static_cast<uint32_t>(
             (p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
-#pragma unroll
+        uint32_t key_lo, key_hi;
+        dropout_key(p.drop, key_lo, key_hi);
         // one Philox call covers eight adjacent keys of this row: each 32-bit output word
         // holds two 16-bit draws, the lower key in the low half
+#pragma unroll
         for (int c = half * kPCols; c < (half + 1) * kPCols; c += 8) {
           uint32_t rnd[4];
           philox4x32_10(static_cast<uint32_t>((kv0 + c) >> 3), static_cast<uint32_t>(qi),
-                        bh_glob, 0u, p.drop.seed_lo, p.drop.seed_hi, rnd);
+                        bh_glob, 0u, key_lo, key_hi, rnd);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if ((rnd[k] & 0xffffu) < p.drop.threshold) x[c + 2 * k] = 0.f;

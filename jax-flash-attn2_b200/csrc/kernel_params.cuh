@@ -16,9 +16,23 @@ struct DropoutDev {
   uint32_t threshold;   // keep an element iff its 16-bit draw >= threshold (0 .. 65535)
   float inv_keep;       // 1 / (1 - p)
   uint32_t seed_lo, seed_hi;
+  // optional: the 64-bit seed is read from this device address instead (a seed that only exists
+  // on the device, e.g. a traced value of the calling framework)
+  const unsigned long long* seed_dev;
   int b_off, h_off, hq_global;
   int enabled;
 };
+
+// The Philox key of a call: (low, high) half of the seed.
+__device__ __forceinline__ void dropout_key(const DropoutDev& d, uint32_t& lo, uint32_t& hi) {
+  lo = d.seed_lo;
+  hi = d.seed_hi;
+  if (d.seed_dev != nullptr) {
+    const unsigned long long s = __ldg(d.seed_dev);
+    lo = static_cast<uint32_t>(s);
+    hi = static_cast<uint32_t>(s >> 32);
+  }
+}
 
 struct FwdKernelParams {
   int B, Sq, Sk, Hq, Hkv, G;

@@ -75,6 +75,7 @@ class FwdParams(C.Structure):
         ("bias", ScoreTerm),
         ("mask", ScoreTerm),
         ("seqlens", C.c_void_p),
+        ("dropout_seed_dev", C.c_void_p),
     ]
 
 
@@ -96,6 +97,7 @@ class BwdParams(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("seqlens", C.c_void_p),
+        ("dropout_seed_dev", C.c_void_p),
     ]
 
 

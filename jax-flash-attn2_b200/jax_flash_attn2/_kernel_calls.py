@@ -137,6 +137,19 @@ def _seqlens_ptr(seqlens: tp.Optional[torch.Tensor], q: torch.Tensor, sk: int):
     return seqlens.data_ptr(), seqlens
 
 
+def _seed_ptr(dropout_seed, q: torch.Tensor):
+    """A seed given as a one-element int64 / uint64 CUDA tensor stays on the device: the kernels
+    read it there (no host synchronisation). Returns (device pointer or None, tensor kept alive)."""
+    if not isinstance(dropout_seed, torch.Tensor):
+        return None, None
+    if dropout_seed.numel() != 1 or dropout_seed.dtype not in (torch.int64, torch.uint64):
+        raise ValueError("a tensor dropout_seed must hold one int64 / uint64 value")
+    if dropout_seed.device != q.device:
+        raise ValueError("a tensor dropout_seed must live on the device of q")
+    dropout_seed = dropout_seed.contiguous()
+    return dropout_seed.data_ptr(), dropout_seed
+
+
 def _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offset, head_offset, heads_q_global):
     batch, sq, hq, d = q.shape
     _, sk, hkv, _ = k.shape
@@ -147,7 +160,10 @@ def _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offs
     p.causal = int(bool(causal))
     p.softmax_scale = float(1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale)
     p.dropout_p = float(dropout_prob)
-    p.dropout_seed = int(0 if dropout_seed is None else dropout_seed) & 0xFFFFFFFFFFFFFFFF
+    if isinstance(dropout_seed, torch.Tensor):
+        p.dropout_seed = 0           # read on the device, see _seed_ptr
+    else:
+        p.dropout_seed = int(0 if dropout_seed is None else dropout_seed) & 0xFFFFFFFFFFFFFFFF
     p.batch_offset = int(batch_offset)
     p.head_offset = int(head_offset)
     p.heads_q_global = int(hq if heads_q_global is None else heads_q_global)
@@ -207,6 +223,7 @@ def fwd_attention_kernel_call(
     a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias")
     a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
+    a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
     _launch(lib.fa2_fwd, a, q.device)
     return out, lse
 
@@ -262,6 +279,7 @@ def bwd_attention_kernel_call(
     a.dv, a.dv_strides = dv.data_ptr(), _strides(dv)
     a.workspace, a.workspace_bytes = workspace.data_ptr(), nbytes
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
+    a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
     _launch(lib.fa2_bwd, a, q.device)
     return dq, dk, dv
 

@@ -89,12 +89,22 @@ const int32_t* SeqlensOrNull(const ffi::AnyBuffer& x, int32_t batch) {
   return static_cast<const int32_t*>(x.untyped_data());
 }
 
+// Dropout seed as an operand: two uint32 words (low, high) or one 64-bit integer, read by the
+// kernels on the device, so that a traced seed never re-specialises the call. Anything else (the
+// caller's one-element dummy of the q dtype) means "absent": the dropout_seed attribute is used.
+const uint64_t* SeedOrNull(const ffi::AnyBuffer& x) {
+  const bool two_words = x.element_type() == ffi::DataType::U32 && x.element_count() == 2;
+  const bool one_word = (x.element_type() == ffi::DataType::U64 || x.element_type() == ffi::DataType::S64) &&
+                        x.element_count() == 1;
+  return (two_words || one_word) ? static_cast<const uint64_t*>(x.untyped_data()) : nullptr;
+}
+
 ffi::Error Failed(const char* what) {
   return ffi::Error::InvalidArgument(std::string(what) + ": " + fa2_last_error());
 }
 
 ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::AnyBuffer v,
-                   ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer seqlens,
+                   ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed,
                    float softmax_scale, float dropout_p, bool causal, int64_t dropout_seed,
                    int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
                    ffi::Result<ffi::AnyBuffer> o, ffi::Result<ffi::AnyBuffer> lse) {
@@ -112,13 +122,15 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
   if (!ScoreTerm(bias, &a.bias) || !ScoreTerm(mask, &a.mask))
     return ffi::Error::InvalidArgument("fa2_b200_fwd: bias / mask must be 4-D fp16, bf16 or fp32");
   a.seqlens = SeqlensOrNull(seqlens, a.p.batch);
+  a.dropout_seed_dev = SeedOrNull(seed);
   if (fa2_fwd(&a, stream) != FA2_OK) return Failed("fa2_b200_fwd");
   return ffi::Error::Success();
 }
 
 ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ffi::AnyBuffer k,
                    ffi::AnyBuffer v, ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer o,
-                   ffi::AnyBuffer lse, ffi::AnyBuffer seqlens, float softmax_scale, float dropout_p,
+                   ffi::AnyBuffer lse, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed, float softmax_scale,
+                   float dropout_p,
                    bool causal, int64_t dropout_seed, int32_t batch_offset, int32_t head_offset,
                    int32_t heads_q_global, ffi::Result<ffi::AnyBuffer> dq,
                    ffi::Result<ffi::AnyBuffer> dk, ffi::Result<ffi::AnyBuffer> dv,
@@ -144,6 +156,7 @@ ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ff
   a.workspace = workspace->untyped_data();
   a.workspace_bytes = static_cast<size_t>(workspace->element_count());
   a.seqlens = SeqlensOrNull(seqlens, a.p.batch);
+  a.dropout_seed_dev = SeedOrNull(seed);
   if (fa2_bwd(&a, stream) != FA2_OK) return Failed("fa2_b200_bwd");
   return ffi::Error::Success();
 }
@@ -160,6 +173,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Arg<ffi::AnyBuffer>()   // bias   (or a one-element dummy)
         .Arg<ffi::AnyBuffer>()   // mask   (or a one-element dummy)
         .Arg<ffi::AnyBuffer>()   // seqlens int32 [B] (or a one-element dummy of another dtype)
+        .Arg<ffi::AnyBuffer>()   // seed: uint32 [2] (low, high) or one 64-bit integer (or a dummy)
         .Attr<float>("softmax_scale")
         .Attr<float>("dropout_p")
         .Attr<bool>("causal")
@@ -183,6 +197,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Arg<ffi::AnyBuffer>()   // o
         .Arg<ffi::AnyBuffer>()   // lse
         .Arg<ffi::AnyBuffer>()   // seqlens
+        .Arg<ffi::AnyBuffer>()   // seed
         .Attr<float>("softmax_scale")
         .Attr<float>("dropout_p")
         .Attr<bool>("causal")

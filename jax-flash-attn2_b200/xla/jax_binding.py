@@ -74,6 +74,15 @@ def _operands(q, bias, attention_mask):
     return (dummy if bias is None else bias), mask, seqlens
 
 
+def _seed_operand(q, dropout_seed):
+    """The seed as a device operand (two uint32 words: low, high), so that a traced seed does not
+    re-specialise the call; a python int or None goes through the attribute instead."""
+    if dropout_seed is None or isinstance(dropout_seed, int):
+        return jnp.zeros((1,), q.dtype), (0 if dropout_seed is None else dropout_seed)
+    s = jnp.asarray(dropout_seed).reshape(()).astype(jnp.uint32)   # jax without x64: 32-bit seeds
+    return jnp.stack([s, jnp.zeros((), jnp.uint32)]), 0
+
+
 def _attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, offsets):
     return dict(
         softmax_scale=np.float32(1.0 / math.sqrt(q.shape[-1]) if softmax_scale is None else softmax_scale),
@@ -95,19 +104,21 @@ def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_
     assert q.dtype in (jnp.float16, jnp.bfloat16), "Only support fp16 and bf16"
     batch, sq, hq, _ = q.shape
     bias_, mask_, seqlens = _operands(q, bias, attention_mask)
+    seed_op, seed_attr = _seed_operand(q, dropout_seed)
     out_types = (
         jax.ShapeDtypeStruct(q.shape, q.dtype),
         jax.ShapeDtypeStruct((batch, hq, -(-sq // 128) * 128), jnp.float32),
     )
     return jax.ffi.ffi_call("fa2_b200_fwd", out_types)(
-        q, k, v, bias_, mask_, seqlens,
-        **_attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, offsets))
+        q, k, v, bias_, mask_, seqlens, seed_op,
+        **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, offsets))
 
 
 def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_prob, causal,
                                softmax_scale, dropout_seed, varlen_mode=True, *, offsets=(0, 0, None)):
     del varlen_mode
     bias_, mask_, seqlens = _operands(q, bias, attention_mask)
+    seed_op, seed_attr = _seed_operand(q, dropout_seed)
     out_types = (
         jax.ShapeDtypeStruct(q.shape, q.dtype),
         jax.ShapeDtypeStruct(k.shape, k.dtype),
@@ -115,8 +126,8 @@ def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_
         jax.ShapeDtypeStruct((_workspace_bytes(q.shape, k.shape, q.dtype),), jnp.uint8),
     )
     dq, dk, dv, _ = jax.ffi.ffi_call("fa2_b200_bwd", out_types)(
-        dO, q, k, v, bias_, mask_, o, M, seqlens,
-        **_attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, offsets))
+        dO, q, k, v, bias_, mask_, o, M, seqlens, seed_op,
+        **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, offsets))
     return dq, dk, dv
 
 

@@ -272,6 +272,55 @@ def test_dropout_mask_is_reproducible_and_keep_rate_matches():
     assert torch.allclose(vals, torch.full_like(vals, 1.0 / (S * (1 - p))), rtol=2e-3)
 
 
+def test_seed_read_from_device_memory_gives_the_same_bits():
+    """A seed handed over as a one-element int64 CUDA tensor is read by the kernels on the device;
+    forward and backward must reproduce the results of the same seed given by value (seed above
+    2^32 so that both key words matter), for every kernel family."""
+    J = _J()
+    seed = (7 << 32) + 12345
+    for D, dtype in ((64, torch.bfloat16), (128, torch.float16), (256, torch.bfloat16)):
+        q, k, v, do = (x.cuda() for x in W.make_qkv(2, 200, 200, 4, 2, D, dtype, D ** -0.25))
+        seed_dev = torch.tensor([seed], dtype=torch.int64, device="cuda")
+        o1, l1 = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.2, True, seed)
+        o2, l2 = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.2, True, seed_dev)
+        assert torch.equal(o1, o2) and torch.equal(l1[:, :, :200], l2[:, :, :200])   # lse is padded to 256
+        g1 = J.bwd_attention_kernel_call(do, q, k, v, None, None, o1, l1, 0.2, True, None, seed)
+        g2 = J.bwd_attention_kernel_call(do, q, k, v, None, None, o1, l1, 0.2, True, None, seed_dev)
+        assert torch.equal(g1[1], g2[1]) and torch.equal(g1[2], g2[2]) and rel_l2(g1[0], g2[0]) < 1e-3
+        seed_dev += 1    # a new seed in the same buffer: different bits, no host round trip
+        o3, _ = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.2, True, seed_dev)
+        assert not torch.equal(o1, o3)
+    assert J.device_status() == 0
+
+
+def test_calls_can_be_captured_in_a_cuda_graph():
+    """The library launches on the given stream only and never synchronises, so forward and
+    backward can be recorded into a CUDA graph (the way XLA command buffers replay custom calls)
+    and replayed on new input values in the same buffers."""
+    J = _J()
+    q, k, v, do = (x.cuda() for x in W.make_qkv(2, 384, 384, 4, 2, 128, torch.bfloat16, 0.3))
+    o_ref, l_ref = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)   # also warms up
+    g_ref = J.bwd_attention_kernel_call(do, q, k, v, None, None, o_ref, l_ref, 0.0, True, None, None)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o, l = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)
+        g = J.bwd_attention_kernel_call(do, q, k, v, None, None, o, l, 0.0, True, None, None)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_ref) and torch.equal(g[1], g_ref[1]) and torch.equal(g[2], g_ref[2])
+    q2, k2, v2, do2 = (x.cuda() for x in W.make_qkv(2, 384, 384, 4, 2, 128, torch.bfloat16, 0.2))
+    o_ref2, l_ref2 = J.fwd_attention_kernel_call(q2, k2, v2, None, None, None, 0.0, True, None)
+    g_ref2 = J.bwd_attention_kernel_call(do2, q2, k2, v2, None, None, o_ref2, l_ref2, 0.0, True, None, None)
+    for dst, src in ((q, q2), (k, k2), (v, v2), (do, do2)):
+        dst.copy_(src)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_ref2) and torch.equal(g[1], g_ref2[1]) and torch.equal(g[2], g_ref2[2])
+    assert rel_l2(g[0], g_ref2[0]) < 1e-3
+    assert J.device_status() == 0
+
+
 def test_reruns_are_bitwise_identical_forward_and_dkdv():
     J = _J()
     q, k, v, do = (x.cuda() for x in W.make_qkv(2, 512, 512, 4, 2, 128, torch.bfloat16, 0.3))
