@@ -366,8 +366,14 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int it = 0; it < T; ++it) {
       int h, i;
       step_coords(it, h, i);
-      ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
-      if (!ok) break;
+      if (ok) ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
+      if (!ok) {
+        // No early exit: a thread that left alone would strand the other 127 at the (unbounded)
+        // named barriers of the staging loop. Keep in step with them: eight barriers per step.
+#pragma unroll 1
+        for (int k = 0; k < 8; ++k) named_bar_sync(3, 128);
+        continue;
+      }
       tc_fence_after();
       uint32_t v[kBQ];
       tmem_ld32(tdQ, reinterpret_cast<uint32_t(&)[32]>(v[0]));

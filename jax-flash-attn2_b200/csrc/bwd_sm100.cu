@@ -49,6 +49,8 @@ struct BwdRoles {
   static constexpr int kThreads = (kPW + 2) * 128;
   static constexpr int kRegsDrain = kPW == 2 ? 152 : 80;
   static constexpr int kRegsOther = kPW == 2 ? 104 : 80;
+  static_assert(kPW == 4 || 2 * 128 + kRegsDrain + kRegsOther == 4 * 128,
+                "setmaxnreg must hand out exactly the launch allocation");
   static constexpr int kWarpDrain = 4 * kPW, kWarpMma = 4 * kPW + 4, kWarpTma = 4 * kPW + 5;
 };
 
@@ -392,8 +394,14 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int it = 0; it < T; ++it) {
       int h, i;
       step_coords(it, h, i);
-      ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
-      if (!ok) break;
+      if (ok) ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
+      if (!ok) {
+        // No early exit: a thread that left alone would strand the other 127 at the (unbounded)
+        // named barriers of the staging loop. Keep in step with them: eight barriers per step.
+#pragma unroll 1
+        for (int k = 0; k < 8; ++k) named_bar_sync(3, 128);
+        continue;
+      }
       if (r == 0) FA2_T(5, it);
       tc_fence_after();
       // Pull the tile into registers first so that the tensor-memory columns are handed back

@@ -402,7 +402,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
       if (tid == 0) FA2_TF(39, o_cnt - 1);
       if (tid == 128) FA2_TF(42, o_cnt - 1);
-      if (!ok) break;
+      // No early exit when a wait has given up: a thread that left alone would strand the rest
+      // of its tile at the (unbounded) named barriers of the next epilogue. With `ok` false the
+      // remaining items cost only those barriers: the loops and waits above are skipped.
     }
     if (r == 0) tma_store_wait_read0();
     if (!ok && r == 0) atomicOr(p.status, 4);
