@@ -239,19 +239,40 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   HeadDim hd;
   split_head_dim(p.head_dim, &hd);
   const int D = hd.padded;
-  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->q_strides, 128, "q")) ||
+  // The problem as the kernel sees it. Decode shape (one query row per head, grouped heads,
+  // nothing that depends on the (query, head) position): the G query heads of a key/value head
+  // become G query rows of one head through the strides alone, so K and V are streamed once per
+  // group instead of once per query head, by one CTA instead of G. A single row sees every key
+  // whether the call is causal or not (bottom-right alignment).
+  const int group = p.heads_q / p.heads_kv;
+  const bool pack_heads = p.seqlen_q == 1 && group > 1 && group <= 128 && !a->bias.ptr &&
+                          !a->mask.ptr && !(p.dropout_p > 0.f) && !a->seqlens &&
+                          a->q_strides.h > 0 && a->o_strides.h > 0;
+  int sq_k = p.seqlen_q, hq_k = p.heads_q;
+  fa2_strides q_st = a->q_strides, o_st = a->o_strides;
+  long long lse_sh = a->lse_stride_h, lse_sq = 1;
+  bool causal = p.causal != 0;
+  if (pack_heads) {
+    sq_k = group;
+    hq_k = p.heads_kv;
+    q_st.s = a->q_strides.h;  q_st.h = a->q_strides.h * group;
+    o_st.s = a->o_strides.h;  o_st.h = a->o_strides.h * group;
+    lse_sq = a->lse_stride_h; lse_sh = a->lse_stride_h * group;
+    causal = false;
+  }
+  if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, sq_k, hq_k, hd, q_st, 128, "q")) ||
       (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k")) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v")) ||
-      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->o_strides, 128, "o")) ||
-      (rc = make_tmap(&L.tmO1, a->o, bf16, p.batch, p.seqlen_q, p.heads_q, hd, a->o_strides, 128, "o", 1)))
+      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
+      (rc = make_tmap(&L.tmO1, a->o, bf16, p.batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
     return rc;
 
   FwdKernelParams& kp = L.kp;
-  kp.B = p.batch; kp.Sq = p.seqlen_q; kp.Sk = p.seqlen_k;
-  kp.Hq = p.heads_q; kp.Hkv = p.heads_kv; kp.G = p.heads_q / p.heads_kv;
-  kp.causal_off = p.seqlen_k - p.seqlen_q;
+  kp.B = p.batch; kp.Sq = sq_k; kp.Sk = p.seqlen_k;
+  kp.Hq = hq_k; kp.Hkv = p.heads_kv; kp.G = hq_k / p.heads_kv;
+  kp.causal_off = p.seqlen_k - sq_k;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
-  kp.lse = a->lse; kp.lse_sb = a->lse_stride_b; kp.lse_sh = a->lse_stride_h;
+  kp.lse = a->lse; kp.lse_sb = a->lse_stride_b; kp.lse_sh = lse_sh; kp.lse_sq = lse_sq;
   if ((rc = make_score_term(&kp.bias, a->bias, p, "bias")) ||
       (rc = make_score_term(&kp.mask, a->mask, p, "mask")))
     return rc;
@@ -264,13 +285,13 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   if (a->dropout_seed_dev && (reinterpret_cast<uintptr_t>(a->dropout_seed_dev) & 7))
     return fail(FA2_ERR_INVALID_ARG, "dropout_seed_dev must be 8-byte aligned");
   kp.drop.seed_dev = reinterpret_cast<const unsigned long long*>(a->dropout_seed_dev);
-  kp.n_qblk = (p.seqlen_q + 255) / 256;
+  kp.n_qblk = (sq_k + 255) / 256;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
 
   L.head_dim = D;
   L.bf16 = bf16;
-  L.causal = p.causal != 0;
+  L.causal = causal;
   // The plain path assumes a positive scale (it takes the row maximum before scaling).
   L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled || !(p.softmax_scale > 0.f);
 

@@ -229,8 +229,8 @@ __device__ __forceinline__ void epilogue_row(uint32_t tO, bool has_acc, uint8_t*
   const float inv = (l > 0.f) ? (kFeat ? p.drop.inv_keep : 1.f) / l : 0.f;
   const float lse = (l > 0.f) ? (m * sc + lg2_approx(l)) * kLn2 : -INFINITY;
   if (qi < p.Sq)
-    p.lse[static_cast<long long>(b) * p.lse_sb + static_cast<long long>(h) * p.lse_sh + qi] =
-        lse;
+    p.lse[static_cast<long long>(b) * p.lse_sb + static_cast<long long>(h) * p.lse_sh +
+          static_cast<long long>(qi) * p.lse_sq] = lse;
   #pragma unroll
   for (int c = 0; c < D / 32; ++c) {
     uint32_t o[32];
@@ -267,7 +267,8 @@ __device__ __forceinline__ float epilogue_stats(const FwdKernelParams& p, int b,
   const float inv = (l > 0.f) ? (kFeat ? p.drop.inv_keep : 1.f) / l : 0.f;
   const float lse = (l > 0.f) ? (m * sc + lg2_approx(l)) * kLn2 : -INFINITY;
   if (qi < p.Sq)
-    p.lse[static_cast<long long>(b) * p.lse_sb + static_cast<long long>(h) * p.lse_sh + qi] = lse;
+    p.lse[static_cast<long long>(b) * p.lse_sb + static_cast<long long>(h) * p.lse_sh +
+          static_cast<long long>(qi) * p.lse_sq] = lse;
   return inv;
 }
 template <bool kBf16>

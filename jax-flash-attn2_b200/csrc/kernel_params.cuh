@@ -40,6 +40,8 @@ struct FwdKernelParams {
   float scale_log2;     // softmax_scale * log2(e)
   float* lse;
   long long lse_sb, lse_sh;
+  long long lse_sq;     // stride between the lse entries of consecutive query rows (1, except when
+                        // the rows of the problem the kernel sees are really query heads)
   ScoreTermDev bias, mask;
   DropoutDev drop;
   int n_qblk;           // number of 256-row query blocks

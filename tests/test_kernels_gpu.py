@@ -182,6 +182,28 @@ def test_seqlens_needs_equal_sequence_lengths():
         J.fwd_attention_kernel_call(q.cuda(), k.cuda(), v.cuda(), seqlens=torch.tensor([5], dtype=torch.int32).cuda())
 
 
+@pytest.mark.parametrize("D,dtype,B,Sk,Hq,Hkv,causal", [
+    (128, torch.bfloat16, 3, 1000, 32, 8, False), (128, torch.float16, 1, 129, 8, 1, True),
+    (64, torch.bfloat16, 2, 4096, 16, 2, False), (256, torch.float16, 2, 300, 8, 4, True),
+    (96, torch.bfloat16, 1, 77, 6, 3, False),
+])
+def test_decode_rows_with_grouped_heads(D, dtype, B, Sk, Hq, Hkv, causal):
+    """One query row per head (decode). The library runs the query heads of a key/value head as
+    rows of one tile (K and V are read once per group); the result, lse included, must be the one
+    of the plain head-by-head computation, causal or not (a single row sees every key)."""
+    J = _J()
+    q, k, v, _ = W.make_qkv(B, 1, Sk, Hq, Hkv, D, dtype, D ** -0.25)
+    out, lse = J.fwd_attention_kernel_call(q.cuda(), k.cuda(), v.cuda(), None, None, None, 0.0, causal, None)
+    ro, rl = BlockAttention().forward(q, k, v, causal=False)
+    assert J.device_status() == 0
+    assert (out.cpu().float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
+    assert (lse.cpu()[:, :, :1] - rl).abs().max().item() <= LSE_TOL
+    # the same through [B, H, S, D] storage (head stride 1 row, sequence stride irrelevant)
+    qt = q.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3).cuda()
+    out2, lse2 = J.fwd_attention_kernel_call(qt, k.cuda(), v.cuda(), None, None, None, 0.0, causal, None)
+    assert torch.equal(out2, out) and torch.equal(lse2[:, :, :1], lse[:, :, :1])
+
+
 @pytest.mark.parametrize("G", [1, 2, 4, 8])
 def test_gqa_groups(G):
     run_case(1, 256, 256, 8, 8 // G, 64, torch.float16, True)
