@@ -98,6 +98,13 @@ typedef struct {
    * flash_attention_triton/_flash_attention.py:91-92; _forward_triton.py:554) needs no host copy and
    * a new seed never changes the launch. */
   const uint64_t* dropout_seed_dev;
+  /* Optional scratch for split-KV (NULL / 0 = none). A problem with too few (batch, head, query
+   * tile) items to fill the GPU, typically a decode step, is cut along the key sequence into
+   * several items whose partial results are merged by a second small kernel; that needs
+   * fa2_fwd_workspace_bytes(&p) bytes of scratch (256-byte aligned; contents undefined before and
+   * after the call). Without enough scratch the call runs unsplit: same result, fewer SMs busy. */
+  void* workspace;
+  size_t workspace_bytes;
 } fa2_fwd_params;
 
 typedef struct {
@@ -131,6 +138,12 @@ int fa2_fwd(const fa2_fwd_params* params, void* cuda_stream);
  * (_backward_triton.py:948-1173): the rowsum(o * d_o) pre-pass (_attn_bwd_preprocess, :79-147),
  * the main kernel (_attn_bwd, :712-945) and the per-group reduction of dk / dv (:1156-1161). */
 int fa2_bwd(const fa2_bwd_params* params, void* cuda_stream);
+
+/* Bytes of scratch with which fa2_fwd would split this problem along the key sequence; 0 when it
+ * would not split it (most problems). Depends on the GPU the calling thread has current. No
+ * counterpart in the reference, whose forward is one program per query tile
+ * (_forward_triton.py:213-459). */
+size_t fa2_fwd_workspace_bytes(const fa2_problem* problem);
 
 /* Bytes of scratch the backward needs for this problem (fp32 dq accumulator and the row sums). */
 size_t fa2_bwd_workspace_bytes(const fa2_problem* problem);

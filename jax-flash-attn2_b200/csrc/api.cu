@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -15,6 +16,7 @@
 #include "../../include/fa2_b200.h"
 #include "bwd_launch.cuh"
 #include "fwd_launch.cuh"
+#include "launch_util.cuh"
 
 namespace fa2 {
 namespace {
@@ -194,6 +196,45 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   return w;
 }
 
+// Split-KV plan of the forward (head dim <= 128 kernel only): how many parts the key sequence is
+// cut into and how many K/V tiles each part gets. A problem is split when its (query block,
+// batch, head) items would leave more than half of the SMs idle and the key sequence is long
+// enough to share out.
+struct SplitPlan {
+  int n_splits, split_tiles;
+  int sq_k, hq_k;          // the problem as the kernel sees it (after packing grouped heads)
+  size_t part_o_bytes, part_lse_off, total;
+};
+SplitPlan plan_splits(const fa2_problem& p, const HeadDim& hd, bool pack_heads) {
+  SplitPlan s{};
+  s.n_splits = 1;
+  s.sq_k = pack_heads ? p.heads_q / p.heads_kv : p.seqlen_q;
+  s.hq_k = pack_heads ? p.heads_kv : p.heads_q;
+  const int n_tiles = (p.seqlen_k + 127) / 128;
+  const long long items = static_cast<long long>((s.sq_k + 255) / 256) * p.batch * s.hq_k;
+  const int sms = sm_count();
+  if (hd.padded > 128 || n_tiles < 8 || items * 2 > sms) return s;
+  int want = static_cast<int>(std::min<long long>(std::min<long long>(sms / items, n_tiles / 4), 32));
+  if (want < 2) return s;
+  s.split_tiles = (n_tiles + want - 1) / want;
+  s.n_splits = (n_tiles + s.split_tiles - 1) / s.split_tiles;
+  if (s.n_splits < 2) {
+    s.n_splits = 1;
+    return s;
+  }
+  const size_t rows = static_cast<size_t>(s.n_splits) * p.batch * s.sq_k * s.hq_k;
+  s.part_o_bytes = align_up(rows * p.head_dim * 2, 256);
+  s.part_lse_off = s.part_o_bytes;
+  const size_t sq_pad = static_cast<size_t>((s.sq_k + 127) / 128) * 128;
+  s.total = s.part_lse_off + align_up(static_cast<size_t>(s.n_splits) * p.batch * s.hq_k * sq_pad * 4, 256);
+  return s;
+}
+
+bool can_pack_heads(const fa2_problem& p) {
+  const int group = p.heads_kv > 0 ? p.heads_q / p.heads_kv : 0;
+  return p.seqlen_q == 1 && group > 1 && group <= 128 && !(p.dropout_p > 0.f);
+}
+
 }  // namespace
 }  // namespace fa2
 
@@ -201,7 +242,7 @@ using namespace fa2;
 
 extern "C" {
 
-int fa2_version(void) { return 1002; }
+int fa2_version(void) { return 1003; }
 
 const char* fa2_last_error(void) { return g_err; }
 
@@ -245,8 +286,7 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   // group instead of once per query head, by one CTA instead of G. A single row sees every key
   // whether the call is causal or not (bottom-right alignment).
   const int group = p.heads_q / p.heads_kv;
-  const bool pack_heads = p.seqlen_q == 1 && group > 1 && group <= 128 && !a->bias.ptr &&
-                          !a->mask.ptr && !(p.dropout_p > 0.f) && !a->seqlens &&
+  const bool pack_heads = can_pack_heads(p) && !a->bias.ptr && !a->mask.ptr && !a->seqlens &&
                           a->q_strides.h > 0 && a->o_strides.h > 0;
   int sq_k = p.seqlen_q, hq_k = p.heads_q;
   fa2_strides q_st = a->q_strides, o_st = a->o_strides;
@@ -260,11 +300,29 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
     lse_sq = a->lse_stride_h; lse_sh = a->lse_stride_h * group;
     causal = false;
   }
+  // Split-KV: the kernel writes per-split partial results into the workspace (as batch elements
+  // split * B + b of a contiguous [n_splits * B, Sq, Hq, D] output and its lse), merged afterwards.
+  SplitPlan sp = plan_splits(p, hd, pack_heads);
+  if (sp.n_splits > 1 && (!a->workspace || a->workspace_bytes < sp.total ||
+                          (reinterpret_cast<uintptr_t>(a->workspace) & 255)))
+    sp.n_splits = 1;   // not enough scratch: run unsplit
+  const bool split = sp.n_splits > 1;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  void* o_ptr = a->o;
+  int o_batch = p.batch;
+  const fa2_strides o_final = o_st;
+  if (split) {
+    o_ptr = ws;
+    o_batch = sp.n_splits * p.batch;
+    o_st.h = p.head_dim;
+    o_st.s = static_cast<int64_t>(hq_k) * p.head_dim;
+    o_st.b = static_cast<int64_t>(sq_k) * o_st.s;
+  }
   if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, sq_k, hq_k, hd, q_st, 128, "q")) ||
       (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k")) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v")) ||
-      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
-      (rc = make_tmap(&L.tmO1, a->o, bf16, p.batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
+      (rc = make_tmap(&L.tmO, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
+      (rc = make_tmap(&L.tmO1, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
     return rc;
 
   FwdKernelParams& kp = L.kp;
@@ -273,6 +331,17 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   kp.causal_off = p.seqlen_k - sq_k;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.lse = a->lse; kp.lse_sb = a->lse_stride_b; kp.lse_sh = lse_sh; kp.lse_sq = lse_sq;
+  kp.n_splits = 1;
+  kp.split_tiles = 0;
+  const int sq_pad = (sq_k + 127) / 128 * 128;
+  if (split) {
+    kp.n_splits = sp.n_splits;
+    kp.split_tiles = sp.split_tiles;
+    kp.lse = reinterpret_cast<float*>(ws + sp.part_lse_off);
+    kp.lse_sq = 1;
+    kp.lse_sh = sq_pad;
+    kp.lse_sb = static_cast<long long>(hq_k) * sq_pad;
+  }
   if ((rc = make_score_term(&kp.bias, a->bias, p, "bias")) ||
       (rc = make_score_term(&kp.mask, a->mask, p, "mask")))
     return rc;
@@ -295,10 +364,36 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   // The plain path assumes a positive scale (it takes the row maximum before scaling).
   L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled || !(p.softmax_scale > 0.f);
 
-  const cudaError_t e = launch_fwd(L, static_cast<cudaStream_t>(cuda_stream));
+  cudaError_t e = launch_fwd(L, static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess)
     return fail(FA2_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
+  if (split) {
+    FwdCombine c{};
+    c.part_o = ws;
+    c.part_lse = reinterpret_cast<const float*>(ws + sp.part_lse_off);
+    c.o = a->o;
+    c.o_strides[0] = o_final.b; c.o_strides[1] = o_final.s; c.o_strides[2] = o_final.h;
+    c.lse = a->lse;
+    c.lse_sb = a->lse_stride_b; c.lse_sh = lse_sh; c.lse_sq = lse_sq;
+    c.n_splits = sp.n_splits; c.B = p.batch; c.Sq = sq_k; c.Hq = hq_k; c.D = p.head_dim;
+    c.sq_pad = sq_pad;
+    c.bf16 = bf16;
+    e = launch_fwd_combine(c, static_cast<cudaStream_t>(cuda_stream));
+    if (e != cudaSuccess)
+      return fail(FA2_ERR_CUDA, "split-KV merge launch failed: %s", cudaGetErrorString(e));
+  }
   return FA2_OK;
+}
+
+size_t fa2_fwd_workspace_bytes(const fa2_problem* problem) {
+  if (!problem || check_problem(*problem)) return 0;
+  HeadDim hd;
+  split_head_dim(problem->head_dim, &hd);
+  // whether grouped heads get packed also depends on operands this function does not see
+  // (bias, mask, lengths): report what the larger of the two plans needs
+  size_t need = plan_splits(*problem, hd, false).total;
+  if (can_pack_heads(*problem)) need = std::max(need, plan_splits(*problem, hd, true).total);
+  return need;
 }
 
 size_t fa2_bwd_workspace_bytes(const fa2_problem* problem) {

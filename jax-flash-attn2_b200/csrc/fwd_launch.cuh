@@ -15,6 +15,21 @@ struct FwdLaunch {
   bool bf16, causal, feat;
 };
 
+// Split-KV: merges the partial results of the splits into the caller's output and lse.
+//   part_o   [n_splits, B, Sq, Hq, D]  normalised partial outputs (the q dtype, contiguous)
+//   part_lse [n_splits, B, Hq, sq_pad] natural-log lse of every split (-inf: the split saw no key)
+struct FwdCombine {
+  const void* part_o;
+  const float* part_lse;
+  void* o;
+  long long o_strides[3];     // (batch, sequence, head) element strides of o
+  float* lse;
+  long long lse_sb, lse_sh, lse_sq;
+  int n_splits, B, Sq, Hq, D, sq_pad;
+  bool bf16;
+};
+cudaError_t launch_fwd_combine(const FwdCombine& c, cudaStream_t stream);
+
 // Launches the forward kernel specialised for (head_dim, dtype, causal, score terms/dropout).
 cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream);
 

@@ -63,6 +63,7 @@ struct FwdSmem {
 // One work item as every role sees it.
 struct FwdItem {
   int b, h, hk, q0;
+  int split, j0;   // split-KV: which part of the K/V sequence, and its first tile
   int sq, sk;   // rows of this batch element that take part (the problem's, or its seqlens entry)
   int n_tiles[kTilesPerCta];
   int n_max;
@@ -70,6 +71,12 @@ struct FwdItem {
 
 template <bool kCausal>
 __device__ __forceinline__ void decode_item(const FwdKernelParams& p, int w, FwdItem& it) {
+  it.split = 0;
+  if (p.n_splits > 1) {
+    it.split = w % p.n_splits;
+    w /= p.n_splits;
+  }
+  it.j0 = it.split * p.split_tiles;
   const int nbh = p.B * p.Hq;
   const int qb_rank = w / nbh;
   const int bh = w - qb_rank * nbh;
@@ -98,6 +105,7 @@ __device__ __forceinline__ void decode_item(const FwdKernelParams& p, int w, Fwd
     } else {
       it.n_tiles[t] = (it.sk + kBN - 1) / kBN;
     }
+    if (p.n_splits > 1) it.n_tiles[t] = max(0, min(it.n_tiles[t] - it.j0, p.split_tiles));
   }
   it.n_max = max(it.n_tiles[0], it.n_tiles[1]);
 }
@@ -132,7 +140,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int total_items = p.n_qblk * p.B * p.Hq;
+  const int total_items = p.n_qblk * p.B * p.Hq * p.n_splits;
   if (tid == 0) FA2_TF(32, 0);
 
   // ---- set-up ---------------------------------------------------------------------------------
@@ -198,7 +206,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           if (!ok) break;
           mbar_arrive_expect_tx(bar_kv_full(slot), L::kKVTileBytes);
           tma_load_5d(sKV + slot * L::kKVTileBytes, (i & 1) ? &tmV : &tmK, bar_kv_full(slot), 0,
-                      (i >> 1) * kBN, 0, it.hk, it.b);
+                      (it.j0 + (i >> 1)) * kBN, 0, it.hk, it.b);
         }
       }
       if (!ok) atomicOr(p.status, 1);
@@ -339,6 +347,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       FwdItem it;
       decode_item<kCausal>(p, w, it);
       const int b = it.b, h = it.h;
+      const int b_out = it.b + it.split * p.B;   // where this item's output and lse go
       const int qi = it.q0 + t * kBM + r;      // global query row
       const int nt = it.n_tiles[t];
       const bool tile_valid = (it.q0 + t * kBM) < p.Sq;
@@ -352,7 +361,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
         if (!ok) break;
         if (lane == 0) FA2_TF(8 + warp, it_cnt);
-        softmax_tile_row<D, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
+        softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
                                           [&](int hh) {
                                             if (hh == 0 && lane == 0) FA2_TF(52 + warp, it_cnt);
                                             return mbar_arrive_zero(bar_p_full(t, hh));
@@ -369,7 +378,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       ++o_cnt;
       // One 64-column block at a time through this tile's 16 KiB staging block. O_t is handed
       // back to the MMA warp as soon as its last columns have been read out of tensor memory.
-      const float inv = (ok && tile_valid) ? epilogue_stats<kFeat>(p, b, h, qi, sc, m, l) : 0.f;
+      const float inv = (ok && tile_valid) ? epilogue_stats<kFeat>(p, b_out, h, qi, sc, m, l) : 0.f;
       uint8_t* stage_gen = smem_gen + L::kOOff + t * L::kBlockBytes;
       tc_fence_after();
 #pragma unroll
@@ -396,7 +405,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         named_bar_sync(1 + t, kBM);
         if (ok && tile_valid && r == 0 && !*abort_flag) {
-          tma_store_5d(&tmO1, sO + t * L::kBlockBytes, 0, it.q0 + t * kBM, blk, h, b);
+          tma_store_5d(&tmO1, sO + t * L::kBlockBytes, 0, it.q0 + t * kBM, blk, h, b_out);
           tma_store_commit();
         }
       }
@@ -423,18 +432,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 // ---------------------------------------------------------------------------------------------
 // launcher
 // ---------------------------------------------------------------------------------------------
-static int sm_count() {
-  static int cached[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 template <int D, bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch_one(const FwdLaunch& a, cudaStream_t stream) {
   using L = FwdSmem<D>;
@@ -442,7 +439,7 @@ static cudaError_t launch_one(const FwdLaunch& a, cudaStream_t stream) {
   static bool smem_opted_in[64] = {};
   cudaError_t e = opt_in_dynamic_smem(kern, L::kDynamicBytes, smem_opted_in);
   if (e != cudaSuccess) return e;
-  const long long items = static_cast<long long>(a.kp.n_qblk) * a.kp.B * a.kp.Hq;
+  const long long items = static_cast<long long>(a.kp.n_qblk) * a.kp.B * a.kp.Hq * a.kp.n_splits;
   if (items <= 0) return cudaSuccess;
   const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
   kern<<<grid, kThreads, L::kDynamicBytes, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmO1, a.kp);

@@ -48,6 +48,11 @@ struct FwdKernelParams {
   // Optional per-batch lengths (Sq == Sk): batch element b is attended as if both sequences had
   // seqlens[b] rows; output rows at or beyond it are written as zeros.
   const int* seqlens;
+  // Split-KV (low-occupancy problems): every work item is cut into n_splits items of
+  // split_tiles K/V tiles each; split s writes its normalised partial output and its lse as
+  // "batch element" s * B + b of the partial buffers that o / lse then point to.
+  int n_splits;         // >= 1
+  int split_tiles;
   int* status;          // device status word (bounded-wait time-outs)
 };
 

@@ -17,4 +17,17 @@ static cudaError_t opt_in_dynamic_smem(Kernel kern, int bytes, bool (&done)[64])
   return e;
 }
 
+// Streaming multiprocessors of the current device (cached per device; 148 if it cannot be read).
+inline int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 }  // namespace fa2

@@ -20,6 +20,7 @@ FA2_ERR_INVALID_ARG, FA2_ERR_UNSUPPORTED, FA2_ERR_CUDA, FA2_ERR_WORKSPACE = -1, 
 EXPORTED_SYMBOLS = (
     "fa2_fwd",
     "fa2_bwd",
+    "fa2_fwd_workspace_bytes",
     "fa2_bwd_workspace_bytes",
     "fa2_last_error",
     "fa2_version",
@@ -76,6 +77,8 @@ class FwdParams(C.Structure):
         ("mask", ScoreTerm),
         ("seqlens", C.c_void_p),
         ("dropout_seed_dev", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -127,6 +130,8 @@ def load() -> C.CDLL:
     lib.fa2_fwd.restype = C.c_int
     lib.fa2_bwd.argtypes = [C.POINTER(BwdParams), C.c_void_p]
     lib.fa2_bwd.restype = C.c_int
+    lib.fa2_fwd_workspace_bytes.argtypes = [C.POINTER(Problem)]
+    lib.fa2_fwd_workspace_bytes.restype = C.c_size_t
     lib.fa2_bwd_workspace_bytes.argtypes = [C.POINTER(Problem)]
     lib.fa2_bwd_workspace_bytes.restype = C.c_size_t
     lib.fa2_last_error.argtypes = []

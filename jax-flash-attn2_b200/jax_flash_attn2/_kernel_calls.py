@@ -198,10 +198,13 @@ def fwd_attention_kernel_call(
     head_offset: int = 0,
     heads_q_global: tp.Optional[int] = None,
     seqlens: tp.Optional[torch.Tensor] = None,
+    split_kv: bool = True,
 ) -> tp.Tuple[torch.Tensor, torch.Tensor]:
     """Forward launch. q [B,Sq,Hq,D]; k, v [B,Sk,Hkv,D]; `attention_mask` here is already an
     additive 4-D term (see normalise_attention_mask); `seqlens` (int32 [B], device) gives every
-    batch element its own length, the reference's varlen mode without packing. Returns
+    batch element its own length, the reference's varlen mode without packing; `split_kv=False`
+    withholds the scratch with which the library splits low-occupancy problems along the key
+    sequence (same result, computed by fewer SMs). Returns
     (out [B,Sq,Hq,D] in q.dtype, lse [B,Hq,ceil(Sq/128)*128] float32, natural log; columns >= Sq
     are not written)."""
     _check_qkv(q, k, v)
@@ -224,6 +227,11 @@ def fwd_attention_kernel_call(
     a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
     a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
+    # low-occupancy problems (decode steps) are split along the key sequence if scratch is offered
+    nbytes = lib.fa2_fwd_workspace_bytes(C.byref(a.p)) if split_kv else 0
+    if nbytes:
+        _keep_w = torch.empty((nbytes,), dtype=torch.uint8, device=q.device)
+        a.workspace, a.workspace_bytes = _keep_w.data_ptr(), nbytes
     _launch(lib.fa2_fwd, a, q.device)
     return out, lse
 

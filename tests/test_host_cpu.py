@@ -21,7 +21,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert set(_capi.EXPORTED_SYMBOLS) <= declared
-    assert lib.fa2_version() == 1002
+    assert lib.fa2_version() == 1003
 
 
 def test_validation_errors_come_before_any_launch():

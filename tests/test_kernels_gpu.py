@@ -204,6 +204,43 @@ def test_decode_rows_with_grouped_heads(D, dtype, B, Sk, Hq, Hkv, causal):
     assert torch.equal(out2, out) and torch.equal(lse2[:, :, :1], lse[:, :, :1])
 
 
+@pytest.mark.parametrize("case", [
+    dict(B=1, Sq=1, Sk=32768, Hq=32, Hkv=8, D=128, dtype=torch.bfloat16, causal=False),   # decode, packed heads
+    dict(B=2, Sq=1, Sk=5000, Hq=8, Hkv=8, D=64, dtype=torch.float16, causal=False),       # decode, MHA, ragged
+    dict(B=1, Sq=256, Sk=4096, Hq=2, Hkv=1, D=128, dtype=torch.bfloat16, causal=True),    # short prefill chunk
+    dict(B=1, Sq=300, Sk=3000, Hq=4, Hkv=2, D=96, dtype=torch.float16, causal=True, p=0.1, bias_heads=4),
+    dict(B=1, Sq=2048, Sk=2048, Hq=4, Hkv=4, D=128, dtype=torch.bfloat16, causal=True),   # some splits see no key
+])
+def test_split_kv_low_occupancy_problems(case):
+    """Problems with few (batch, head, query tile) items are cut along the key sequence and merged
+    by a second kernel. The library must report scratch for them, and the split result must agree
+    with the unsplit one and with the oracle (dropout bits and bias included: both are indexed by
+    absolute positions)."""
+    J = _J()
+    from jax_flash_attn2 import _capi
+    import ctypes
+    B, Sq, Sk, Hq, Hkv, D = (case[k] for k in ("B", "Sq", "Sk", "Hq", "Hkv", "D"))
+    dtype, causal, p, bias_heads = case["dtype"], case["causal"], case.get("p", 0.0), case.get("bias_heads", 0)
+    q, k, v, _ = W.make_qkv(B, Sq, Sk, Hq, Hkv, D, dtype, D ** -0.25)
+    g = torch.Generator().manual_seed(3)
+    bias = (0.5 * torch.randn(B, bias_heads, Sq, Sk, generator=g)).to(dtype) if bias_heads else None
+    prob = _capi.Problem()
+    prob.batch, prob.seqlen_q, prob.seqlen_k, prob.heads_q, prob.heads_kv, prob.head_dim = B, Sq, Sk, Hq, Hkv, D
+    prob.dtype = _capi.FA2_BF16 if dtype == torch.bfloat16 else _capi.FA2_FP16
+    prob.softmax_scale, prob.dropout_p, prob.causal = 1.0, p, int(causal)
+    prob.heads_q_global = Hq
+    assert _capi.load().fa2_fwd_workspace_bytes(ctypes.byref(prob)) > 0
+    dev = lambda x: None if x is None else x.cuda()
+    o_s, l_s = J.fwd_attention_kernel_call(dev(q), dev(k), dev(v), None, dev(bias), None, p, causal, 5)
+    o_u, l_u = J.fwd_attention_kernel_call(dev(q), dev(k), dev(v), None, dev(bias), None, p, causal, 5, split_kv=False)
+    assert J.device_status() == 0
+    ro, rl = BlockAttention().forward(q, k, v, bias=bias, causal=causal and Sq > 1, dropout_p=p, dropout_seed=5)
+    for o, l in ((o_s, l_s), (o_u, l_u)):
+        assert (o.cpu().float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
+        assert (l.cpu()[:, :, :Sq] - rl).abs().max().item() <= LSE_TOL
+    assert (o_s.float() - o_u.float()).abs().max().item() <= OUT_TOL[dtype] / 2
+
+
 @pytest.mark.parametrize("G", [1, 2, 4, 8])
 def test_gqa_groups(G):
     run_case(1, 256, 256, 8, 8 // G, 64, torch.float16, True)
