@@ -107,7 +107,8 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
                    ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed,
                    float softmax_scale, float dropout_p, bool causal, int64_t dropout_seed,
                    int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
-                   ffi::Result<ffi::AnyBuffer> o, ffi::Result<ffi::AnyBuffer> lse) {
+                   ffi::Result<ffi::AnyBuffer> o, ffi::Result<ffi::AnyBuffer> lse,
+                   ffi::Result<ffi::AnyBuffer> workspace) {
   fa2_fwd_params a = {};
   if (!Problem(q, k, causal, softmax_scale, dropout_p, dropout_seed, batch_offset, head_offset,
                heads_q_global, &a.p))
@@ -123,6 +124,10 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
     return ffi::Error::InvalidArgument("fa2_b200_fwd: bias / mask must be 4-D fp16, bf16 or fp32");
   a.seqlens = SeqlensOrNull(seqlens, a.p.batch);
   a.dropout_seed_dev = SeedOrNull(seed);
+  // scratch for split-KV: a uint8 result of fa2_fwd_workspace_bytes(problem) bytes (one byte when
+  // the problem is not split); fa2_fwd ignores scratch that is too small
+  a.workspace = workspace->untyped_data();
+  a.workspace_bytes = static_cast<size_t>(workspace->element_count());
   if (fa2_fwd(&a, stream) != FA2_OK) return Failed("fa2_b200_fwd");
   return ffi::Error::Success();
 }
@@ -182,7 +187,8 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Attr<int32_t>("head_offset")
         .Attr<int32_t>("heads_q_global")
         .Ret<ffi::AnyBuffer>()    // o
-        .Ret<ffi::AnyBuffer>());  // lse
+        .Ret<ffi::AnyBuffer>()    // lse
+        .Ret<ffi::AnyBuffer>());  // workspace (uint8)
 
 XLA_FFI_DEFINE_HANDLER_SYMBOL(
     fa2_b200_bwd, BwdImpl,

@@ -41,20 +41,33 @@ class _Problem(ctypes.Structure):   # fa2_problem of include/fa2_b200.h
     ]
 
 
-_core.fa2_bwd_workspace_bytes.restype = ctypes.c_size_t
-_core.fa2_bwd_workspace_bytes.argtypes = [ctypes.POINTER(_Problem)]
+for _fn in (_core.fa2_bwd_workspace_bytes, _core.fa2_fwd_workspace_bytes):
+    _fn.restype = ctypes.c_size_t
+    _fn.argtypes = [ctypes.POINTER(_Problem)]
 
 
-def _workspace_bytes(q_shape, k_shape, dtype) -> int:
+def _problem(q_shape, k_shape, dtype, dropout_prob=0.0) -> _Problem:
     p = _Problem()
     p.batch, p.seqlen_q, p.heads_q, p.head_dim = (int(x) for x in q_shape)
     p.seqlen_k, p.heads_kv = int(k_shape[1]), int(k_shape[2])
     p.dtype = 1 if dtype == jnp.bfloat16 else 0
     p.softmax_scale = 1.0
-    n = int(_core.fa2_bwd_workspace_bytes(ctypes.byref(p)))
+    p.dropout_p = float(dropout_prob)
+    p.heads_q_global = p.heads_q
+    return p
+
+
+def _workspace_bytes(q_shape, k_shape, dtype) -> int:
+    n = int(_core.fa2_bwd_workspace_bytes(ctypes.byref(_problem(q_shape, k_shape, dtype))))
     if n == 0:
         raise ValueError("fa2_b200: unsupported problem (head_dim, dtype or shape)")
     return n
+
+
+def _fwd_workspace_bytes(q_shape, k_shape, dtype, dropout_prob) -> int:
+    """Scratch with which the forward splits a low-occupancy problem along the key sequence
+    (0 for most problems; a one-byte result is declared then)."""
+    return int(_core.fa2_fwd_workspace_bytes(ctypes.byref(_problem(q_shape, k_shape, dtype, dropout_prob))))
 
 
 def _operands(q, bias, attention_mask):
@@ -108,10 +121,12 @@ def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_
     out_types = (
         jax.ShapeDtypeStruct(q.shape, q.dtype),
         jax.ShapeDtypeStruct((batch, hq, -(-sq // 128) * 128), jnp.float32),
+        jax.ShapeDtypeStruct((max(1, _fwd_workspace_bytes(q.shape, k.shape, q.dtype, dropout_prob)),), jnp.uint8),
     )
-    return jax.ffi.ffi_call("fa2_b200_fwd", out_types)(
+    out, lse, _ = jax.ffi.ffi_call("fa2_b200_fwd", out_types)(
         q, k, v, bias_, mask_, seqlens, seed_op,
         **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, offsets))
+    return out, lse
 
 
 def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_prob, causal,
