@@ -60,6 +60,24 @@ def test_validation_errors_come_before_any_launch():
     assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_INVALID_ARG
 
 
+def test_forward_scratch_is_only_asked_for_low_occupancy_problems():
+    lib = _capi.load()
+    p = _capi.Problem()
+    p.dtype, p.softmax_scale = _capi.FA2_BF16, 1.0
+    def need(batch, sq, sk, hq, hkv, d):
+        p.batch, p.seqlen_q, p.seqlen_k, p.heads_q, p.heads_kv, p.head_dim = batch, sq, sk, hq, hkv, d
+        p.heads_q_global = hq
+        return lib.fa2_fwd_workspace_bytes(C.byref(p))
+    assert need(8, 4096, 4096, 32, 8, 128) == 0          # training shape: plenty of items
+    assert need(1, 1, 32768, 32, 8, 128) > 0             # decode step: split along the keys
+    assert need(1, 1, 512, 32, 8, 128) == 0              # too few keys to share out
+    assert need(1, 1, 32768, 8, 8, 256) == 0             # head dim 256 kernel does not split
+    assert lib.fa2_fwd_workspace_bytes(None) == 0
+    # partial outputs + partial lse of every split, each rounded up to 256 bytes
+    n = need(1, 256, 4096, 2, 2, 128)
+    assert n > 0 and n % 256 == 0
+
+
 def test_config_defaults_and_pairs():
     cfg = J.AttentionConfig(backend=J.Backend.GPU)
     assert cfg.platform == J.Platform.TRITON and cfg.blocksize_q == 128 and cfg.blocksize_k == 128
