@@ -241,6 +241,36 @@ def test_split_kv_low_occupancy_problems(case):
     assert (o_s.float() - o_u.float()).abs().max().item() <= OUT_TOL[dtype] / 2
 
 
+def _fuzz_cases(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    pick = lambda xs: xs[int(torch.randint(0, len(xs), (1,), generator=g))]
+    cases = []
+    for _ in range(n):
+        D = pick([32, 64, 64, 96, 128, 128, 192, 256])
+        hkv, grp = pick([1, 2, 3]), pick([1, 2, 4])
+        sq = pick([1, 17, 128, 130, 257, 400, 513])
+        sk = pick([sq, sq, 64, 200, 385, 640])
+        feat = pick(["plain", "plain", "bias1", "biasH", "pad", "full_f32", "drop", "all"])
+        if sk < 64 and feat in ("pad", "all"):
+            feat = "full_f32"    # the key-padding mask of run_case would leave no key at all
+        cases.append(dict(B=pick([1, 2, 3]), Sq=sq, Sk=sk, Hq=hkv * grp, Hkv=hkv, D=D,
+                          dtype=pick([torch.bfloat16, torch.float16]), causal=pick([False, True]), feat=feat))
+    return cases
+
+
+@pytest.mark.parametrize("case", _fuzz_cases(28, 20240611), ids=lambda c: "-".join(str(v).replace("torch.", "") for v in c.values()))
+def test_seeded_random_shapes(case):
+    """A fixed, seeded sample of the argument space (shapes on and off the tile grid, grouped
+    heads, every head-dim kernel, both dtypes, all score features) against the oracle."""
+    feat = case["feat"]
+    Hq = case["Hq"]
+    run_case(case["B"], case["Sq"], case["Sk"], Hq, case["Hkv"], case["D"], case["dtype"], case["causal"],
+             scale=case["D"] ** -0.25,
+             bias_heads={"bias1": 1, "biasH": Hq, "all": 1}.get(feat, 0),
+             mask_kind={"pad": "pad", "full_f32": "full_f32", "all": "pad"}.get(feat),
+             p={"drop": 0.15, "all": 0.1}.get(feat, 0.0))
+
+
 @pytest.mark.parametrize("G", [1, 2, 4, 8])
 def test_gqa_groups(G):
     run_case(1, 256, 256, 8, 8 // G, 64, torch.float16, True)
