@@ -239,6 +239,15 @@ def test_split_kv_low_occupancy_problems(case):
         assert (o.cpu().float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
         assert (l.cpu()[:, :, :Sq] - rl).abs().max().item() <= LSE_TOL
     assert (o_s.float() - o_u.float()).abs().max().item() <= OUT_TOL[dtype] / 2
+    if Sq > 1:
+        # the merged output and lse feed the backward like those of an unsplit forward
+        do = torch.randn(B, Sq, Hq, D, generator=g).to(dtype)
+        grads = J.bwd_attention_kernel_call(dev(do), dev(q), dev(k), dev(v), dev(bias), None, o_s, l_s, p,
+                                            causal, None, 5)
+        ref = BlockAttention().backward(do, q, k, v, o_s.cpu(), l_s.cpu()[:, :, :Sq], bias=bias, causal=causal,
+                                        dropout_p=p, dropout_seed=5, out_dtype=torch.float32)
+        for mine, want in zip(grads, ref):
+            assert rel_l2(mine.cpu(), want) <= GRAD_TOL
 
 
 def _fuzz_cases(n, seed):
