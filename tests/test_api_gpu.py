@@ -216,3 +216,39 @@ def test_full_size_config3_one_batch_element_against_the_oracle():
                               out_dtype=torch.float32, **kw)
     for mine, ref in ((dq, rq), (dk, rk), (dv, rv)):
         assert rel_l2(mine[b:b + 1].cpu(), ref) <= 1e-2
+
+
+def test_calls_on_two_streams_and_two_host_threads_do_not_interfere():
+    """The library keeps no state between calls (tensor maps live on the caller's stack, work goes
+    to the stream handed in), so forward + backward of different problems may be in flight on
+    different streams, issued from different host threads, at the same time."""
+    import threading
+    import jax_flash_attn2 as J
+    problems = [W.make_qkv(2, 1024, 1024, 8, 2, 128, torch.bfloat16, 0.2),
+                W.make_qkv(1, 777, 1300, 4, 4, 64, torch.float16, 0.3)]
+    dev = [tuple(x.cuda() for x in pr) for pr in problems]
+    serial = []
+    for q, k, v, do in dev:
+        o, l = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)
+        g = J.bwd_attention_kernel_call(do, q, k, v, None, None, o, l, 0.0, True, None, None)
+        serial.append((o, g))
+    torch.cuda.synchronize()
+    results = [None, None]
+    def worker(i):
+        q, k, v, do = dev[i]
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            for _ in range(5):
+                o, l = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)
+                g = J.bwd_attention_kernel_call(do, q, k, v, None, None, o, l, 0.0, True, None, None)
+            s.synchronize()
+        results[i] = (o, g)
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for (o, g), (o_ref, g_ref) in zip(results, serial):
+        assert torch.equal(o, o_ref) and torch.equal(g[1], g_ref[1]) and torch.equal(g[2], g_ref[2])
+        assert rel_l2(g[0], g_ref[0]) < 1e-3
+    assert J.device_status() == 0
