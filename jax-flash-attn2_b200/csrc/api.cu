@@ -318,9 +318,12 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
     o_st.s = static_cast<int64_t>(hq_k) * p.head_dim;
     o_st.b = static_cast<int64_t>(sq_k) * o_st.s;
   }
+  // head dim 256: K arrives in halves of the head dim, V in halves of the 128 key rows
   if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, sq_k, hq_k, hd, q_st, 128, "q")) ||
-      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k")) ||
-      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v")) ||
+      (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k",
+                      D == 256 ? 2 : 0)) ||
+      (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides,
+                      D == 256 ? 64 : 128, "v")) ||
       (rc = make_tmap(&L.tmO, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
       (rc = make_tmap(&L.tmO1, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
     return rc;

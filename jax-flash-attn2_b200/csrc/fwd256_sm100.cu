@@ -8,8 +8,12 @@
 // other buffer, and P_j (16 bit, over S_j) then feeds O += P_j V_j.
 //   warps 0-3 : softmax, one thread per query row
 //   warp  4   : tcgen05.mma issuer
-//   warp  5   : TMA producer: Q once; K tiles through slot 0 and V tiles through slot 1
-// Shared memory: Q 64 KiB + K slot 64 KiB + V slot 64 KiB.
+//   warp  5   : TMA producer: Q once; K tiles through one slot and V tiles through another
+// Shared memory: Q 64 KiB + K slot 64 KiB + V slot 64 KiB. There is no room for second slots, so
+// each slot is handed over in two halves with their own full / empty barriers: K by head-dim blocks
+// (the first eight S MMAs contract over dims 0-127, the last eight over 128-255), V by key rows (the
+// P.V MMAs of the first half of P read keys 0-63). The next tile's first half then loads while the
+// MMAs still read the second half of the current one.
 #include "fwd_launch.cuh"
 #include "fwd_row.cuh"
 #include "launch_util.cuh"
@@ -30,8 +34,10 @@ struct Smem256 {
   static constexpr int kVOff = kKOff + kKVTileBytes;
   static constexpr int kBarOff = kVOff + kKVTileBytes;
   // barriers: q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2 buffers][2 halves],
-  // pv_done, o_full
-  static constexpr int kNumBars = 9 + 2 * kPSplit;
+  // pv_done, o_full, then the second-half barriers k_full, k_empty, v_full, v_empty
+  static constexpr int kNumBars = 9 + 2 * kPSplit + 4;
+  static constexpr int kHalfBytes = kKVTileBytes / 2;
+  static_assert(kPSplit == 2, "V halves follow the two halves of P");
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;
@@ -50,8 +56,12 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base + L::kQOff, sK = smem_base + L::kKOff, sV = smem_base + L::kVOff;
   const uint32_t bars = smem_base + L::kBarOff;
-  const uint32_t bar_q_full = bars, bar_k_full = bars + 8, bar_k_empty = bars + 16;
-  const uint32_t bar_v_full = bars + 24, bar_v_empty = bars + 32;
+  const uint32_t bar_q_full = bars;
+  const uint32_t bars2 = bars + 8u * (9 + 2 * kPSplit);   // second-half barriers
+  auto bar_k_full = [&](int half) { return half == 0 ? bars + 8 : bars2; };
+  auto bar_k_empty = [&](int half) { return half == 0 ? bars + 16 : bars2 + 8; };
+  auto bar_v_full = [&](int half) { return half == 0 ? bars + 24 : bars2 + 16; };
+  auto bar_v_empty = [&](int half) { return half == 0 ? bars + 32 : bars2 + 24; };
   auto bar_s_full = [&](int s) { return bars + 8u * (5 + s); };
   auto bar_p_full = [&](int s, int half) { return bars + 8u * (7 + kPSplit * s + half); };
   const uint32_t bar_pv_done = bars + 8u * (7 + 2 * kPSplit), bar_o_full = bars + 8u * (8 + 2 * kPSplit);
@@ -92,10 +102,12 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar_q_full, 1);
-    mbar_init(bar_k_full, 1);
-    mbar_init(bar_k_empty, 1);
-    mbar_init(bar_v_full, 1);
-    mbar_init(bar_v_empty, 1);
+    for (int half = 0; half < 2; ++half) {
+      mbar_init(bar_k_full(half), 1);
+      mbar_init(bar_k_empty(half), 1);
+      mbar_init(bar_v_full(half), 1);
+      mbar_init(bar_v_empty(half), 1);
+    }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_s_full(s), 1);
       for (int hh = 0; hh < kPSplit; ++hh) mbar_init(bar_p_full(s, hh), kBM);
@@ -127,14 +139,20 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       tma_load_5d(sQ, &tmQ, bar_q_full, 0, q0, 0, h, b);
       bool ok = true;
       for (int j = 0; j < nt && ok; ++j) {
-        ok = mbar_wait(bar_k_empty, (j & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        mbar_arrive_expect_tx(bar_k_full, L::kKVTileBytes);
-        tma_load_5d(sK, &tmK, bar_k_full, 0, j * kBN, 0, hk, b);
-        ok = mbar_wait(bar_v_empty, (j & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        mbar_arrive_expect_tx(bar_v_full, L::kKVTileBytes);
-        tma_load_5d(sV, &tmV, bar_v_full, 0, j * kBN, 0, hk, b);
+        // K: two head-dim blocks per copy (the K map's box); V: 64 key rows per copy (the V map's
+        // box), which land as four [64 rows][64 dims] blocks
+        for (int half = 0; half < 2 && ok; ++half) {
+          ok = mbar_wait(bar_k_empty(half), (j & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_k_full(half), L::kHalfBytes);
+          tma_load_5d(sK + half * L::kHalfBytes, &tmK, bar_k_full(half), 0, j * kBN, 2 * half, hk, b);
+        }
+        for (int half = 0; half < 2 && ok; ++half) {
+          ok = mbar_wait(bar_v_empty(half), (j & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(bar_v_full(half), L::kHalfBytes);
+          tma_load_5d(sV + half * L::kHalfBytes, &tmV, bar_v_full(half), 0, j * kBN + 64 * half, 0, hk, b);
+        }
       }
       if (!ok) atomicOr(p.status, 1);
     }
@@ -146,46 +164,50 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       constexpr uint32_t idesc_o = make_idesc(kBf16, kBM, kD, false, true);
       const uint64_t dQ = make_sdesc(sQ, 16, 1024);
       const uint64_t dK = make_sdesc(sK, 16, 1024);
-      const uint64_t dV = make_sdesc(sV, kBlockBytes, 1024);
+      // a V half is four [64 rows][64 dims] blocks, 8 KiB apart
+      const uint64_t dVh = make_sdesc(sV, kBlockBytes / 2, 1024);
       bool ok = true;
-      auto issue_s = [&](int buf) {
+      // S = Q K^T into buffer `buf`, K tile number jk: each half of K is released as soon as the
+      // MMAs that contract over its dims have been issued
+      auto issue_s = [&](int buf, int jk) {
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k) {
-          const uint32_t off = (k >> 2) * kBlockBytes + (k & 3) * 32;
-          mma_ss_e(tmem_base + kColS + buf * kBN, sdesc_advance(dQ, off), sdesc_advance(dK, off),
-                 idesc_s, k > 0 ? 1u : 0u);
+        for (int half = 0; half < 2; ++half) {
+          if (ok) ok = mbar_wait_warp(bar_k_full(half), jk & 1, abort_flag);
+          if (!ok) return;
+          tc_fence_after();
+#pragma unroll
+          for (int k = half * (kD / 32); k < (half + 1) * (kD / 32); ++k) {
+            const uint32_t off = (k >> 2) * kBlockBytes + (k & 3) * 32;
+            mma_ss_e(tmem_base + kColS + buf * kBN, sdesc_advance(dQ, off), sdesc_advance(dK, off),
+                   idesc_s, k > 0 ? 1u : 0u);
+          }
+          mma_commit_e(bar_k_empty(half));
         }
         mma_commit_e(bar_s_full(buf));
-        mma_commit_e(bar_k_empty);
       };
       ok = mbar_wait_warp(bar_q_full, 0, abort_flag);
-      if (ok) ok = mbar_wait_warp(bar_k_full, 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-      }
+      if (ok) issue_s(0, 0);
       for (int j = 0; j < nt && ok; ++j) {
         const int buf = j & 1;
         if (j + 1 < nt) {
-          ok = mbar_wait_warp(bar_k_full, (j + 1) & 1, abort_flag);
+          issue_s(buf ^ 1, j + 1);
           if (!ok) break;
-          tc_fence_after();
-          issue_s(buf ^ 1);
         }
-        ok = mbar_wait_warp(bar_v_full, j & 1, abort_flag);
 #pragma unroll
         for (int half = 0; half < kPSplit; ++half) {
+          if (ok) ok = mbar_wait_warp(bar_v_full(half), j & 1, abort_flag);
           if (ok) ok = mbar_wait_warp(bar_p_full(buf, half), (j >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
-          for (int k = half * (kPCols / 16); k < (half + 1) * (kPCols / 16); ++k) {
-            mma_ts_e(tmem_base + kColO, tmem_base + kColS + buf * kBN + k * 8,
-                   sdesc_advance(dV, k * 2048), idesc_o, (j == 0 && k == 0) ? 0u : 1u);
+          for (int k = 0; k < kPCols / 16; ++k) {
+            mma_ts_e(tmem_base + kColO, tmem_base + kColS + buf * kBN + (half * (kPCols / 16) + k) * 8,
+                   sdesc_advance(dVh, half * L::kHalfBytes + k * 2048), idesc_o,
+                   (j == 0 && half == 0 && k == 0) ? 0u : 1u);
           }
+          mma_commit_e(bar_v_empty(half));
         }
         if (!ok) break;
-        mma_commit_e(bar_v_empty);
         mma_commit_e(bar_pv_done);
         if (j + 1 == nt) mma_commit_e(bar_o_full);
       }
