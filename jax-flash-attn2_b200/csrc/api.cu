@@ -18,6 +18,10 @@
 #include "fwd_launch.cuh"
 #include "launch_util.cuh"
 
+#ifndef FA2_FWD256_PARTS
+#define FA2_FWD256_PARTS 2
+#endif
+
 namespace fa2 {
 namespace {
 
@@ -321,9 +325,9 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   // head dim 256: K arrives in halves of the head dim, V in halves of the 128 key rows
   if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, sq_k, hq_k, hd, q_st, 128, "q")) ||
       (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k",
-                      D == 256 ? 2 : 0)) ||
+                      D == 256 ? 4 / FA2_FWD256_PARTS : 0)) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides,
-                      D == 256 ? 64 : 128, "v")) ||
+                      D == 256 ? 128 / FA2_FWD256_PARTS : 128, "v")) ||
       (rc = make_tmap(&L.tmO, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
       (rc = make_tmap(&L.tmO1, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
     return rc;

@@ -23,6 +23,12 @@ namespace fa2 {
 
 namespace {
 
+// Pieces a K / V slot is handed over in (2 or 4). Measured on config 5: one piece 1.20 ms, two
+// 1.10-1.12 ms, four 1.11 ms.
+#ifndef FA2_FWD256_PARTS
+#define FA2_FWD256_PARTS 2
+#endif
+
 constexpr int kD = 256;
 constexpr int kThreads256 = 192;
 
@@ -35,8 +41,9 @@ struct Smem256 {
   static constexpr int kBarOff = kVOff + kKVTileBytes;
   // barriers: q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2 buffers][2 halves],
   // pv_done, o_full, then the second-half barriers k_full, k_empty, v_full, v_empty
-  static constexpr int kNumBars = 9 + 2 * kPSplit + 4;
-  static constexpr int kHalfBytes = kKVTileBytes / 2;
+  static constexpr int kParts = FA2_FWD256_PARTS;      // pieces a K / V slot is handed over in
+  static constexpr int kNumBars = 9 + 2 * kPSplit + 4 * kParts;
+  static constexpr int kHalfBytes = kKVTileBytes / kParts;
   static_assert(kPSplit == 2, "V halves follow the two halves of P");
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
@@ -57,11 +64,11 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const uint32_t sQ = smem_base + L::kQOff, sK = smem_base + L::kKOff, sV = smem_base + L::kVOff;
   const uint32_t bars = smem_base + L::kBarOff;
   const uint32_t bar_q_full = bars;
-  const uint32_t bars2 = bars + 8u * (9 + 2 * kPSplit);   // second-half barriers
-  auto bar_k_full = [&](int half) { return half == 0 ? bars + 8 : bars2; };
-  auto bar_k_empty = [&](int half) { return half == 0 ? bars + 16 : bars2 + 8; };
-  auto bar_v_full = [&](int half) { return half == 0 ? bars + 24 : bars2 + 16; };
-  auto bar_v_empty = [&](int half) { return half == 0 ? bars + 32 : bars2 + 24; };
+  const uint32_t bars2 = bars + 8u * (9 + 2 * kPSplit);   // per-piece barriers
+  auto bar_k_full = [&](int part) { return bars2 + 8u * (4 * part); };
+  auto bar_k_empty = [&](int part) { return bars2 + 8u * (4 * part + 1); };
+  auto bar_v_full = [&](int part) { return bars2 + 8u * (4 * part + 2); };
+  auto bar_v_empty = [&](int part) { return bars2 + 8u * (4 * part + 3); };
   auto bar_s_full = [&](int s) { return bars + 8u * (5 + s); };
   auto bar_p_full = [&](int s, int half) { return bars + 8u * (7 + kPSplit * s + half); };
   const uint32_t bar_pv_done = bars + 8u * (7 + 2 * kPSplit), bar_o_full = bars + 8u * (8 + 2 * kPSplit);
@@ -102,7 +109,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   if (tid == 0) {
     *abort_flag = 0;
     mbar_init(bar_q_full, 1);
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < L::kParts; ++half) {
       mbar_init(bar_k_full(half), 1);
       mbar_init(bar_k_empty(half), 1);
       mbar_init(bar_v_full(half), 1);
@@ -141,17 +148,17 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       for (int j = 0; j < nt && ok; ++j) {
         // K: two head-dim blocks per copy (the K map's box); V: 64 key rows per copy (the V map's
         // box), which land as four [64 rows][64 dims] blocks
-        for (int half = 0; half < 2 && ok; ++half) {
+        for (int half = 0; half < L::kParts && ok; ++half) {
           ok = mbar_wait(bar_k_empty(half), (j & 1) ^ 1, abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(bar_k_full(half), L::kHalfBytes);
-          tma_load_5d(sK + half * L::kHalfBytes, &tmK, bar_k_full(half), 0, j * kBN, 2 * half, hk, b);
+          tma_load_5d(sK + half * L::kHalfBytes, &tmK, bar_k_full(half), 0, j * kBN, (4 / L::kParts) * half, hk, b);
         }
-        for (int half = 0; half < 2 && ok; ++half) {
+        for (int half = 0; half < L::kParts && ok; ++half) {
           ok = mbar_wait(bar_v_empty(half), (j & 1) ^ 1, abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(bar_v_full(half), L::kHalfBytes);
-          tma_load_5d(sV + half * L::kHalfBytes, &tmV, bar_v_full(half), 0, j * kBN + 64 * half, 0, hk, b);
+          tma_load_5d(sV + half * L::kHalfBytes, &tmV, bar_v_full(half), 0, j * kBN + (kBN / L::kParts) * half, 0, hk, b);
         }
       }
       if (!ok) atomicOr(p.status, 1);
@@ -165,18 +172,18 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       const uint64_t dQ = make_sdesc(sQ, 16, 1024);
       const uint64_t dK = make_sdesc(sK, 16, 1024);
       // a V half is four [64 rows][64 dims] blocks, 8 KiB apart
-      const uint64_t dVh = make_sdesc(sV, kBlockBytes / 2, 1024);
+      const uint64_t dVh = make_sdesc(sV, kBlockBytes / L::kParts, 1024);
       bool ok = true;
       // S = Q K^T into buffer `buf`, K tile number jk: each half of K is released as soon as the
       // MMAs that contract over its dims have been issued
       auto issue_s = [&](int buf, int jk) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < L::kParts; ++half) {
           if (ok) ok = mbar_wait_warp(bar_k_full(half), jk & 1, abort_flag);
           if (!ok) return;
           tc_fence_after();
 #pragma unroll
-          for (int k = half * (kD / 32); k < (half + 1) * (kD / 32); ++k) {
+          for (int k = half * (kD / 16 / L::kParts); k < (half + 1) * (kD / 16 / L::kParts); ++k) {
             const uint32_t off = (k >> 2) * kBlockBytes + (k & 3) * 32;
             mma_ss_e(tmem_base + kColS + buf * kBN, sdesc_advance(dQ, off), sdesc_advance(dK, off),
                    idesc_s, k > 0 ? 1u : 0u);
@@ -194,18 +201,21 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           if (!ok) break;
         }
 #pragma unroll
-        for (int half = 0; half < kPSplit; ++half) {
-          if (ok) ok = mbar_wait_warp(bar_v_full(half), j & 1, abort_flag);
-          if (ok) ok = mbar_wait_warp(bar_p_full(buf, half), (j >> 1) & 1, abort_flag);
+        for (int part = 0; part < L::kParts; ++part) {
+          constexpr int kStepsPerPart = kBN / 16 / L::kParts;          // 16-key MMA steps per piece of V
+          constexpr int kPartsPerHalf = L::kParts / kPSplit;           // pieces of V per half of P
+          if (ok) ok = mbar_wait_warp(bar_v_full(part), j & 1, abort_flag);
+          if (ok && part % kPartsPerHalf == 0)
+            ok = mbar_wait_warp(bar_p_full(buf, part / kPartsPerHalf), (j >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < kPCols / 16; ++k) {
-            mma_ts_e(tmem_base + kColO, tmem_base + kColS + buf * kBN + (half * (kPCols / 16) + k) * 8,
-                   sdesc_advance(dVh, half * L::kHalfBytes + k * 2048), idesc_o,
-                   (j == 0 && half == 0 && k == 0) ? 0u : 1u);
+          for (int k = 0; k < kStepsPerPart; ++k) {
+            mma_ts_e(tmem_base + kColO, tmem_base + kColS + buf * kBN + (part * kStepsPerPart + k) * 8,
+                   sdesc_advance(dVh, part * L::kHalfBytes + k * 2048), idesc_o,
+                   (j == 0 && part == 0 && k == 0) ? 0u : 1u);
           }
-          mma_commit_e(bar_v_empty(half));
+          mma_commit_e(bar_v_empty(part));
         }
         if (!ok) break;
         mma_commit_e(bar_pv_done);
