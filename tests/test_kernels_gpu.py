@@ -175,6 +175,27 @@ def test_per_batch_lengths(D, dtype, causal, S, lengths, extras):
             assert rel_l2(sl(mine), ref) <= GRAD_TOL, (name, b, rel_l2(sl(mine), ref))
 
 
+def test_per_batch_lengths_on_a_split_problem():
+    """Lengths and split-KV together: a low-occupancy problem (split along the keys) whose batch
+    elements are shorter than the buffers."""
+    J = _J()
+    B, S, Hq, Hkv, D, dtype = 2, 2048, 2, 1, 128, torch.bfloat16
+    lengths = [1500, 129]
+    q, k, v, do = W.make_qkv(B, S, S, Hq, Hkv, D, dtype, D ** -0.25)
+    seqlens = torch.tensor(lengths, dtype=torch.int32).cuda()
+    args = (q.cuda(), k.cuda(), v.cuda(), None, None, None, 0.0, True, None)
+    o_s, l_s = J.fwd_attention_kernel_call(*args, seqlens=seqlens)
+    o_u, l_u = J.fwd_attention_kernel_call(*args, seqlens=seqlens, split_kv=False)
+    assert J.device_status() == 0
+    blk = BlockAttention()
+    for b, n in enumerate(lengths):
+        ro, rl = blk.forward(q[b:b + 1, :n], k[b:b + 1, :n], v[b:b + 1, :n], causal=True)
+        for o, l in ((o_s, l_s), (o_u, l_u)):
+            assert (o[b:b + 1, :n].cpu().float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
+            assert (l[b:b + 1, :, :n].cpu() - rl).abs().max().item() <= LSE_TOL
+            assert torch.all(o[b, n:] == 0) and torch.all(l[b, :, n:S] == float("-inf"))
+
+
 def test_seqlens_needs_equal_sequence_lengths():
     J = _J()
     q, k, v, _ = W.make_qkv(1, 128, 256, 2, 2, 64, torch.bfloat16)
