@@ -7,7 +7,8 @@ a small numpy stand-in for exactly those calls under the module names `jax`, `ja
 `jax.lax`, `jax.sharding` and `eformer.escale`, loads the reference's source files unmodified
 from REFERENCE_ROOT, runs them on seeded inputs and stores inputs and outputs. The vectors pin
 oracle/block.py (see tests/test_oracle.py). Nothing is copied from the reference: it is executed
-where it lies. Run:  python tests/golden/make_golden.py [/path/to/reference]
+where it lies. Run:  python tests/golden/make_golden.py /path/to/reference
+(or set REFERENCE_ROOT in the environment).
 """
 from __future__ import annotations
 
@@ -19,7 +20,9 @@ import types
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_ROOT = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REFERENCE_ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", "")
+if not os.path.isdir(REFERENCE_ROOT):
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/jax-flash-attn2 (the reference checkout)")
 
 
 def _install_numpy_jax():
