@@ -68,7 +68,7 @@ struct BwdSmem {
   static constexpr int kdSOff = kStageOff + 2 * kChunkBytes;   // [128 keys][128 queries] 16 bit
   static constexpr int kStatsOff = kdSOff + 128 * 128 * 2; // 2 stages x (lse2[128], delta[128])
   static constexpr int kBarOff = kStatsOff + 2 * 1024;
-  static constexpr int kNumBars = 16;
+  static constexpr int kNumBars = 17;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
@@ -170,6 +170,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t bar_dp_full = bars + 8u * 11, bar_ds_full = bars + 8u * 12;
   const uint32_t bar_dq_full = bars + 8u * 13, bar_dq_drained = bars + 8u * 14;
   const uint32_t bar_dkv_full = bars + 8u * 15;
+  const uint32_t bar_kv_tmem = bars + 8u * 16;   // D = 64: K and V have been copied into tensor memory
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
@@ -216,6 +217,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_drained, 128);
     mbar_init(bar_dkv_full, 1);
+    mbar_init(bar_kv_tmem, 256);
     fence_mbar_init();
   }
   if (warp == kWarpTma && lane == 0) {
@@ -234,6 +236,11 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
   constexpr uint32_t kColS = 0, kColdP = 128, kColdK = 256, kColdV = 256 + D;
   constexpr uint32_t kColdQ = (D == 128) ? 128 : 384;
+  // D = 64 leaves 64 columns free: K and V (16 bit, 32 columns each) live there as well, so that
+  // S^T = K Q^T and dP^T = V dO^T read their loop-invariant A operand from tensor memory instead of
+  // shared memory, the resource this kernel is bound by.
+  constexpr bool kKvInTmem = (D == 64);
+  constexpr uint32_t kColKt = 448, kColVt = 480;
 
   auto step_coords = [&](int it, int& h, int& i) {
     const int g = it / nI;
@@ -291,11 +298,18 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint64_t ddO_k = make_sdesc(sdO, 16, 1024), ddO_mn = make_sdesc(sdO, L::kBlockBytes, 1024);
       const uint64_t ddS_k = make_sdesc(sdS, 16, 1024), ddS_mn = make_sdesc(sdS, L::kBlockBytes, 1024);
 
-      // D[kv, q] = A[kv, d] * B[q, d]^T, both operands K-major over the head dim
+      // D[kv, q] = A[kv, d] * B[q, d]^T, both operands K-major over the head dim; at D = 64 the A
+      // operand (K for S^T, V for dP^T) comes from tensor memory: 8 columns per 16 dims
       auto issue_kd = [&](uint32_t d_col, uint64_t a_desc, uint64_t b_desc) {
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
+          if constexpr (kKvInTmem) {
+            const uint32_t a_col = (d_col == kColS ? kColKt : kColVt) + 8 * k;
+            mma_ts_e(tmem_base + d_col, tmem_base + a_col, sdesc_advance(b_desc, off), idesc_s,
+                     k > 0 ? 1u : 0u);
+            continue;
+          }
           mma_ss_e(tmem_base + d_col, sdesc_advance(a_desc, off), sdesc_advance(b_desc, off), idesc_s,
                  k > 0 ? 1u : 0u);
         }
@@ -328,6 +342,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       };
 
       ok = mbar_wait_warp(bar_kv_full, 0, abort_flag);
+      if (kKvInTmem && ok) ok = mbar_wait_warp(bar_kv_tmem, 0, abort_flag);
       if (ok) ok = mbar_wait_warp(bar_q_full(0), 0, abort_flag);
       if (ok) {
         tc_fence_after();
@@ -468,7 +483,32 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float do_scale = kBf16 ? 1.f : do_scale_from_bits(p.do_absmax_bits);
     bool ok = true;
 
-    for (int it = 0; it < T; ++it) {
+    if constexpr (kKvInTmem) {
+      // One-time: warpgroup 0 copies K, warpgroup 1 copies V into tensor memory, one key row per
+      // thread (= lane), two 16-bit values per column in head-dim order (the layout of a 16-bit
+      // A operand, the one P^T is written in). K also stays in shared memory for dQ.
+      if (w < 2 && T > 0) {
+        ok = mbar_wait(bar_kv_full, 0, abort_flag);
+        if (ok) {
+          const uint8_t* src = smem_gen + (w == 0 ? L::kKOff : L::kVOff) + r * 128;
+          uint32_t kx[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 v4 = *reinterpret_cast<const uint4*>(src + ((j ^ (r & 7)) << 4));
+            kx[4 * j + 0] = v4.x;
+            kx[4 * j + 1] = v4.y;
+            kx[4 * j + 2] = v4.z;
+            kx[4 * j + 3] = v4.w;
+          }
+          tmem_st32(tmem_base + lane_base + (w == 0 ? kColKt : kColVt), kx);
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar_kv_tmem);
+        }
+      }
+    }
+
+    for (int it = 0; it < T && ok; ++it) {
       const int st = it & 1;
       int h, i;
       step_coords(it, h, i);
