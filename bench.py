@@ -44,6 +44,8 @@ WORKLOADS = {
     "long_context_causal_bf16": (1, 32768, 32768, 64, 8, 128, torch.bfloat16, True, 1.0 / math.sqrt(128)),
     "mha_bias_mask_dropout_bf16": (4, 2048, 2048, 16, 16, 64, torch.bfloat16, False, 1.0),
     "head_dim_256_causal_fp16": (4, 8192, 8192, 8, 8, 256, torch.float16, True, 1.0 / 16),
+    # a quarter of the batch: the small case the ncu captures of the head-dim-256 kernels run on
+    "head_dim_256_causal_fp16_b1": (1, 8192, 8192, 8, 8, 256, torch.float16, True, 1.0 / 16),
 }
 # additive bias 1/(1+|i-j|), key-padding mask (valid length U[S/2, S] per batch element, finfo.min
 # beyond it), dropout 0.1 with seed 42
