@@ -69,8 +69,8 @@ bwd256_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, l
                   long long ss, long long sh, int Sq, int Hq, int nQ64, float scale_in,
                   const unsigned* __restrict__ do_absmax_bits, int blk_real) {
   const float scale = scale_in / (kBf16 ? 1.f : do_scale_from_bits(do_absmax_bits));
-  const int i = blockIdx.x;
-  const int bh = blockIdx.y;
+  const int i = blockIdx.x % nQ64;   // one-dimensional grid, tile index fastest
+  const int bh = blockIdx.x / nQ64;
   const int b = bh / Hq, h = bh - b * Hq;
   const int tid = threadIdx.x;
   const int dpair = tid & 63;                 // dims 2*dpair, 2*dpair + 1 of a half
@@ -638,7 +638,7 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
     if (em != cudaSuccess) return em;
   }
   mark(0);
-  bwd_pre_kernel<kD, kBf16><<<dim3(nQ128, kp.B * kp.Hq), 128, 0, stream>>>(
+  bwd_pre_kernel<kD, kBf16><<<static_cast<unsigned>(static_cast<long long>(nQ128) * kp.B * kp.Hq), 128, 0, stream>>>(
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax,
@@ -655,7 +655,7 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
   }
   if (e != cudaSuccess) return e;
   mark(2);
-  bwd256_dq_convert<kBf16><<<dim3(nQ64, kp.B * kp.Hq), 256, 0, stream>>>(
+  bwd256_dq_convert<kBf16><<<static_cast<unsigned>(static_cast<long long>(nQ64) * kp.B * kp.Hq), 256, 0, stream>>>(
       kp.dq_acc, static_cast<uint16_t*>(a.dq), a.dq_strides[0], a.dq_strides[1], a.dq_strides[2],
       kp.Sq, kp.Hq, nQ64, kp.scale, kBf16 ? nullptr : kp.do_absmax_bits, a.head_blk);
   mark(3);

@@ -124,8 +124,9 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ,
                unsigned* __restrict__ do_absmax_bits, int d_real,
                const int* __restrict__ seqlens) {
-  const int i = blockIdx.x;
-  const int bh = blockIdx.y;
+  // one-dimensional grid (the y and z extents of a grid stop at 65535): tile index fastest
+  const int i = blockIdx.x % nQ;
+  const int bh = blockIdx.x / nQ;
   const int b = bh / Hq, h = bh - b * Hq;
   // rows past a batch element's own length take no gradient (and their dO is never read)
   const int sq_b = seqlens ? max(0, min(__ldg(seqlens + b), Sq)) : Sq;

@@ -102,8 +102,8 @@ bwd_dq_convert(const float* __restrict__ dq_acc, uint16_t* __restrict__ dq, long
   const float scale = scale_in / (kBf16 ? 1.f : do_scale_from_bits(do_absmax_bits));
   constexpr int kPitch = 129;                       // float4 per column chunk: 128 rows + 1 pad
   __shared__ float4 tile[16 * kPitch];              // 16 chunks of 4 columns = 64 columns
-  const int i = blockIdx.x;
-  const int bh = blockIdx.y;
+  const int i = blockIdx.x % nQ;     // one-dimensional grid, tile index fastest
+  const int bh = blockIdx.x / nQ;
   const int b = bh / Hq, h = bh - b * Hq;
   const int tid = threadIdx.x;
   const float4* src = reinterpret_cast<const float4*>(dq_acc) +
@@ -720,7 +720,7 @@ template <int D, bool kBf16>
 static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   const BwdKernelParams& kp = a.kp;
   const int nQ = (kp.Sq + kBM - 1) / kBM;
-  const dim3 grid(nQ, kp.B * kp.Hq);
+  const unsigned grid = static_cast<unsigned>(static_cast<long long>(nQ) * kp.B * kp.Hq);
   auto mark = [&](int i) {
     if (a.stage_events[i]) cudaEventRecord(a.stage_events[i], stream);
   };

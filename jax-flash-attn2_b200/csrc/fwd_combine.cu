@@ -16,7 +16,10 @@ fwd_combine_kernel(const uint16_t* __restrict__ part_o, const float* __restrict_
                    uint16_t* __restrict__ o, long long osb, long long oss, long long osh,
                    float* __restrict__ lse, long long lse_sb, long long lse_sh, long long lse_sq,
                    int n_splits, int B, int Sq, int Hq, int D, int sq_pad) {
-  const int s = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // one-dimensional grid (the y and z extents of a grid stop at 65535): row fastest, then head
+  const int s = blockIdx.x % Sq;
+  const int h = (blockIdx.x / Sq) % Hq;
+  const int b = blockIdx.x / (Sq * Hq);
   const long long lse_split = static_cast<long long>(B) * Hq * sq_pad;
   const float* pl = part_lse + (static_cast<long long>(b) * Hq + h) * sq_pad + s;
   float m = -INFINITY;
@@ -41,7 +44,7 @@ fwd_combine_kernel(const uint16_t* __restrict__ part_o, const float* __restrict_
 }
 
 cudaError_t launch_fwd_combine(const FwdCombine& c, cudaStream_t stream) {
-  const dim3 grid(c.Sq, c.Hq, c.B);
+  const unsigned grid = static_cast<unsigned>(static_cast<long long>(c.Sq) * c.Hq * c.B);
   if (c.bf16)
     fwd_combine_kernel<true><<<grid, 128, 0, stream>>>(
         static_cast<const uint16_t*>(c.part_o), c.part_lse, static_cast<uint16_t*>(c.o), c.o_strides[0],

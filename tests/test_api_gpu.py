@@ -252,3 +252,25 @@ def test_calls_on_two_streams_and_two_host_threads_do_not_interfere():
         assert torch.equal(o, o_ref) and torch.equal(g[1], g_ref[1]) and torch.equal(g[2], g_ref[2])
         assert rel_l2(g[0], g_ref[0]) < 1e-3
     assert J.device_status() == 0
+
+
+def test_more_than_65535_batch_times_heads():
+    """batch x heads beyond the 65535 limit of a grid's second dimension (every launch uses a
+    one-dimensional grid): B=1100, H=64, 16 tokens each; three batch elements against the oracle."""
+    import jax_flash_attn2 as J
+    B, S, H, D = 1100, 16, 64, 64
+    q, k, v, do = W.make_qkv(B, S, S, H, H, D, torch.bfloat16, 0.5)
+    qc, kc, vc, doc = (x.cuda() for x in (q, k, v, do))
+    out, lse = J.fwd_attention_kernel_call(qc, kc, vc, None, None, None, 0.0, True, None)
+    dq, dk, dv = J.bwd_attention_kernel_call(doc, qc, kc, vc, None, None, out, lse, 0.0, True, None, None)
+    assert J.device_status() == 0
+    blk = BlockAttention()
+    for b in (0, 517, B - 1):
+        sl = lambda x: x[b:b + 1]
+        ro, rl = blk.forward(sl(q), sl(k), sl(v), causal=True)
+        assert (sl(out).cpu().float() - ro.float()).abs().max().item() <= 2e-2
+        assert (lse[b:b + 1, :, :S].cpu() - rl).abs().max().item() <= 1e-3
+        ref = blk.backward(sl(do), sl(q), sl(k), sl(v), sl(out).cpu(), lse[b:b + 1, :, :S].cpu(), causal=True,
+                           out_dtype=torch.float32)
+        for mine, want in zip((dq, dk, dv), ref):
+            assert rel_l2(sl(mine).cpu(), want) <= 1e-2
