@@ -200,7 +200,7 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   return w;
 }
 
-// Split-KV plan of the forward (head dim <= 128 kernel only): how many parts the key sequence is
+// Split-KV plan of the forward: how many parts the key sequence is
 // cut into and how many K/V tiles each part gets. A problem is split when its (query block,
 // batch, head) items would leave more than half of the SMs idle and the key sequence is long
 // enough to share out.
@@ -215,9 +215,11 @@ SplitPlan plan_splits(const fa2_problem& p, const HeadDim& hd, bool pack_heads) 
   s.sq_k = pack_heads ? p.heads_q / p.heads_kv : p.seqlen_q;
   s.hq_k = pack_heads ? p.heads_kv : p.heads_q;
   const int n_tiles = (p.seqlen_k + 127) / 128;
-  const long long items = static_cast<long long>((s.sq_k + 255) / 256) * p.batch * s.hq_k;
+  // work items: 256 query rows per item in the head dim <= 128 kernel, 128 in the head dim 256 one
+  const int item_rows = hd.padded > 128 ? 128 : 256;
+  const long long items = static_cast<long long>((s.sq_k + item_rows - 1) / item_rows) * p.batch * s.hq_k;
   const int sms = sm_count();
-  if (hd.padded > 128 || n_tiles < 8 || items * 2 > sms) return s;
+  if (n_tiles < 8 || items * 2 > sms) return s;
   int want = static_cast<int>(std::min<long long>(std::min<long long>(sms / items, n_tiles / 4), 32));
   if (want < 2) return s;
   s.split_tiles = (n_tiles + want - 1) / want;

@@ -80,10 +80,14 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   const int lane = tid & 31;
 
   // ---- work item: one 128-row query tile of one (batch, head); longest tiles first if causal --
+  // split-KV: the grid holds n_splits CTAs per item, each with its own range of K/V tiles
+  const int split = p.n_splits > 1 ? static_cast<int>(blockIdx.x % p.n_splits) : 0;
+  const int item = p.n_splits > 1 ? static_cast<int>(blockIdx.x / p.n_splits) : static_cast<int>(blockIdx.x);
+  const int j0 = split * p.split_tiles;          // first K/V tile of this CTA
   const int nbh = p.B * p.Hq;
   const int n_qtiles = (p.Sq + kBM - 1) / kBM;
-  const int rank = blockIdx.x / nbh;
-  const int bh = blockIdx.x - rank * nbh;
+  const int rank = item / nbh;
+  const int bh = item - rank * nbh;
   const int qt = kCausal ? (n_qtiles - 1 - rank) : rank;
   const int b = bh / p.Hq;
   const int h = bh - b * p.Hq;
@@ -105,6 +109,8 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
   } else {
     nt = (sk_b + kBN - 1) / kBN;
   }
+  if (p.n_splits > 1) nt = max(0, min(nt - j0, p.split_tiles));
+  const int b_out = b + split * p.B;             // where this CTA's output and lse go
 
   if (tid == 0) {
     *abort_flag = 0;
@@ -152,13 +158,13 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
           ok = mbar_wait(bar_k_empty(half), (j & 1) ^ 1, abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(bar_k_full(half), L::kHalfBytes);
-          tma_load_5d(sK + half * L::kHalfBytes, &tmK, bar_k_full(half), 0, j * kBN, (4 / L::kParts) * half, hk, b);
+          tma_load_5d(sK + half * L::kHalfBytes, &tmK, bar_k_full(half), 0, (j0 + j) * kBN, (4 / L::kParts) * half, hk, b);
         }
         for (int half = 0; half < L::kParts && ok; ++half) {
           ok = mbar_wait(bar_v_empty(half), (j & 1) ^ 1, abort_flag);
           if (!ok) break;
           mbar_arrive_expect_tx(bar_v_full(half), L::kHalfBytes);
-          tma_load_5d(sV + half * L::kHalfBytes, &tmV, bar_v_full(half), 0, j * kBN + (kBN / L::kParts) * half, 0, hk, b);
+          tma_load_5d(sV + half * L::kHalfBytes, &tmV, bar_v_full(half), 0, (j0 + j) * kBN + (kBN / L::kParts) * half, 0, hk, b);
         }
       }
       if (!ok) atomicOr(p.status, 1);
@@ -245,7 +251,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag)) ok = false;
         tc_fence_after();
       };
-      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv,
+      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j0 + j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv,
                                          [&](int half) { return mbar_arrive_zero(bar_p_full(buf, half)); });
       if (!ok) break;
     }
@@ -254,11 +260,11 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (ok && nt > 0) ok = mbar_wait(bar_o_full, 0, abort_flag);
     if (ok) {
       tc_fence_after();
-      epilogue_row<kD, kBf16, kFeat>(tO, nt > 0, smem_gen + L::kQOff, r, p, b, h, qi, sc, m, l);
+      epilogue_row<kD, kBf16, kFeat>(tO, nt > 0, smem_gen + L::kQOff, r, p, b_out, h, qi, sc, m, l);
     }
     named_bar_sync(1, kBM);
     if (ok && r == 0 && !*abort_flag) {
-      tma_store_5d(&tmO, sQ, 0, q0, 0, h, b);
+      tma_store_5d(&tmO, sQ, 0, q0, 0, h, b_out);
       tma_store_commit();
       tma_store_wait_read0();
     }
@@ -280,7 +286,7 @@ static cudaError_t launch256_one(const FwdLaunch& a, cudaStream_t stream) {
   cudaError_t e = opt_in_dynamic_smem(kern, Smem256::kDynamicBytes, smem_opted_in);
   if (e != cudaSuccess) return e;
   const long long nblocks =
-      static_cast<long long>((a.kp.Sq + kBM - 1) / kBM) * a.kp.B * a.kp.Hq;
+      static_cast<long long>((a.kp.Sq + kBM - 1) / kBM) * a.kp.B * a.kp.Hq * a.kp.n_splits;
   kern<<<static_cast<unsigned>(nblocks), kThreads256, Smem256::kDynamicBytes, stream>>>(
       a.tmQ, a.tmK, a.tmV, a.tmO, a.kp);
   return cudaGetLastError();

@@ -231,6 +231,8 @@ def test_decode_rows_with_grouped_heads(D, dtype, B, Sk, Hq, Hkv, causal):
     dict(B=1, Sq=256, Sk=4096, Hq=2, Hkv=1, D=128, dtype=torch.bfloat16, causal=True),    # short prefill chunk
     dict(B=1, Sq=300, Sk=3000, Hq=4, Hkv=2, D=96, dtype=torch.float16, causal=True, p=0.1, bias_heads=4),
     dict(B=1, Sq=2048, Sk=2048, Hq=4, Hkv=4, D=128, dtype=torch.bfloat16, causal=True),   # some splits see no key
+    dict(B=1, Sq=1, Sk=9000, Hq=16, Hkv=4, D=256, dtype=torch.bfloat16, causal=False),    # decode, head dim 256
+    dict(B=1, Sq=384, Sk=2500, Hq=2, Hkv=2, D=192, dtype=torch.float16, causal=True, p=0.1),
 ])
 def test_split_kv_low_occupancy_problems(case):
     """Problems with few (batch, head, query tile) items are cut along the key sequence and merged
