@@ -18,10 +18,6 @@
 #include "fwd_launch.cuh"
 #include "launch_util.cuh"
 
-#ifndef FA2_FWD256_PARTS
-#define FA2_FWD256_PARTS 2
-#endif
-
 namespace fa2 {
 namespace {
 
@@ -122,7 +118,7 @@ int make_tmap(CUtensorMap* tm, const void* ptr, bool bf16, int B, int S, int H, 
   return FA2_OK;
 }
 
-int check_problem(const fa2_problem& p, bool backward = false) {
+int check_problem(const fa2_problem& p) {
   if (p.batch <= 0 || p.seqlen_q <= 0 || p.seqlen_k <= 0 || p.heads_q <= 0 || p.heads_kv <= 0)
     return fail(FA2_ERR_INVALID_ARG, "batch, sequence lengths and head counts must be positive");
   if (p.heads_q % p.heads_kv != 0)
@@ -130,7 +126,6 @@ int check_problem(const fa2_problem& p, bool backward = false) {
                 p.heads_q, p.heads_kv);
   if (p.dtype != FA2_FP16 && p.dtype != FA2_BF16)
     return fail(FA2_ERR_UNSUPPORTED, "only fp16 and bf16 inputs are supported");
-  (void)backward;
   HeadDim hd;
   if (!split_head_dim(p.head_dim, &hd))
     return fail(FA2_ERR_UNSUPPORTED,
@@ -327,9 +322,9 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   // head dim 256: K arrives in halves of the head dim, V in halves of the 128 key rows
   if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, sq_k, hq_k, hd, q_st, 128, "q")) ||
       (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k",
-                      D == 256 ? 4 / FA2_FWD256_PARTS : 0)) ||
+                      D == 256 ? 4 / kKV256Parts : 0)) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides,
-                      D == 256 ? 128 / FA2_FWD256_PARTS : 128, "v")) ||
+                      D == 256 ? 128 / kKV256Parts : 128, "v")) ||
       (rc = make_tmap(&L.tmO, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
       (rc = make_tmap(&L.tmO1, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
     return rc;
@@ -406,14 +401,14 @@ size_t fa2_fwd_workspace_bytes(const fa2_problem* problem) {
 }
 
 size_t fa2_bwd_workspace_bytes(const fa2_problem* problem) {
-  if (!problem || check_problem(*problem, true)) return 0;
+  if (!problem || check_problem(*problem)) return 0;
   return bwd_workspace(*problem).total;
 }
 
 int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
   const fa2_problem& p = a->p;
-  int rc = check_problem(p, true);
+  int rc = check_problem(p);
   if (rc) return rc;
   if (!a->q || !a->k || !a->v || !a->o || !a->d_o || !a->lse || !a->dq || !a->dk || !a->dv)
     return fail(FA2_ERR_INVALID_ARG, "q, k, v, o, d_o, lse, dq, dk and dv must be non-null");
@@ -533,7 +528,7 @@ int static_scratch_address(void** out) {
 
 int fa2_bwd_static_scratch(const fa2_bwd_params* a, void* cuda_stream) {
   if (!a) return fail(FA2_ERR_INVALID_ARG, "params is null");
-  const int rc = check_problem(a->p, true);
+  const int rc = check_problem(a->p);
   if (rc) return rc;
   const size_t need = bwd_workspace(a->p).total;
   if (need > static_cast<size_t>(FA2_BWD_STATIC_SCRATCH_BYTES))

@@ -239,7 +239,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __syncwarp();
   } else if (warp == 12) {
     // =========================== MMA issuer ==================================================
-    if (true && T > 0) {
+    if (T > 0) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, 128, kBQ, false, false);
       constexpr uint32_t idesc_dkv = make_idesc(kBf16, 128, 128, false, true);
       constexpr uint32_t idesc_dq = make_idesc(kBf16, 128, kBQ, true, true);

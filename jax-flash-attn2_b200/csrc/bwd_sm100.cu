@@ -39,11 +39,7 @@ constexpr int kBN = 128;   // keys per CTA
 //            then takes a D = 128 tile in two halves, fits in 80
 template <int D>
 struct BwdRoles {
-#ifdef FA2_BWD_PWG
-  static constexpr int kPW = FA2_BWD_PWG;
-#else
   static constexpr int kPW = (D == 64) ? 4 : 2;
-#endif
   static_assert(kPW == 2 || kPW == 4, "2 or 4 P/dS warpgroups");
   static constexpr int kCW = 128 / kPW;                 // query columns per P/dS warpgroup
   static constexpr int kThreads = (kPW + 2) * 128;
@@ -78,13 +74,6 @@ struct BwdSmem {
 __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&x)[32]) { tmem_st32(taddr, x); }
 __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&x)[16]) { tmem_st16(taddr, x); }
 
-#ifdef FA2_TRACE
-// Development aid (not compiled by default): per-role time stamps of CTA 0.
-__device__ long long g_trace[48 * 4096];
-#define FA2_T(role, idx) do { if (blockIdx.x == FA2_TRACE_CTA && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64(); } while (0)
-#else
-#define FA2_T(role, idx) do { } while (0)
-#endif
 
 }  // namespace
 
@@ -282,7 +271,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     __syncwarp();
   } else if (warp == kWarpMma) {
     // =========================== MMA issuer ==================================================
-    if (true && T > 0) {
+    if (T > 0) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, 128, 128, false, false);
       constexpr uint32_t idesc_dv = make_idesc(kBf16, 128, D, false, true);
       constexpr uint32_t idesc_dk = make_idesc(kBf16, 128, D, false, true);
@@ -362,34 +351,27 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool has_next = it + 1 < T;
         ok = mbar_wait_warp(bar_p_full, par, abort_flag);
         if (!ok) break;
-        FA2_T(0, it);
         tc_fence_after();
         issue_dv(it == 0);
         mma_commit_e(bar_do_empty);          // the single dO buffer can be refilled
         if (has_next) {
-          FA2_T(40, it);
           ok = mbar_wait_warp(bar_q_full(nx), par_next, abort_flag);
           if (!ok) break;
-          FA2_T(41, it);
           tc_fence_after();
           issue_kd(kColS, dK_k, sdesc_advance(dQ_k0, nx * L::kTileBytes));
           mma_commit_e(bar_s_full);
         }
-        FA2_T(1, it);
         ok = mbar_wait_warp(bar_ds_full, par, abort_flag);
         if (!ok) break;
-        FA2_T(2, it);
         tc_fence_after();
         issue_dq();
         mma_commit_e(bar_dq_full);
         issue_dk(sdesc_advance(dQ_mn0, st * L::kTileBytes), it == 0);
         mma_commit_e(bar_q_empty(st));
         if (has_next) {
-          FA2_T(3, it);
           ok = mbar_wait_warp(bar_dq_drained, par, abort_flag);
           if (ok) ok = mbar_wait_warp(bar_do_full, (it + 1) & 1, abort_flag);
           if (!ok) break;
-          FA2_T(4, it);
           tc_fence_after();
           issue_kd(kColdP, dV_k, ddO_k);
           mma_commit_e(bar_dp_full);
@@ -417,7 +399,6 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int k = 0; k < 8; ++k) named_bar_sync(3, 128);
         continue;
       }
-      if (r == 0) FA2_T(5, it);
       tc_fence_after();
       // Pull the tile into registers first so that the tensor-memory columns are handed back
       // early; the reductions (slow: they queue in the memory pipe) then overlap with the MMAs of
@@ -440,7 +421,6 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (part == kParts - 1) {
           tc_fence_before();
           mbar_arrive(bar_dq_drained);
-          if (r == 0) FA2_T(6, it);
         }
 #pragma unroll
         for (int cl = 0; cl < 4 / kParts; ++cl) {
@@ -519,8 +499,6 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ok = mbar_wait(bar_q_full(st), (it >> 1) & 1, abort_flag);
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
-      if (tid == 0) FA2_T(7, it);
-      if (lane == 0 && warp < 8) FA2_T(32 + warp, it);
       tc_fence_after();
       // some (query, key) pairs of this step are above the causal diagonal
       const bool diag = (kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off)) || dead_keys;
@@ -538,7 +516,6 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int c = 0; c < kCW / 32; ++c)
           tmem_ld32(tS + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
         tc_wait_ld();
-        if (tid == 0) FA2_T(11, it);
         if constexpr (kFeat) {
           if (p.drop.enabled) {
             const uint32_t bh_glob =
@@ -595,17 +572,13 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       } else {
         store_p(pk);
       }
-      if (tid == 0) FA2_T(14, it);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_full);
-      if (tid == 0) FA2_T(8, it);
-      if (lane == 0 && warp < 8) FA2_T(16 + warp, it);
 
       // ---- dS^T = P^T * (dP^T * keep/(1-p) - delta) -> shared memory, 16 bit ------------------
       ok = mbar_wait(bar_dp_full, it & 1, abort_flag);
       if (!ok) break;
-      if (tid == 0) FA2_T(9, it);
       tc_fence_after();
       {
         uint32_t dp[kCW];
@@ -613,7 +586,6 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int c = 0; c < kCW / 32; ++c)
           tmem_ld32(tdP + 32 * c, reinterpret_cast<uint32_t(&)[32]>(dp[32 * c]));
         tc_wait_ld();
-        if (tid == 0) FA2_T(12, it);
 #pragma unroll
         for (int c4 = 0; c4 < kCW / 4; ++c4) {
           const float4 dl = delta4[c4];
@@ -640,11 +612,8 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               make_uint4(dp[4 * q4], dp[4 * q4 + 1], dp[4 * q4 + 2], dp[4 * q4 + 3]);
         }
       }
-      if (tid == 0) FA2_T(13, it);
       fence_proxy_async_smem();
       mbar_arrive(bar_ds_full);
-      if (tid == 0) FA2_T(10, it);
-      if (lane == 0 && warp < 8) FA2_T(24 + warp, it);
     }
 
     // ---- epilogue: the first half of the warpgroups writes dK (scaled), the second half dV ----
@@ -755,11 +724,6 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-#ifdef FA2_TRACE
-extern "C" int fa2_trace_read_bwd(long long* host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, sizeof(long long) * n));
-}
-#endif
 
 cudaError_t launch_bwd(const BwdLaunch& a, cudaStream_t stream) {
   if (a.head_dim == 64) return a.bf16 ? launch_all<64, true>(a, stream) : launch_all<64, false>(a, stream);

@@ -23,12 +23,6 @@ namespace fa2 {
 
 namespace {
 
-// Pieces a K / V slot is handed over in (2 or 4). Measured on config 5: one piece 1.20 ms, two
-// 1.10-1.12 ms, four 1.11 ms.
-#ifndef FA2_FWD256_PARTS
-#define FA2_FWD256_PARTS 2
-#endif
-
 constexpr int kD = 256;
 constexpr int kThreads256 = 192;
 
@@ -41,7 +35,7 @@ struct Smem256 {
   static constexpr int kBarOff = kVOff + kKVTileBytes;
   // barriers: q_full, k_full, k_empty, v_full, v_empty, s_full[2], p_full[2 buffers][2 halves],
   // pv_done, o_full, then the second-half barriers k_full, k_empty, v_full, v_empty
-  static constexpr int kParts = FA2_FWD256_PARTS;      // pieces a K / V slot is handed over in
+  static constexpr int kParts = kKV256Parts;           // pieces a K / V slot is handed over in
   static constexpr int kNumBars = 9 + 2 * kPSplit + 4 * kParts;
   static constexpr int kHalfBytes = kKVTileBytes / kParts;
   static_assert(kPSplit == 2, "V halves follow the two halves of P");
@@ -172,7 +166,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     __syncwarp();
   } else if (warp == 4) {
     // =========================== MMA issuer ==================================================
-    if (true && nt > 0) {
+    if (nt > 0) {
       constexpr uint32_t idesc_s = make_idesc(kBf16, kBM, kBN, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, kBM, kD, false, true);
       const uint64_t dQ = make_sdesc(sQ, 16, 1024);
@@ -252,7 +246,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         tc_fence_after();
       };
       softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j0 + j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv,
-                                         [&](int half) { return mbar_arrive_zero(bar_p_full(buf, half)); });
+                                         [&](int half) { mbar_arrive(bar_p_full(buf, half)); });
       if (!ok) break;
     }
 

@@ -7,6 +7,11 @@
 
 namespace fa2 {
 
+// Head dim 256: a K / V slot of the forward is handed over in this many pieces (K by head-dim
+// blocks, V by key rows); the host builds the tensor maps of K and V with matching boxes.
+// Measured on B=4, S=8192, H=8 causal fp16: one piece 1.20 ms, two 1.10-1.12 ms, four 1.11 ms.
+constexpr int kKV256Parts = 2;
+
 struct FwdLaunch {
   CUtensorMap tmQ, tmK, tmV, tmO;
   CUtensorMap tmO1;   // o with a box of one 64-column block (head dim 64 / 128 kernel)

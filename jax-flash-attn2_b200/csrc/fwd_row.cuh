@@ -13,24 +13,10 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // in log2 units: P stays below 2^8
 
-// Of every 8 column pairs, this many take their exponential from the FMA-pipe polynomial
-// instead of the XU pipe. Measured on B200 (B=8, S=4096, Hq=32, D=128, causal): 0 -> 1.016 ms,
-// 2 -> 1.019 ms, 3 -> 1.048 ms, 4 -> 1.039 ms, 5 -> 1.083 ms, so the default is 0: with packed
-// f32x2 arithmetic the XU pipe is not what limits the kernel.
-#ifndef FA2_FWD_POLY_PER8
-#define FA2_FWD_POLY_PER8 0
-#endif
-constexpr int kPolyPer8 = FA2_FWD_POLY_PER8;
-// P of one K/V tile is handed to the MMA warp in this many pieces (2 or 4).
-#ifndef FA2_FWD_P_SPLIT
-#define FA2_FWD_P_SPLIT 2
-#endif
-constexpr int kPSplit = FA2_FWD_P_SPLIT;
-// 1: the next piece's arithmetic is made to depend on the hand-over arrive (strict ordering);
-// 0: the assembler may overlap it with the hand-over.
-#ifndef FA2_FWD_ORDERED_HANDOVER
-#define FA2_FWD_ORDERED_HANDOVER 0
-#endif
+// P of one K/V tile is handed to the MMA warp in two pieces of 64 keys (measured: four pieces
+// are slower, and neither an FMA-pipe polynomial for part of the exponentials nor a strictly
+// ordered hand-over between the pieces gains anything: the XU pipe is not what limits the kernel).
+constexpr int kPSplit = 2;
 constexpr int kPCols = kBN / kPSplit;   // keys per piece
 
 template <bool kBf16>
@@ -87,7 +73,7 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 // `before_o_rescale()` is called (by the whole warp) just before O is touched, so that a kernel
 // whose P.V MMA may still be running can wait for it there.
 // `after_half(h)` is called after piece h (keys [kPCols h, kPCols (h+1))) of P has been stored and
-// fenced: the caller signals the MMA warp there (mbar_arrive_zero) and returns that call's value.
+// fenced: the caller signals the MMA warp there.
 template <int D, bool kBf16, bool kFeat, class BeforeRescale, class AfterHalf>
 __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j, bool have_o,
                                                  const FwdKernelParams& p, int b, int h, int qi,
@@ -150,7 +136,7 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
     }
   }
   const float m_use = (m == -INFINITY) ? 0.f : m;
-  float neg_ms = -m_use * sc;
+  const float neg_ms = -m_use * sc;
   // P is produced and handed over in two halves of 64 keys: the P.V MMAs of the first half run
   // while the exponentials of the second half are still being computed.
   float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
@@ -160,18 +146,10 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
     for (int c = half * kPCols; c < (half + 1) * kPCols; c += 4) {
       fma2(x[c], x[c + 1], x[c], x[c + 1], sc, sc, neg_ms, neg_ms);
       fma2(x[c + 2], x[c + 3], x[c + 2], x[c + 3], sc, sc, neg_ms, neg_ms);
-      if (((c >> 1) & 7) < kPolyPer8) {
-        ex2_poly2(x[c], x[c + 1]);
-      } else {
-        x[c] = ex2_approx(x[c]);
-        x[c + 1] = ex2_approx(x[c + 1]);
-      }
-      if ((((c >> 1) + 1) & 7) < kPolyPer8) {
-        ex2_poly2(x[c + 2], x[c + 3]);
-      } else {
-        x[c + 2] = ex2_approx(x[c + 2]);
-        x[c + 3] = ex2_approx(x[c + 3]);
-      }
+      x[c] = ex2_approx(x[c]);
+      x[c + 1] = ex2_approx(x[c + 1]);
+      x[c + 2] = ex2_approx(x[c + 2]);
+      x[c + 3] = ex2_approx(x[c + 3]);
       add2(l0, l1, l0, l1, x[c], x[c + 1]);
       add2(l2, l3, l2, l3, x[c + 2], x[c + 3]);
     }
@@ -200,21 +178,11 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
 #pragma unroll
     for (int c = 0; c < kPCols / 2; ++c)
       pk[c] = pack2<kBf16>(x[half * kPCols + 2 * c], x[half * kPCols + 2 * c + 1]);
-    if constexpr (kPSplit == 2) {
-      tmem_st32(tS + 32 * half, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
-    } else {
-      tmem_st16(tS + 16 * half, pk);
-    }
+    static_assert(kPCols == 64, "one 32-column store per piece");
+    tmem_st32(tS + 32 * half, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
     tc_wait_st();
     tc_fence_before();
-    // `after_half` arrives on the barrier and returns a zero the compiler cannot see through;
-    // folding it into the next piece's FMA offset keeps the assembler from scheduling that
-    // piece's exponentials ahead of this hand-over.
-#if FA2_FWD_ORDERED_HANDOVER
-    neg_ms += after_half(half);
-#else
-    (void)after_half(half);
-#endif
+    after_half(half);
   }
   l += (l0 + l1) + (l2 + l3);
 }

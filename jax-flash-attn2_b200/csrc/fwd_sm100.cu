@@ -28,14 +28,6 @@ namespace fa2 {
 
 namespace {
 
-#ifdef FA2_TRACE
-// Development aid (not compiled by default): per-role time stamps of one CTA.
-__device__ long long g_trace_fwd[64 * 1024];
-#define FA2_TF(role, idx) do { if (blockIdx.x == FA2_TRACE_CTA && (idx) < 1024) g_trace_fwd[(role) * 1024 + (idx)] = clock64(); } while (0)
-#else
-#define FA2_TF(role, idx) do { } while (0)
-#endif
-
 constexpr int kTilesPerCta = 2;
 constexpr int kThreads = 384;
 constexpr int kRegsSoftmax = 208;   // per scheduler: 2 softmax warps + 1 other warp share the 3 * 168 registers of the launch
@@ -141,7 +133,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int total_items = p.n_qblk * p.B * p.Hq * p.n_splits;
-  if (tid == 0) FA2_TF(32, 0);
 
   // ---- set-up ---------------------------------------------------------------------------------
   if (tid == 0) {
@@ -214,7 +205,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     __syncwarp();
   } else if (warp == 8) {
     // =========================== MMA issuer ==================================================
-    if (true) {
+    {
       constexpr uint32_t idesc_s = make_idesc(kBf16, kBM, kBN, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, kBM, D, false, true);
       bool ok = true;
@@ -248,7 +239,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x, ++item_idx) {
         FwdItem it;
         decode_item<kCausal>(p, w, it);
-        FA2_TF(34, item_idx);
         // Q tiles of this item have landed (also for tiles without work: their buffer is handed
         // back at once so that the producer's next load into it is ordered after this one)
 #pragma unroll
@@ -263,12 +253,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           }
         }
         if (!ok || it.n_max == 0) continue;
-        FA2_TF(35, item_idx);
         {
           const int slot = kv_count % L::kStages;
           ok = mbar_wait_warp(bar_kv_full(slot), (kv_count / L::kStages) & 1u, abort_flag);
           if (!ok) break;
-          FA2_TF(36, item_idx);
           tc_fence_after();
 #pragma unroll
           for (int t = 0; t < kTilesPerCta; ++t) {
@@ -290,7 +278,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             ok = mbar_wait_warp(bar_kv_full(slot_k), ((kv_count + 1) / L::kStages) & 1u, abort_flag);
             if (!ok) break;
           }
-          FA2_TF(43, it_cnt[1]);
 #pragma unroll
           for (int t = 0; t < kTilesPerCta; ++t) {
             if (j < it.n_tiles[t]) {
@@ -303,18 +290,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
               for (int hh = 0; hh < kPSplit; ++hh) {
                 ok = mbar_wait_warp(bar_p_full(t, hh), it_cnt[t] & 1u, abort_flag);
                 if (!ok) break;
-                if (hh == 0) FA2_TF(t, it_cnt[t]);
-                if (hh == kPSplit - 1) FA2_TF(44 + t, it_cnt[t]);
                 tc_fence_after();
                 issue_o(t, slot_v, j == 0, hh);
-                if (hh == 0) FA2_TF(48 + t, it_cnt[t]);
               }
               if (!ok) break;
-              FA2_TF(50 + t, it_cnt[t]);
               ++it_cnt[t];
               if (j + 1 < it.n_tiles[t]) {
                 issue_s(t, slot_k);
-                FA2_TF(46 + t, it_cnt[t] - 1);
                 if (j + 2 == it.n_tiles[t]) mma_commit_e(bar_q_free(t));   // last S of tile t issued
               } else {
                 mma_commit_e(bar_o_full(t));
@@ -360,21 +342,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
         ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
         if (!ok) break;
-        if (lane == 0) FA2_TF(8 + warp, it_cnt);
         softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
-                                          [&](int hh) {
-                                            if (hh == 0 && lane == 0) FA2_TF(52 + warp, it_cnt);
-                                            return mbar_arrive_zero(bar_p_full(t, hh));
-                                          });
-        if (lane == 0) FA2_TF(16 + warp, it_cnt);
+                                          [&](int hh) { mbar_arrive(bar_p_full(t, hh)); });
       }
 
       // ---- epilogue: O / l -> 16 bit -> swizzled shared memory -> TMA store; LSE -------------
-      if (tid == 0) FA2_TF(37, o_cnt);
-      if (tid == 128) FA2_TF(40, o_cnt);
       if (ok) ok = mbar_wait(bar_o_full(t), o_cnt & 1u, abort_flag);   // once per item, work or not
-      if (tid == 0) FA2_TF(38, o_cnt);
-      if (tid == 128) FA2_TF(41, o_cnt);
       ++o_cnt;
       // One 64-column block at a time through this tile's 16 KiB staging block. O_t is handed
       // back to the MMA warp as soon as its last columns have been read out of tensor memory.
@@ -409,8 +382,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           tma_store_commit();
         }
       }
-      if (tid == 0) FA2_TF(39, o_cnt - 1);
-      if (tid == 128) FA2_TF(42, o_cnt - 1);
       // No early exit when a wait has given up: a thread that left alone would strand the rest
       // of its tile at the (unbounded) named barriers of the next epilogue. With `ok` false the
       // remaining items cost only those barriers: the loops and waits above are skipped.
@@ -419,7 +390,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (!ok && r == 0) atomicOr(p.status, 4);
   }
 
-  if (tid == 0) FA2_TF(33, 0);
   // ---- teardown -------------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -460,12 +430,6 @@ static cudaError_t launch_d(const FwdLaunch& a, cudaStream_t stream) {
     default: return launch_one<D, true, true, true>(a, stream);
   }
 }
-
-#ifdef FA2_TRACE
-extern "C" int fa2_trace_read_fwd(long long* host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace_fwd, sizeof(long long) * n));
-}
-#endif
 
 cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream) {
   switch (a.head_dim) {
