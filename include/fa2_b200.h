@@ -10,7 +10,9 @@
  *
  * Conventions
  *   - Every pointer is a device pointer owned by the caller. The library allocates nothing,
- *     frees nothing and keeps no pointer after a call returns.
+ *     frees nothing and keeps no pointer after a call returns. Its only device memory of its own
+ *     is part of the library image: one status word and the fixed scratch array of
+ *     fa2_bwd_static_scratch (see there).
  *   - Work is launched on the CUDA stream passed in (a cudaStream_t cast to void*); no call
  *     synchronises the host with the device.
  *   - Tensors are addressed by element strides, so [B,S,H,D] and [B,H,S,D] storage (and
@@ -52,8 +54,22 @@ typedef struct {
 typedef struct {
   const void* ptr;            /* NULL = absent                                               */
   int32_t dtype;              /* fa2_dtype: the q/k/v dtype or FA2_FP32                      */
+  /* Query head h reads head h / head_div of the term (0 and 1 both mean one term head per query
+   * head). A bias with one head per key/value head passes heads_q / heads_kv here and is never
+   * repeated in memory (the reference repeats it: flash_attention.py:161-164). */
+  int32_t head_div;
   int64_t stride_b, stride_h, stride_q;
 } fa2_score_term;
+
+/* Optional gradient of the bias (no counterpart in the reference, which returns no bias cotangent:
+ * flash_attention_triton/_flash_attention.py:88). Dense float32 [batch, heads, seqlen_q, seqlen_k]
+ * with batch in {1, B} and heads in {1, heads_kv, heads_q}: the gradient of the scores, summed over
+ * the batch elements / query heads that share a bias entry. The library zeroes it and then adds
+ * into it, so its previous contents do not matter. */
+typedef struct {
+  float* ptr;                 /* NULL = not wanted                                           */
+  int32_t batch, heads;
+} fa2_score_grad;
 
 typedef struct {
   /* head_dim: any multiple of 8 up to 64, of 16 up to 128, of 32 up to 256. Head dims other than
@@ -73,6 +89,11 @@ typedef struct {
    * dropout bits the unsharded call would draw. */
   int32_t batch_offset, head_offset, heads_q_global;
 } fa2_problem;
+
+/* Both parameter blocks end with `offsets_dev`: optional (NULL = absent) int32 [2] on the device,
+ * (batch_offset, head_offset). When given it replaces the two fields of fa2_problem, so that a
+ * caller whose position in the mesh is a traced value (jax.lax.axis_index under shard_map) passes
+ * it as an operand instead of compiling one call per mesh position. */
 
 typedef struct {
   fa2_problem p;
@@ -101,10 +122,11 @@ typedef struct {
   /* Optional scratch for split-KV (NULL / 0 = none). A problem with too few (batch, head, query
    * tile) items to fill the GPU, typically a decode step, is cut along the key sequence into
    * several items whose partial results are merged by a second small kernel; that needs
-   * fa2_fwd_workspace_bytes(&p) bytes of scratch (256-byte aligned; contents undefined before and
+   * fa2_fwd_workspace_bytes(&p) bytes of scratch (128-byte aligned; contents undefined before and
    * after the call). Without enough scratch the call runs unsplit: same result, fewer SMs busy. */
   void* workspace;
   size_t workspace_bytes;
+  const int32_t* offsets_dev;
 } fa2_fwd_params;
 
 typedef struct {
@@ -120,13 +142,15 @@ typedef struct {
   void* dq; fa2_strides dq_strides;           /* [B, Sq, Hq,  D] in the q dtype               */
   void* dk; fa2_strides dk_strides;           /* [B, Sk, Hkv, D], already summed over a group */
   void* dv; fa2_strides dv_strides;
-  void* workspace;                             /* fa2_bwd_workspace_bytes() bytes, 256-aligned */
+  void* workspace;                             /* fa2_bwd_workspace_bytes() bytes, 128-aligned */
   size_t workspace_bytes;
   /* Optional per-batch lengths: the array that was given to the forward call.
    * Rows of dq, dk and dv past a batch element's length are written as zeros and its d_o rows
    * past it are never read (_backward_triton.py:973-1025, 1163-1171). */
   const int32_t* seqlens;
   const uint64_t* dropout_seed_dev;            /* optional device-resident seed, see above        */
+  const int32_t* offsets_dev;
+  fa2_score_grad dbias;                        /* optional gradient of `bias`                     */
 } fa2_bwd_params;
 
 /* Forward: o = softmax(scale q k^T + bias + mask [causal]) v with dropout on the weights, and
@@ -151,7 +175,10 @@ size_t fa2_bwd_workspace_bytes(const fa2_problem* problem);
 /* Message of the last failing call on this thread ("" if none). */
 const char* fa2_last_error(void);
 
-/* ABI version of this header: major * 1000 + minor. */
+/* ABI version of this header: major * 1000 + minor. A change to the layout or meaning of a
+ * structure is a new major version; bindings compare fa2_version() with the FA2_ABI_VERSION they
+ * were written against and refuse a library whose major version differs. */
+#define FA2_ABI_VERSION 2000
 int fa2_version(void);
 
 /* Reads and clears the device status word written by a kernel whose bounded wait ran out

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <climits>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -138,13 +139,26 @@ int check_problem(const fa2_problem& p) {
   if (p.dropout_p > 0.f && (p.heads_q_global < p.head_offset + p.heads_q || p.batch_offset < 0 ||
                             p.head_offset < 0))
     return fail(FA2_ERR_INVALID_ARG, "dropout offsets: head_offset + heads_q exceeds heads_q_global");
+  // The kernels count work items and blocks in 32-bit integers (one item per 128 query rows and
+  // query head at most, times up to 32 key splits): refuse what would not fit instead of wrapping.
+  const long long q_tiles = (static_cast<long long>(p.seqlen_q) + 127) / 128;
+  const long long k_tiles = (static_cast<long long>(p.seqlen_k) + 127) / 128;
+  const long long bh = static_cast<long long>(p.batch) * p.heads_q;
+  if (bh > INT_MAX || bh * q_tiles * 32 > INT_MAX || bh * k_tiles * 2 > INT_MAX ||
+      bh * p.seqlen_q > INT_MAX)
+    return fail(FA2_ERR_UNSUPPORTED,
+                "problem too large: batch * heads_q * max(seqlen_q, 64 * ceil(seqlen / 128)) must stay below 2^31");
   return FA2_OK;
 }
 
 int make_score_term(ScoreTermDev* out, const fa2_score_term& t, const fa2_problem& p,
                     const char* what) {
   std::memset(out, 0, sizeof(*out));
+  out->head_div = 1;
   if (!t.ptr) return FA2_OK;
+  if (t.head_div < 0 || (t.head_div > 1 && p.heads_q % t.head_div != 0))
+    return fail(FA2_ERR_INVALID_ARG, "%s: head_div must divide heads_q", what);
+  out->head_div = t.head_div > 1 ? t.head_div : 1;
   if (t.dtype != p.dtype && t.dtype != FA2_FP32)
     return fail(FA2_ERR_UNSUPPORTED, "%s: dtype must be the q dtype or fp32", what);
   if (t.stride_b < 0 || t.stride_h < 0 || t.stride_q < 0)
@@ -175,6 +189,21 @@ void make_dropout(DropoutDev* d, const fa2_problem& p) {
   d->h_off = p.head_offset;
   d->hq_global = p.heads_q_global;
 }
+
+// The optional device-resident operands of the dropout stream (seed, shard offsets).
+int set_dropout_operands(DropoutDev* d, const uint64_t* seed_dev, const int32_t* offsets_dev) {
+  if (seed_dev && (reinterpret_cast<uintptr_t>(seed_dev) & 7))
+    return fail(FA2_ERR_INVALID_ARG, "dropout_seed_dev must be 8-byte aligned");
+  if (offsets_dev && (reinterpret_cast<uintptr_t>(offsets_dev) & 3))
+    return fail(FA2_ERR_INVALID_ARG, "offsets_dev must be 4-byte aligned");
+  d->seed_dev = reinterpret_cast<const unsigned long long*>(seed_dev);
+  d->offsets_dev = offsets_dev;
+  return FA2_OK;
+}
+
+// What the kernels need of a scratch pointer: 16-byte bulk copies and float4 accesses; 128 bytes is
+// what allocators of every framework (XLA's sub-allocated temporaries included) guarantee.
+constexpr uintptr_t kWorkspaceAlign = 128;
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
@@ -243,7 +272,7 @@ using namespace fa2;
 
 extern "C" {
 
-int fa2_version(void) { return 1003; }
+int fa2_version(void) { return FA2_ABI_VERSION; }
 
 const char* fa2_last_error(void) { return g_err; }
 
@@ -305,7 +334,7 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   // split * B + b of a contiguous [n_splits * B, Sq, Hq, D] output and its lse), merged afterwards.
   SplitPlan sp = plan_splits(p, hd, pack_heads);
   if (sp.n_splits > 1 && (!a->workspace || a->workspace_bytes < sp.total ||
-                          (reinterpret_cast<uintptr_t>(a->workspace) & 255)))
+                          (reinterpret_cast<uintptr_t>(a->workspace) & (kWorkspaceAlign - 1))))
     sp.n_splits = 1;   // not enough scratch: run unsplit
   const bool split = sp.n_splits > 1;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
@@ -355,9 +384,7 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
   kp.seqlens = a->seqlens;
-  if (a->dropout_seed_dev && (reinterpret_cast<uintptr_t>(a->dropout_seed_dev) & 7))
-    return fail(FA2_ERR_INVALID_ARG, "dropout_seed_dev must be 8-byte aligned");
-  kp.drop.seed_dev = reinterpret_cast<const unsigned long long*>(a->dropout_seed_dev);
+  if ((rc = set_dropout_operands(&kp.drop, a->dropout_seed_dev, a->offsets_dev))) return rc;
   kp.n_qblk = (sq_k + 255) / 256;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
@@ -417,8 +444,17 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   const BwdWorkspace w = bwd_workspace(p);
   if (!a->workspace || a->workspace_bytes < w.total)
     return fail(FA2_ERR_WORKSPACE, "workspace must hold %zu bytes", w.total);
-  if (reinterpret_cast<uintptr_t>(a->workspace) & 255)
-    return fail(FA2_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  if (reinterpret_cast<uintptr_t>(a->workspace) & (kWorkspaceAlign - 1))
+    return fail(FA2_ERR_WORKSPACE, "workspace must be 128-byte aligned");
+  if (a->dbias.ptr) {
+    if (!a->bias.ptr) return fail(FA2_ERR_INVALID_ARG, "dbias is given but bias is not");
+    if ((a->dbias.batch != 1 && a->dbias.batch != p.batch) ||
+        (a->dbias.heads != 1 && a->dbias.heads != p.heads_kv && a->dbias.heads != p.heads_q))
+      return fail(FA2_ERR_INVALID_ARG, "dbias: batch must be 1 or %d and heads 1, %d or %d", p.batch,
+                  p.heads_kv, p.heads_q);
+    if (reinterpret_cast<uintptr_t>(a->dbias.ptr) & 3)
+      return fail(FA2_ERR_INVALID_ARG, "dbias must be 4-byte aligned");
+  }
 
   BwdLaunch L;
   std::memset(&L, 0, sizeof(L));
@@ -464,9 +500,7 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
   kp.seqlens = a->seqlens;
-  if (a->dropout_seed_dev && (reinterpret_cast<uintptr_t>(a->dropout_seed_dev) & 7))
-    return fail(FA2_ERR_INVALID_ARG, "dropout_seed_dev must be 8-byte aligned");
-  kp.drop.seed_dev = reinterpret_cast<const unsigned long long*>(a->dropout_seed_dev);
+  if ((rc = set_dropout_operands(&kp.drop, a->dropout_seed_dev, a->offsets_dev))) return rc;
   kp.n_kvblk = (p.seqlen_k + 127) / 128;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
@@ -475,6 +509,18 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   L.bf16 = bf16;
   L.causal = p.causal != 0;
   L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled;
+  if (a->dbias.ptr) {
+    const long long plane = static_cast<long long>(p.seqlen_q) * p.seqlen_k;
+    kp.dbias.ptr = a->dbias.ptr;
+    kp.dbias.sh = a->dbias.heads == 1 ? 0 : plane;
+    kp.dbias.sb = a->dbias.batch == 1 ? 0 : plane * a->dbias.heads;
+    kp.dbias.head_div = a->dbias.heads == p.heads_q ? 1 : p.heads_q / p.heads_kv;
+    // entries no step touches (above the causal diagonal, behind a batch element's length) stay 0
+    const cudaError_t ez = cudaMemsetAsync(a->dbias.ptr, 0, sizeof(float) * plane * a->dbias.heads * a->dbias.batch,
+                                           static_cast<cudaStream_t>(cuda_stream));
+    if (ez != cudaSuccess)
+      return fail(FA2_ERR_CUDA, "clearing dbias failed: %s", cudaGetErrorString(ez));
+  }
   L.o = a->o; L.o_strides[0] = a->o_strides.b; L.o_strides[1] = a->o_strides.s; L.o_strides[2] = a->o_strides.h;
   L.d_o = a->d_o; L.do_strides[0] = a->do_strides.b; L.do_strides[1] = a->do_strides.s; L.do_strides[2] = a->do_strides.h;
   L.dq = a->dq; L.dq_strides[0] = a->dq_strides.b; L.dq_strides[1] = a->dq_strides.s; L.dq_strides[2] = a->dq_strides.h;

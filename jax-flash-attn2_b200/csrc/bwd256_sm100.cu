@@ -471,7 +471,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if constexpr (kFeat) {
           if (p.drop.enabled) {
             const uint32_t bh_glob =
-                static_cast<uint32_t>((p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
+                dropout_bh_index(p.drop, b, h);
             uint32_t bits[1];
             dropout_keep_bits_transposed<32>(p.drop, bh_glob, kv, q_first, lane, bits);
             keep = bits[0];
@@ -559,9 +559,14 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (r & 7)) << 4)) =
               make_uint4(dp[4 * q4], dp[4 * q4 + 1], dp[4 * q4 + 2], dp[4 * q4 + 3]);
         }
+        fence_proxy_async_smem();
+        mbar_arrive(bar_ds_full);
+        if constexpr (kFeat) {
+          // both halves of the head dim compute the same dS^T: the first one reports it
+          if (p.dbias.ptr != nullptr && half == 0)
+            add_bias_grad<kBf16, 32>(p.dbias, b, h, q_first, kv, p.Sq, p.Sk, dp, do_scale);
+        }
       }
-      fence_proxy_async_smem();
-      mbar_arrive(bar_ds_full);
     }
 
     // ---- epilogue: warpgroup 0 writes dK[:, half] (scaled), warpgroup 1 writes dV[:, half] ----

@@ -81,7 +81,7 @@ template <bool kBf16, int kCols>
 __device__ __forceinline__ void add_term_column(const ScoreTermDev& t, int b, int h, int q_first,
                                                 int kv, int Sq, int Sk, uint32_t (&x)[kCols]) {
   if (t.ptr == nullptr) return;
-  const long long base = static_cast<long long>(b) * t.sb + static_cast<long long>(h) * t.sh +
+  const long long base = static_cast<long long>(b) * t.sb + static_cast<long long>(h / t.head_div) * t.sh +
                          min(kv, Sk - 1);
   if (t.is_f32) {
     const float* ptr = static_cast<const float*>(t.ptr) + base;
@@ -107,6 +107,27 @@ __device__ __forceinline__ void add_term_column(const ScoreTermDev& t, int b, in
       for (int k = 0; k < 16; ++k)
         x[c0 + k] = __float_as_uint(fmaf(to_float16bit<kBf16>(v[k]), kLog2e, __uint_as_float(x[c0 + k])));
     }
+  }
+}
+
+// Gradient of the bias: g[b, h / head_div, q_first + c, kv] += ds[c] / ds_scale for kCols
+// consecutive queries of this thread's key row. `ds` holds the 16-bit pairs the thread has just
+// stored as dS^T (queries c, c + 1 in the low and high half of word c / 2); ds_scale is the power
+// of two fp16 problems multiply dS with. The threads of a warp own consecutive keys, so every
+// atomic of the warp covers 128 contiguous bytes. Entries that are masked hold exact zeros and are
+// skipped, which also keeps the causal upper triangle free of traffic.
+template <bool kBf16, int kCols>
+__device__ __forceinline__ void add_bias_grad(const ScoreGradDev& g, int b, int h, int q_first, int kv,
+                                              int Sq, int Sk, const uint32_t* ds, float ds_scale) {
+  if (kv >= Sk) return;
+  float* row = g.ptr + static_cast<long long>(b) * g.sb + static_cast<long long>(h / g.head_div) * g.sh +
+               static_cast<long long>(q_first) * Sk + kv;
+  const float inv = 1.f / ds_scale;
+#pragma unroll
+  for (int c = 0; c < kCols; c += 2) {
+    const float d0 = unpack_lo<kBf16>(ds[c >> 1]) * inv, d1 = unpack_hi<kBf16>(ds[c >> 1]) * inv;
+    if (q_first + c < Sq && d0 != 0.f) atomicAdd(row + static_cast<long long>(c) * Sk, d0);
+    if (q_first + c + 1 < Sq && d1 != 0.f) atomicAdd(row + static_cast<long long>(c + 1) * Sk, d1);
   }
 }
 

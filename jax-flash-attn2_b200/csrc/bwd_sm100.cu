@@ -519,7 +519,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if constexpr (kFeat) {
           if (p.drop.enabled) {
             const uint32_t bh_glob =
-                static_cast<uint32_t>((p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
+                dropout_bh_index(p.drop, b, h);
             dropout_keep_bits_transposed<kCW>(p.drop, bh_glob, kv, q_first, lane, keep);
           }
         }
@@ -611,9 +611,14 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           *reinterpret_cast<uint4*>(ds_row + (((chunk0 + q4) ^ (r & 7)) << 4)) =
               make_uint4(dp[4 * q4], dp[4 * q4 + 1], dp[4 * q4 + 2], dp[4 * q4 + 3]);
         }
+        fence_proxy_async_smem();
+        mbar_arrive(bar_ds_full);
+        if constexpr (kFeat) {
+          // off the critical path: the MMAs of dQ and dK are already free to start
+          if (p.dbias.ptr != nullptr)
+            add_bias_grad<kBf16, kCW>(p.dbias, b, h, q_first, kv, p.Sq, p.Sk, dp, do_scale);
+        }
       }
-      fence_proxy_async_smem();
-      mbar_arrive(bar_ds_full);
     }
 
     // ---- epilogue: the first half of the warpgroups writes dK (scaled), the second half dV ----

@@ -22,7 +22,7 @@ constexpr int kPCols = kBN / kPSplit;   // keys per piece
 template <bool kBf16>
 __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermDev& t, int b,
                                                int h, int qi, int kv0, int Sk) {
-  const long long base = static_cast<long long>(b) * t.sb + static_cast<long long>(h) * t.sh +
+  const long long base = static_cast<long long>(b) * t.sb + static_cast<long long>(h / t.head_div) * t.sh +
                          static_cast<long long>(qi) * t.sq + kv0;
   const bool full = (kv0 + kBN <= Sk);
   if (t.is_f32) {
@@ -155,8 +155,7 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
     }
     if constexpr (kFeat) {
       if (p.drop.enabled) {
-        const uint32_t bh_glob = static_cast<uint32_t>(
-            (p.drop.b_off + b) * p.drop.hq_global + p.drop.h_off + h);
+        const uint32_t bh_glob = dropout_bh_index(p.drop, b, h);
         uint32_t key_lo, key_hi;
         dropout_key(p.drop, key_lo, key_hi);
         // one Philox call covers eight adjacent keys of this row: each 32-bit output word

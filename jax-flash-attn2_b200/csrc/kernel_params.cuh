@@ -10,6 +10,15 @@ struct ScoreTermDev {
   long long sb, sh, sq;
   int is_f32;           // 1: float32 elements, 0: the 16-bit dtype of q
   int vec_ok;           // 1: rows can be read with 16-byte loads (pointer and strides aligned)
+  int head_div;         // >= 1: query head h reads head h / head_div of the term
+};
+
+// Gradient of the bias: float32 [batch, heads, Sq, Sk], added into with atomics (several batch
+// elements / query heads may share an entry). sb / sh are 0 on broadcast dimensions.
+struct ScoreGradDev {
+  float* ptr;           // nullptr = not wanted
+  long long sb, sh;
+  int head_div;         // >= 1: query head h adds into head h / head_div
 };
 
 struct DropoutDev {
@@ -20,6 +29,8 @@ struct DropoutDev {
   // on the device, e.g. a traced value of the calling framework)
   const unsigned long long* seed_dev;
   int b_off, h_off, hq_global;
+  // optional: (batch offset, head offset) read from this device address instead of b_off / h_off
+  const int* offsets_dev;
   int enabled;
 };
 
@@ -32,6 +43,17 @@ __device__ __forceinline__ void dropout_key(const DropoutDev& d, uint32_t& lo, u
     lo = static_cast<uint32_t>(s);
     hi = static_cast<uint32_t>(s >> 32);
   }
+}
+
+// Index of (batch b, head h) of this call in the Philox counter: its position in the unsharded
+// problem, so that every partitioning draws the same bits.
+__device__ __forceinline__ uint32_t dropout_bh_index(const DropoutDev& d, int b, int h) {
+  int b_off = d.b_off, h_off = d.h_off;
+  if (d.offsets_dev != nullptr) {
+    b_off = __ldg(d.offsets_dev);
+    h_off = __ldg(d.offsets_dev + 1);
+  }
+  return static_cast<uint32_t>((b_off + b) * d.hq_global + h_off + h);
 }
 
 struct FwdKernelParams {
@@ -73,6 +95,7 @@ struct BwdKernelParams {
   // fp16 only: bit pattern of max|dO| over the whole call (written by the pre-pass); dS is
   // scaled by a power of two derived from it so that small cotangents do not underflow in fp16.
   const unsigned* do_absmax_bits;
+  ScoreGradDev dbias;
   int* status;
 };
 

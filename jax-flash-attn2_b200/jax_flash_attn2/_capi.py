@@ -29,6 +29,8 @@ EXPORTED_SYMBOLS = (
     "fa2_bwd_static_scratch",
 )
 FA2_BWD_STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
+# FA2_ABI_VERSION of the header these structures were written against (major * 1000 + minor)
+FA2_ABI_VERSION = 2000
 
 
 class Strides(C.Structure):
@@ -39,10 +41,15 @@ class ScoreTerm(C.Structure):
     _fields_ = [
         ("ptr", C.c_void_p),
         ("dtype", C.c_int32),
+        ("head_div", C.c_int32),
         ("stride_b", C.c_int64),
         ("stride_h", C.c_int64),
         ("stride_q", C.c_int64),
     ]
+
+
+class ScoreGrad(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("batch", C.c_int32), ("heads", C.c_int32)]
 
 
 class Problem(C.Structure):
@@ -79,6 +86,7 @@ class FwdParams(C.Structure):
         ("dropout_seed_dev", C.c_void_p),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
+        ("offsets_dev", C.c_void_p),
     ]
 
 
@@ -101,6 +109,8 @@ class BwdParams(C.Structure):
         ("workspace_bytes", C.c_size_t),
         ("seqlens", C.c_void_p),
         ("dropout_seed_dev", C.c_void_p),
+        ("offsets_dev", C.c_void_p),
+        ("dbias", ScoreGrad),
     ]
 
 
@@ -126,6 +136,15 @@ def load() -> C.CDLL:
             "There is no fallback implementation."
         )
     lib = C.CDLL(LIB_PATH)
+    lib.fa2_version.argtypes = []
+    lib.fa2_version.restype = C.c_int
+    found = lib.fa2_version()
+    if found // 1000 != FA2_ABI_VERSION // 1000 or found < FA2_ABI_VERSION:
+        # a stale build would read the parameter blocks with another layout
+        raise ImportError(
+            f"{LIB_PATH} reports ABI version {found}, this binding needs {FA2_ABI_VERSION}: rebuild it with "
+            f"`python {os.path.join(_PKG_ROOT, 'build.py')} --force`."
+        )
     lib.fa2_fwd.argtypes = [C.POINTER(FwdParams), C.c_void_p]
     lib.fa2_fwd.restype = C.c_int
     lib.fa2_bwd.argtypes = [C.POINTER(BwdParams), C.c_void_p]
@@ -136,8 +155,6 @@ def load() -> C.CDLL:
     lib.fa2_bwd_workspace_bytes.restype = C.c_size_t
     lib.fa2_last_error.argtypes = []
     lib.fa2_last_error.restype = C.c_char_p
-    lib.fa2_version.argtypes = []
-    lib.fa2_version.restype = C.c_int
     lib.fa2_debug_device_status.argtypes = [C.c_void_p]
     lib.fa2_debug_device_status.restype = C.c_int
     lib.fa2_bwd_static_scratch.argtypes = [C.POINTER(BwdParams), C.c_void_p]

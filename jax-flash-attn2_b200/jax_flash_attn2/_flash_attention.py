@@ -3,7 +3,8 @@
 Mirrors the structure of the reference's `flash_attention_call` custom_vjp
 (jax_flash_attn2/flash_attention_triton/_flash_attention.py:27-157): the forward saves
 (q, k, v, bias, attention_mask, out, lse, dropout_seed); the backward returns gradients for
-q, k and v only (bias, mask and seed get none). torch.autograd.Function plays the part of
+q, k and v (mask and seed get none). One addition: a bias that requires a gradient gets one, where
+the reference returns None (:88). torch.autograd.Function plays the part of
 jax.custom_vjp because JAX is not available where this library is built and tested.
 """
 from __future__ import annotations
@@ -28,16 +29,19 @@ class _FlashAttentionCall(torch.autograd.Function):
         )   # `shard` also carries the per-batch lengths, when there are any
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.extras = (attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard)
+        ctx.bias_grad = bias is not None and bias.requires_grad
         return out
 
     @staticmethod
     def backward(ctx, dO):
         q, k, v, out, lse = ctx.saved_tensors
         attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard = ctx.extras
-        dq, dk, dv = bwd_attention_kernel_call(
-            dO, q, k, v, bias, attention_mask, out, lse, dropout_prob, causal, softmax_scale, dropout_seed, **shard
+        grads = bwd_attention_kernel_call(
+            dO, q, k, v, bias, attention_mask, out, lse, dropout_prob, causal, softmax_scale, dropout_seed,
+            bias_grad=ctx.bias_grad, **shard
         )
-        return dq, dk, dv, None, None, None, None, None, None, None
+        dbias = grads[3].to(bias.dtype) if ctx.bias_grad else None
+        return grads[0], grads[1], grads[2], None, dbias, None, None, None, None, None
 
 
 def flash_attention(

@@ -51,10 +51,13 @@ def _unit_last(x: torch.Tensor) -> torch.Tensor:
     return x if x.stride(-1) == 1 else x.contiguous()
 
 
-def _score_term(x: tp.Optional[torch.Tensor], batch: int, heads: int, sq: int, sk: int, name: str):
+def _score_term(x: tp.Optional[torch.Tensor], batch: int, heads: int, sq: int, sk: int, name: str,
+                heads_kv: tp.Optional[int] = None):
     """Broadcast rules of calc_bias_strides (flash_attention_triton/_utils.py:151-193): batch in
     {1, B}, heads in {1, Hq}, the two sequence dims equal to (Sq, Sk); additionally the query dim
-    may be 1 (a key-padding term). Returns (ScoreTerm, tensor kept alive)."""
+    may be 1 (a key-padding term), and a term with one head per key/value head (`heads_kv`) is
+    indexed by query head // group size inside the kernels, without the repeat of the reference
+    (flash_attention.py:161-164). Returns (ScoreTerm, tensor kept alive)."""
     term = _capi.ScoreTerm()
     if x is None:
         return term, None
@@ -65,13 +68,15 @@ def _score_term(x: tp.Optional[torch.Tensor], batch: int, heads: int, sq: int, s
     bb, bh, bq, bk = x.shape
     if bb not in (1, batch):
         raise ValueError(f"{name} batch size must be {batch} or 1, got {bb}")
-    if bh not in (1, heads):
+    per_kv_head = heads_kv is not None and bh == heads_kv and bh not in (1, heads)
+    if bh not in (1, heads) and not per_kv_head:
         raise ValueError(f"{name} heads must be {heads} or 1, got {bh}")
     if bq not in (1, sq) or bk != sk:
         raise ValueError(f"{name} sequence dims must be ({sq}, {sk}), got ({bq}, {bk})")
     x = _unit_last(x)
     term.ptr = x.data_ptr()
     term.dtype = _DTYPE_CODE[x.dtype]
+    term.head_div = heads // heads_kv if per_kv_head else 1
     term.stride_b = 0 if bb == 1 else x.stride(0)
     term.stride_h = 0 if bh == 1 else x.stride(1)
     term.stride_q = 0 if bq == 1 else x.stride(2)
@@ -150,6 +155,19 @@ def _seed_ptr(dropout_seed, q: torch.Tensor):
     return dropout_seed.data_ptr(), dropout_seed
 
 
+def _offsets_ptr(offsets_dev, q: torch.Tensor):
+    """(batch_offset, head_offset) as an int32 [2] CUDA tensor: read by the kernels on the device
+    in place of the two integer arguments. Returns (device pointer or None, tensor kept alive)."""
+    if offsets_dev is None:
+        return None, None
+    if offsets_dev.dtype != torch.int32 or offsets_dev.numel() != 2:
+        raise ValueError("offsets_dev must hold two int32 values (batch offset, head offset)")
+    if offsets_dev.device != q.device:
+        raise ValueError("offsets_dev must live on the device of q")
+    offsets_dev = offsets_dev.contiguous()
+    return offsets_dev.data_ptr(), offsets_dev
+
+
 def _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offset, head_offset, heads_q_global):
     batch, sq, hq, d = q.shape
     _, sk, hkv, _ = k.shape
@@ -199,12 +217,14 @@ def fwd_attention_kernel_call(
     heads_q_global: tp.Optional[int] = None,
     seqlens: tp.Optional[torch.Tensor] = None,
     split_kv: bool = True,
+    offsets_dev: tp.Optional[torch.Tensor] = None,
 ) -> tp.Tuple[torch.Tensor, torch.Tensor]:
     """Forward launch. q [B,Sq,Hq,D]; k, v [B,Sk,Hkv,D]; `attention_mask` here is already an
     additive 4-D term (see normalise_attention_mask); `seqlens` (int32 [B], device) gives every
     batch element its own length, the reference's varlen mode without packing; `split_kv=False`
     withholds the scratch with which the library splits low-occupancy problems along the key
-    sequence (same result, computed by fewer SMs). Returns
+    sequence (same result, computed by fewer SMs); `offsets_dev` (int32 [2], device) carries
+    (batch_offset, head_offset) as a device operand. Returns
     (out [B,Sq,Hq,D] in q.dtype, lse [B,Hq,ceil(Sq/128)*128] float32, natural log; columns >= Sq
     are not written)."""
     _check_qkv(q, k, v)
@@ -223,10 +243,11 @@ def fwd_attention_kernel_call(
     a.v, a.v_strides = v.data_ptr(), _strides(v)
     a.o, a.o_strides = out.data_ptr(), _strides(out)
     a.lse, a.lse_stride_b, a.lse_stride_h = lse.data_ptr(), lse.stride(0), lse.stride(1)
-    a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias")
+    a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias", k.shape[2])
     a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
     a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
+    a.offsets_dev, _keep_f = _offsets_ptr(offsets_dev, q)
     # low-occupancy problems (decode steps) are split along the key sequence if scratch is offered
     nbytes = lib.fa2_fwd_workspace_bytes(C.byref(a.p)) if split_kv else 0
     if nbytes:
@@ -254,9 +275,14 @@ def bwd_attention_kernel_call(
     head_offset: int = 0,
     heads_q_global: tp.Optional[int] = None,
     seqlens: tp.Optional[torch.Tensor] = None,
-) -> tp.Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    offsets_dev: tp.Optional[torch.Tensor] = None,
+    bias_grad: bool = False,
+):
     """Backward launch; `M` is the lse returned by the forward. Returns (dq, dk, dv) in the input
-    dtype; dk and dv are already reduced over the query heads of each key/value head."""
+    dtype; dk and dv are already reduced over the query heads of each key/value head. With
+    `bias_grad=True` a fourth result is the gradient of `bias` in float32 and in the bias's own
+    shape (summed over the batch elements / query heads that share an entry); the reference has no
+    bias cotangent (flash_attention_triton/_flash_attention.py:88)."""
     _check_qkv(q, k, v)
     lib = _capi.load()
     q, k, v, o, dO = map(_unit_last, (q, k, v, o, dO))
@@ -280,15 +306,24 @@ def bwd_attention_kernel_call(
     a.o, a.o_strides = o.data_ptr(), _strides(o)
     a.d_o, a.do_strides = dO.data_ptr(), _strides(dO)
     a.lse, a.lse_stride_b, a.lse_stride_h = M.data_ptr(), M.stride(0), M.stride(1)
-    a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias")
+    a.bias, _keep_b = _score_term(bias, batch, hq, sq, sk, "bias", k.shape[2])
     a.mask, _keep_m = _score_term(attention_mask, batch, hq, sq, sk, "attention_mask")
+    dbias = None
+    if bias_grad:
+        if bias is None or bias.shape[2] != sq:
+            raise ValueError("bias_grad needs a bias with a full query dimension")
+        dbias = torch.empty(tuple(bias.shape), dtype=torch.float32, device=q.device)
+        a.dbias.ptr, a.dbias.batch, a.dbias.heads = dbias.data_ptr(), bias.shape[0], bias.shape[1]
     a.dq, a.dq_strides = dq.data_ptr(), _strides(dq)
     a.dk, a.dk_strides = dk.data_ptr(), _strides(dk)
     a.dv, a.dv_strides = dv.data_ptr(), _strides(dv)
     a.workspace, a.workspace_bytes = workspace.data_ptr(), nbytes
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
     a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
+    a.offsets_dev, _keep_f = _offsets_ptr(offsets_dev, q)
     _launch(lib.fa2_bwd, a, q.device)
+    if bias_grad:
+        return dq, dk, dv, dbias
     return dq, dk, dv
 
 

@@ -49,6 +49,14 @@ def _expand_term(x: tp.Optional[torch.Tensor], b: int, h: int, sq: int, sk: int)
     return x.to(torch.float32).expand(b, h, sq, sk)
 
 
+def _expand_bias(x: tp.Optional[torch.Tensor], b: int, h: int, sq: int, sk: int) -> tp.Optional[torch.Tensor]:
+    """Bias head rules of jax_flash_attn2/flash_attention.py:151-169: 1 or Hq heads broadcast,
+    Hkv heads are repeated per group ("b h q k -> b (h r) q k")."""
+    if x is not None and x.shape[1] not in (1, h):
+        x = x.repeat_interleave(h // x.shape[1], dim=1)
+    return _expand_term(x, b, h, sq, sk)
+
+
 def _visible(i0: int, bq: int, j0: int, bk: int, off: int) -> torch.Tensor:
     """Causal visibility of a (bq x bk) block: key j visible from query i iff j <= i + off."""
     qi = torch.arange(i0, i0 + bq)[:, None]
@@ -77,7 +85,7 @@ class BlockAttention:
         qf = rd(q.to(torch.float32).permute(0, 2, 1, 3) * scale)
         kf = k.to(torch.float32).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
         vf = v.to(torch.float32).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
-        bias_f = _expand_term(bias, B, Hq, Sq, Sk)
+        bias_f = _expand_bias(bias, B, Hq, Sq, Sk)
         mask_f = _expand_term(mask, B, Hq, Sq, Sk)
         keep = None
         if dropout_p > 0:
@@ -124,9 +132,12 @@ class BlockAttention:
     # -------------------------------------------------------------------------------------
     def backward(self, dO, q, k, v, o, lse, bias=None, mask=None, softmax_scale=None, causal=False,
                  dropout_p=0.0, dropout_seed=0, batch_offset=0, head_offset=0, heads_q_global=None,
-                 out_dtype=None):
+                 out_dtype=None, bias_grad=False):
         """Returns (dq, dk, dv) in `out_dtype` (default: the input dtype); dk / dv are summed over
-        the query heads of each key/value head."""
+        the query heads of each key/value head. With `bias_grad` a fourth result is the gradient of
+        the bias (float32, the bias's shape): dS summed over the batch elements and heads that share
+        a bias entry. The reference computes no such gradient; dS is the quantity of
+        _backward_jax.py:121 (`dS = p * (dP - D)`), which is d loss / d (scores + bias)."""
         dt = q.dtype if out_dtype is None else out_dtype
         B, Sq, Hq, D = q.shape
         Sk, Hkv = k.shape[1], k.shape[2]
@@ -138,8 +149,9 @@ class BlockAttention:
         vf = v.to(torch.float32).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
         of = o.to(torch.float32).permute(0, 2, 1, 3)
         dof = dO.to(torch.float32).permute(0, 2, 1, 3)
-        bias_f = _expand_term(bias, B, Hq, Sq, Sk)
+        bias_f = _expand_bias(bias, B, Hq, Sq, Sk)
         mask_f = _expand_term(mask, B, Hq, Sq, Sk)
+        dbias = torch.zeros(B, Hq, Sq, Sk) if bias_grad else None
         keep = None
         if dropout_p > 0:
             keep = torch.from_numpy(
@@ -176,8 +188,20 @@ class BlockAttention:
                     p_drop = p
                 dv[:, :, j0:j1] = rd(dv[:, :, j0:j1] + p_drop.transpose(-1, -2) @ dof[:, :, i0:i1])
                 ds = p * (dp - delta[:, :, i0:i1, None])
+                if dbias is not None:
+                    dbias[:, :, i0:i1, j0:j1] = ds
                 dq[:, :, i0:i1] = rd(dq[:, :, i0:i1] + (ds @ k_j) * scale)
                 dk[:, :, j0:j1] = rd(dk[:, :, j0:j1] + (ds.transpose(-1, -2) @ qf[:, :, i0:i1]) * scale)
         dk = dk.reshape(B, Hkv, G, Sk, D).sum(2)
         dv = dv.reshape(B, Hkv, G, Sk, D).sum(2)
-        return (dq.permute(0, 2, 1, 3).to(dt), dk.permute(0, 2, 1, 3).to(dt), dv.permute(0, 2, 1, 3).to(dt))
+        grads = (dq.permute(0, 2, 1, 3).to(dt), dk.permute(0, 2, 1, 3).to(dt), dv.permute(0, 2, 1, 3).to(dt))
+        if dbias is None:
+            return grads
+        bb, bh = bias.shape[0], bias.shape[1]
+        if bh not in (1, Hq):                            # one bias head per key/value head
+            dbias = dbias.reshape(B, bh, Hq // bh, Sq, Sk).sum(2)
+        elif bh == 1:
+            dbias = dbias.sum(1, keepdim=True)
+        if bb == 1:
+            dbias = dbias.sum(0, keepdim=True)
+        return grads + (dbias,)

@@ -30,7 +30,10 @@ def attention(q, k, v, bias=None, mask=None, softmax_scale=None, causal=False, d
     vd = v.to(torch.float64).permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
     s = (qd @ kd.transpose(-1, -2)) * scale
     if bias is not None:
-        s = s + bias.to(torch.float64)
+        bias = bias.to(torch.float64)
+        if bias.shape[1] not in (1, Hq):     # one bias head per key/value head (flash_attention.py:161-164)
+            bias = bias.repeat_interleave(Hq // bias.shape[1], dim=1)
+        s = s + bias
     if mask is not None:
         s = s + mask.to(torch.float64)
     if causal:
@@ -50,8 +53,13 @@ def attention(q, k, v, bias=None, mask=None, softmax_scale=None, causal=False, d
     return out.permute(0, 2, 1, 3), lse
 
 
-def attention_grads(dO, q, k, v, **kw):
-    """(dq, dk, dv) in float64 for the cotangent dO."""
+def attention_grads(dO, q, k, v, bias_grad=False, **kw):
+    """(dq, dk, dv) in float64 for the cotangent dO; with `bias_grad` also the gradient of
+    kw["bias"], in the bias's own shape."""
     q_, k_, v_ = (x.detach().to(torch.float64).requires_grad_(True) for x in (q, k, v))
+    wrt = (q_, k_, v_)
+    if bias_grad:
+        kw = dict(kw, bias=kw["bias"].detach().to(torch.float64).requires_grad_(True))
+        wrt = wrt + (kw["bias"],)
     out, _ = attention(q_, k_, v_, **kw)
-    return torch.autograd.grad(out, (q_, k_, v_), dO.to(torch.float64))
+    return torch.autograd.grad(out, wrt, dO.to(torch.float64))

@@ -17,6 +17,7 @@ import os
 import sys
 import types
 
+import ml_dtypes
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -36,6 +37,13 @@ def _install_numpy_jax():
 
     def _drop_precision(fn):
         def wrapped(*a, precision=None, **kw):
+            # numpy has no bfloat16 contraction kernel: bfloat16 operands are contracted in float32
+            # and the result rounded to bfloat16 once, which is also what XLA's CPU dot does for
+            # 16-bit operands. (float16 stays on numpy's own float16 path, as in the first vectors.)
+            arrays = [x for x in a if isinstance(x, np.ndarray)]
+            if arrays and all(x.dtype == ml_dtypes.bfloat16 for x in arrays):
+                a = tuple(x.astype(np.float32) if isinstance(x, np.ndarray) else x for x in a)
+                return fn(*a, **kw).astype(ml_dtypes.bfloat16)
             return fn(*a, **kw)
         return wrapped
 
@@ -45,6 +53,7 @@ def _install_numpy_jax():
     jnp.einsum = _drop_precision(np.einsum)
     jnp.matmul = _drop_precision(np.matmul)
     jnp.dtype = np.dtype
+    jnp.bfloat16 = ml_dtypes.bfloat16
 
     def dynamic_slice_in_dim(x, start, size, axis=0):
         idx = [slice(None)] * x.ndim
@@ -146,3 +155,7 @@ if __name__ == "__main__":
     _case("f32_bias", 1, 2, 128, 32, np.float32, False, True, 64, 1)
     _case("f32_causal_bias_b128", 1, 1, 256, 32, np.float32, True, True, 128, 2)
     _case("f16_causal", 1, 2, 256, 32, np.float16, True, False, 128, 3)
+    # 16-bit inputs at the head dims and block size of the CUDA kernels, causal mask and bias together
+    _case("bf16_causal_bias_d64_b128", 1, 1, 512, 64, ml_dtypes.bfloat16, True, True, 128, 4)
+    _case("bf16_causal_bias_d128_b128", 1, 1, 384, 128, ml_dtypes.bfloat16, True, True, 128, 5)
+    _case("f16_causal_bias_d128_b128", 1, 1, 256, 128, np.float16, True, True, 128, 6)

@@ -21,7 +21,8 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert set(_capi.EXPORTED_SYMBOLS) <= declared
-    assert lib.fa2_version() == 1003
+    assert lib.fa2_version() == _capi.FA2_ABI_VERSION == 2000
+    assert f"#define FA2_ABI_VERSION {_capi.FA2_ABI_VERSION}" in header
 
 
 def test_validation_errors_come_before_any_launch():
@@ -58,6 +59,70 @@ def test_validation_errors_come_before_any_launch():
     b = _capi.BwdParams()
     b.p = a.p
     assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_INVALID_ARG
+
+
+def _bwd_params_with_fake_pointers(workspace_address):
+    """A backward parameter block whose pointers are never dereferenced: validation stops first."""
+    lib = _capi.load()
+    b = _capi.BwdParams()
+    b.p.batch, b.p.seqlen_q, b.p.seqlen_k = 1, 128, 128
+    b.p.heads_q, b.p.heads_kv, b.p.head_dim = 4, 2, 128
+    b.p.dtype, b.p.softmax_scale, b.p.heads_q_global = _capi.FA2_BF16, 1.0, 4
+    for name in ("q", "k", "v", "o", "d_o", "lse", "dq", "dk", "dv"):
+        setattr(b, name, 0x10000)
+    b.lse_stride_h, b.lse_stride_b = 128, 4 * 128
+    b.workspace = workspace_address
+    b.workspace_bytes = lib.fa2_bwd_workspace_bytes(C.byref(b.p))
+    return lib, b
+
+
+def test_workspace_alignment_contract_is_128_bytes():
+    """A caller whose allocator hands out 128-byte-aligned temporaries (XLA's buffer assignment
+    does) must get past the workspace check; 64-byte alignment is refused with a clear message.
+    No kernel is launched: with fake pointers the call stops at the next validation step."""
+    lib, b = _bwd_params_with_fake_pointers(0x20000 + 64)
+    assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_WORKSPACE
+    assert b"128-byte aligned" in lib.fa2_last_error()
+    lib, b = _bwd_params_with_fake_pointers(0x20000 + 128)
+    b.q_strides = _capi.Strides(0, 0, 0)          # the next check after the workspace: operand strides
+    rc = lib.fa2_bwd(C.byref(b), None)
+    assert rc != _capi.FA2_OK and rc != _capi.FA2_ERR_WORKSPACE
+    b.workspace_bytes -= 1
+    assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_WORKSPACE
+
+
+def test_bias_gradient_arguments_are_validated():
+    lib, b = _bwd_params_with_fake_pointers(0x20000)
+    b.dbias.ptr, b.dbias.batch, b.dbias.heads = 0x30000, 1, 4
+    assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_INVALID_ARG
+    assert b"bias is not" in lib.fa2_last_error()
+    b.bias.ptr, b.bias.dtype = 0x40000, _capi.FA2_BF16
+    b.dbias.heads = 3
+    assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_INVALID_ARG
+    assert b"heads 1, 2 or 4" in lib.fa2_last_error()
+
+
+def test_problems_whose_item_counts_overflow_are_refused():
+    lib = _capi.load()
+    p = _capi.Problem()
+    p.dtype, p.softmax_scale = _capi.FA2_BF16, 1.0
+    p.batch, p.seqlen_q, p.seqlen_k, p.heads_q, p.heads_kv, p.head_dim = 65536, 16384, 16384, 64, 8, 128
+    p.heads_q_global = 64
+    assert lib.fa2_bwd_workspace_bytes(C.byref(p)) == 0
+    a = _capi.FwdParams()
+    a.p = p
+    assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_UNSUPPORTED
+    assert b"too large" in lib.fa2_last_error()
+
+
+def test_stale_library_version_is_refused(monkeypatch):
+    """The binding refuses a library whose ABI version differs from the one it was written for."""
+    monkeypatch.setattr(_capi, "_lib", None)
+    monkeypatch.setattr(_capi, "FA2_ABI_VERSION", 3000)
+    with pytest.raises(ImportError, match="ABI version"):
+        _capi.load()
+    monkeypatch.setattr(_capi, "FA2_ABI_VERSION", 2000)
+    assert _capi.load().fa2_version() == 2000
 
 
 def test_forward_scratch_is_only_asked_for_low_occupancy_problems():
@@ -97,14 +162,17 @@ def test_head_and_bias_rules():
     k = torch.zeros(1, 8, 4, 64, dtype=torch.bfloat16)
     with pytest.raises(ValueError, match="divisible"):
         fa(q, k, k)
-    assert fa._handle_bias(torch.zeros(1, 2, 8, 8), 4, 2).shape == (1, 4, 8, 8)
+    # a bias with one head per key/value head is passed through (the kernels index it by
+    # query head // group size instead of repeating it as the reference does)
+    kv_bias = torch.zeros(1, 2, 8, 8)
+    assert fa._handle_bias(kv_bias, 4, 2) is kv_bias
     assert fa._handle_bias(torch.zeros(1, 1, 8, 8), 4, 2).shape == (1, 1, 8, 8)
     with pytest.raises(ValueError, match="Incompatible bias shape"):
         fa._handle_bias(torch.zeros(1, 3, 8, 8), 4, 2)
-    # repeat follows "b h q k -> b (h r) q k": q head h uses bias head h // r
-    bias = torch.arange(2).float()[None, :, None, None].expand(1, 2, 8, 8)
-    rep = fa._handle_bias(bias, 4, 2)
-    assert rep[0, :, 0, 0].tolist() == [0, 0, 1, 1]
+    t, _ = _score_term(kv_bias, 1, 4, 8, 8, "bias", 2)
+    assert t.head_div == 2 and t.stride_h == 64
+    t, _ = _score_term(torch.zeros(1, 4, 8, 8), 1, 4, 8, 8, "bias", 2)
+    assert t.head_div == 1
     with pytest.raises(NotImplementedError):
         J.FlashAttention(J.AttentionConfig(backend=J.Backend.CPU))(q, q, q)
 

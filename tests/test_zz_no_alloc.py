@@ -54,11 +54,20 @@ def test_static_scratch_backward_matches_workspace_backward_twice_in_a_row():
         # dk / dv are bit-reproducible; dq is accumulated by unordered fp32 reductions
         assert torch.equal(dk, ref_dk) and torch.equal(dv, ref_dv)
         assert _rel(dq, ref_dq) <= 1e-2
-        # and once more on the same inputs
+        # and once more on the same inputs, this time watching the device's memory: with the
+        # outputs allocated beforehand the call itself must not take or return a single byte,
+        # neither from the driver (free memory of the device) nor from torch's caching allocator
         dq2, dk2, dv2 = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         a2 = _params(_capi, q, k, v, out, do, lse, dq2, dk2, dv2, causal)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        stats_before = torch.cuda.memory_stats()
         _capi.check(lib.fa2_bwd_static_scratch(C.byref(a2), stream))
         torch.cuda.synchronize()
+        stats_after = torch.cuda.memory_stats()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        for key in ("allocation.all.allocated", "allocation.all.freed", "segment.all.allocated"):
+            assert stats_after[key] == stats_before[key], key
         assert torch.equal(dk2, ref_dk) and torch.equal(dv2, ref_dv)
         assert _rel(dq2, ref_dq) <= 1e-2
 
