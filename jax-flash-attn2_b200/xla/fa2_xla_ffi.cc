@@ -11,10 +11,15 @@
 //       -I"$(python -c 'import jax.ffi; print(jax.ffi.include_dir())')" -I../../include \
 //       -I/usr/local/cuda/include -L.. -lfa2_b200 -Wl,-rpath,'$ORIGIN/..'
 //
-// Operands an attention call does not have (bias, mask, seqlens) are passed as one-element dummies,
-// as the reference does (_forward_triton.py:551-554); a dummy is recognised by element_count() <= 1.
-// Operand layout: q, o, d_o, dq [B, Sq, Hq, D]; k, v, dk, dv [B, Sk, Hkv, D]; bias / mask
-// [1|B, 1|Hq, 1|Sq, Sk]; lse [B, Hq, ceil(Sq/128)*128] float32; seqlens [B] int32.
+// Operands an attention call does not have (bias, mask, seqlens, seed, offsets) are passed as
+// one-element dummies, as the reference does (_forward_triton.py:551-554); a dummy is recognised by
+// its element count or element type.
+// Operand layout: q, o, d_o, dq [B, Sq, Hq, D]; k, v, dk, dv [B, Sk, Hkv, D]; bias
+// [1|B, 1|Hkv|Hq, 1|Sq, Sk]; mask [1|B, 1|Hq, 1|Sq, Sk]; lse [B, Hq, ceil(Sq/128)*128] float32;
+// seqlens [B] int32; seed uint32 [2] or one 64-bit integer; offsets int32 [2] = (batch offset, head
+// offset) of this shard, a traced value under shard_map.
+// Scratch results are declared kScratchSlack bytes larger than the library asks for and aligned up
+// here, so the handlers do not depend on the alignment XLA gives a sub-allocated result.
 #include <cstdint>
 #include <string>
 
@@ -26,6 +31,26 @@
 namespace ffi = xla::ffi;
 
 namespace {
+
+constexpr size_t kScratchAlign = 128;   // what fa2_fwd / fa2_bwd require of a workspace pointer
+constexpr size_t kScratchSlack = 128;   // extra bytes the JAX side declares for the alignment
+
+// The first call refuses a core library whose structures have another layout than this file's.
+bool AbiMatches() {
+  static const bool ok = (fa2_version() / 1000 == FA2_ABI_VERSION / 1000) && fa2_version() >= FA2_ABI_VERSION;
+  return ok;
+}
+
+struct Scratch {
+  void* ptr;
+  size_t bytes;
+};
+Scratch AlignedScratch(void* data, size_t total) {
+  const uintptr_t raw = reinterpret_cast<uintptr_t>(data);
+  const uintptr_t up = (raw + kScratchAlign - 1) / kScratchAlign * kScratchAlign;
+  const size_t lost = static_cast<size_t>(up - raw);
+  return {reinterpret_cast<void*>(up), total > lost ? total - lost : 0};
+}
 
 fa2_strides ContiguousBSHD(const ffi::AnyBuffer& x) {
   const auto d = x.dimensions();
@@ -43,13 +68,15 @@ bool DtypeOf(const ffi::AnyBuffer& x, int32_t* out) {
 }
 
 // Additive score term [1|B, 1|Hq, 1|Sq, Sk] (row-major): stride 0 on broadcast dimensions, the
-// rules of calc_bias_strides (flash_attention_triton/_utils.py:151-193).
-bool ScoreTerm(const ffi::AnyBuffer& x, fa2_score_term* t) {
+// rules of calc_bias_strides (flash_attention_triton/_utils.py:151-193). A term with heads_kv heads
+// (1 < heads_kv < heads_q) is read by query head / group size instead of being repeated.
+bool ScoreTerm(const ffi::AnyBuffer& x, int32_t heads_q, int32_t heads_kv, fa2_score_term* t) {
   *t = fa2_score_term{};
   if (x.element_count() <= 1) return true;   // dummy: absent
   const auto d = x.dimensions();
   if (d.size() != 4 || !DtypeOf(x, &t->dtype)) return false;
   t->ptr = x.untyped_data();
+  t->head_div = (d[1] == heads_kv && d[1] != heads_q && d[1] != 1) ? heads_q / heads_kv : 1;
   t->stride_q = d[2] == 1 ? 0 : d[3];
   t->stride_h = d[1] == 1 ? 0 : d[2] * d[3];
   t->stride_b = d[0] == 1 ? 0 : d[1] * d[2] * d[3];
@@ -99,16 +126,24 @@ const uint64_t* SeedOrNull(const ffi::AnyBuffer& x) {
   return (two_words || one_word) ? static_cast<const uint64_t*>(x.untyped_data()) : nullptr;
 }
 
+// Shard offsets as an operand: int32 [2]; anything else means "absent" (the attributes are used).
+const int32_t* OffsetsOrNull(const ffi::AnyBuffer& x) {
+  return (x.element_type() == ffi::DataType::S32 && x.element_count() == 2)
+             ? static_cast<const int32_t*>(x.untyped_data())
+             : nullptr;
+}
+
 ffi::Error Failed(const char* what) {
   return ffi::Error::InvalidArgument(std::string(what) + ": " + fa2_last_error());
 }
 
 ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi::AnyBuffer v,
                    ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed,
-                   float softmax_scale, float dropout_p, bool causal, int64_t dropout_seed,
-                   int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
+                   ffi::AnyBuffer offsets, float softmax_scale, float dropout_p, bool causal,
+                   int64_t dropout_seed, int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
                    ffi::Result<ffi::AnyBuffer> o, ffi::Result<ffi::AnyBuffer> lse,
                    ffi::Result<ffi::AnyBuffer> workspace) {
+  if (!AbiMatches()) return ffi::Error::InvalidArgument("fa2_b200_fwd: libfa2_b200.so has another ABI version");
   fa2_fwd_params a = {};
   if (!Problem(q, k, causal, softmax_scale, dropout_p, dropout_seed, batch_offset, head_offset,
                heads_q_global, &a.p))
@@ -120,26 +155,29 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
   a.lse = static_cast<float*>(lse->untyped_data());
   a.lse_stride_h = lse->dimensions()[2];
   a.lse_stride_b = a.lse_stride_h * lse->dimensions()[1];
-  if (!ScoreTerm(bias, &a.bias) || !ScoreTerm(mask, &a.mask))
+  if (!ScoreTerm(bias, a.p.heads_q, a.p.heads_kv, &a.bias) || !ScoreTerm(mask, a.p.heads_q, a.p.heads_q, &a.mask))
     return ffi::Error::InvalidArgument("fa2_b200_fwd: bias / mask must be 4-D fp16, bf16 or fp32");
   a.seqlens = SeqlensOrNull(seqlens, a.p.batch);
   a.dropout_seed_dev = SeedOrNull(seed);
-  // scratch for split-KV: a uint8 result of fa2_fwd_workspace_bytes(problem) bytes (one byte when
-  // the problem is not split); fa2_fwd ignores scratch that is too small
-  a.workspace = workspace->untyped_data();
-  a.workspace_bytes = static_cast<size_t>(workspace->element_count());
+  a.offsets_dev = OffsetsOrNull(offsets);
+  // scratch for split-KV: a uint8 result of fa2_fwd_workspace_bytes(problem) + kScratchSlack bytes
+  // (just the slack when the problem is not split); fa2_fwd ignores scratch that is too small
+  const Scratch ws = AlignedScratch(workspace->untyped_data(), static_cast<size_t>(workspace->element_count()));
+  a.workspace = ws.ptr;
+  a.workspace_bytes = ws.bytes;
   if (fa2_fwd(&a, stream) != FA2_OK) return Failed("fa2_b200_fwd");
   return ffi::Error::Success();
 }
 
 ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ffi::AnyBuffer k,
                    ffi::AnyBuffer v, ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer o,
-                   ffi::AnyBuffer lse, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed, float softmax_scale,
-                   float dropout_p,
-                   bool causal, int64_t dropout_seed, int32_t batch_offset, int32_t head_offset,
-                   int32_t heads_q_global, ffi::Result<ffi::AnyBuffer> dq,
-                   ffi::Result<ffi::AnyBuffer> dk, ffi::Result<ffi::AnyBuffer> dv,
+                   ffi::AnyBuffer lse, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed, ffi::AnyBuffer offsets,
+                   float softmax_scale, float dropout_p, bool causal, int64_t dropout_seed,
+                   int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
+                   ffi::Result<ffi::AnyBuffer> dq, ffi::Result<ffi::AnyBuffer> dk,
+                   ffi::Result<ffi::AnyBuffer> dv, ffi::Result<ffi::AnyBuffer> dbias,
                    ffi::Result<ffi::AnyBuffer> workspace) {
+  if (!AbiMatches()) return ffi::Error::InvalidArgument("fa2_b200_bwd: libfa2_b200.so has another ABI version");
   fa2_bwd_params a = {};
   if (!Problem(q, k, causal, softmax_scale, dropout_p, dropout_seed, batch_offset, head_offset,
                heads_q_global, &a.p))
@@ -152,16 +190,29 @@ ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ff
   a.lse = static_cast<const float*>(lse.untyped_data());
   a.lse_stride_h = lse.dimensions()[2];
   a.lse_stride_b = a.lse_stride_h * lse.dimensions()[1];
-  if (!ScoreTerm(bias, &a.bias) || !ScoreTerm(mask, &a.mask))
+  if (!ScoreTerm(bias, a.p.heads_q, a.p.heads_kv, &a.bias) || !ScoreTerm(mask, a.p.heads_q, a.p.heads_q, &a.mask))
     return ffi::Error::InvalidArgument("fa2_b200_bwd: bias / mask must be 4-D fp16, bf16 or fp32");
+  // gradient of the bias: a float32 result of the bias's shape when it is wanted, a one-element
+  // dummy otherwise
+  if (dbias->element_count() > 1) {
+    const auto bd = dbias->dimensions();
+    if (bd.size() != 4 || dbias->element_type() != ffi::DataType::F32)
+      return ffi::Error::InvalidArgument("fa2_b200_bwd: dbias must be a 4-D float32 result");
+    a.dbias.ptr = static_cast<float*>(dbias->untyped_data());
+    a.dbias.batch = static_cast<int32_t>(bd[0]);
+    a.dbias.heads = static_cast<int32_t>(bd[1]);
+  }
   a.dq = dq->untyped_data(); a.dq_strides = ContiguousBSHD(q);
   a.dk = dk->untyped_data(); a.dk_strides = ContiguousBSHD(k);
   a.dv = dv->untyped_data(); a.dv_strides = ContiguousBSHD(k);
-  // the workspace is a uint8 result of fa2_bwd_workspace_bytes(problem) bytes, so XLA allocates it
-  a.workspace = workspace->untyped_data();
-  a.workspace_bytes = static_cast<size_t>(workspace->element_count());
+  // the workspace is a uint8 result of fa2_bwd_workspace_bytes(problem) + kScratchSlack bytes, so
+  // XLA allocates it
+  const Scratch ws = AlignedScratch(workspace->untyped_data(), static_cast<size_t>(workspace->element_count()));
+  a.workspace = ws.ptr;
+  a.workspace_bytes = ws.bytes;
   a.seqlens = SeqlensOrNull(seqlens, a.p.batch);
   a.dropout_seed_dev = SeedOrNull(seed);
+  a.offsets_dev = OffsetsOrNull(offsets);
   if (fa2_bwd(&a, stream) != FA2_OK) return Failed("fa2_b200_bwd");
   return ffi::Error::Success();
 }
@@ -179,6 +230,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Arg<ffi::AnyBuffer>()   // mask   (or a one-element dummy)
         .Arg<ffi::AnyBuffer>()   // seqlens int32 [B] (or a one-element dummy of another dtype)
         .Arg<ffi::AnyBuffer>()   // seed: uint32 [2] (low, high) or one 64-bit integer (or a dummy)
+        .Arg<ffi::AnyBuffer>()   // offsets: int32 [2] (batch offset, head offset) (or a dummy)
         .Attr<float>("softmax_scale")
         .Attr<float>("dropout_p")
         .Attr<bool>("causal")
@@ -204,6 +256,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Arg<ffi::AnyBuffer>()   // lse
         .Arg<ffi::AnyBuffer>()   // seqlens
         .Arg<ffi::AnyBuffer>()   // seed
+        .Arg<ffi::AnyBuffer>()   // offsets
         .Attr<float>("softmax_scale")
         .Attr<float>("dropout_p")
         .Attr<bool>("causal")
@@ -214,4 +267,5 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Ret<ffi::AnyBuffer>()    // dq
         .Ret<ffi::AnyBuffer>()    // dk
         .Ret<ffi::AnyBuffer>()    // dv
+        .Ret<ffi::AnyBuffer>()    // dbias: float32, the bias's shape (or a one-element dummy)
         .Ret<ffi::AnyBuffer>());  // workspace (uint8)

@@ -23,7 +23,12 @@ import jax.numpy as jnp
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
+FA2_ABI_VERSION = 2000      # of the include/fa2_b200.h this module was written against
+_SCRATCH_SLACK = 128        # kScratchSlack of fa2_xla_ffi.cc: room to align a scratch result
 _core = ctypes.CDLL(os.path.join(_HERE, "..", "libfa2_b200.so"), mode=ctypes.RTLD_GLOBAL)
+_core.fa2_version.restype = ctypes.c_int
+if _core.fa2_version() // 1000 != FA2_ABI_VERSION // 1000 or _core.fa2_version() < FA2_ABI_VERSION:
+    raise ImportError(f"libfa2_b200.so has ABI version {_core.fa2_version()}, this binding needs {FA2_ABI_VERSION}")
 _shim = ctypes.CDLL(os.path.join(_HERE, "libfa2_b200_xla.so"))
 for _name in ("fa2_b200_fwd", "fa2_b200_bwd"):
     jax.ffi.register_ffi_target(_name, jax.ffi.pycapsule(getattr(_shim, _name)), platform="CUDA")
@@ -61,13 +66,14 @@ def _workspace_bytes(q_shape, k_shape, dtype) -> int:
     n = int(_core.fa2_bwd_workspace_bytes(ctypes.byref(_problem(q_shape, k_shape, dtype))))
     if n == 0:
         raise ValueError("fa2_b200: unsupported problem (head_dim, dtype or shape)")
-    return n
+    return n + _SCRATCH_SLACK
 
 
 def _fwd_workspace_bytes(q_shape, k_shape, dtype, dropout_prob) -> int:
     """Scratch with which the forward splits a low-occupancy problem along the key sequence
-    (0 for most problems; a one-byte result is declared then)."""
-    return int(_core.fa2_fwd_workspace_bytes(ctypes.byref(_problem(q_shape, k_shape, dtype, dropout_prob))))
+    (nothing for most problems: only the alignment slack is declared then)."""
+    n = int(_core.fa2_fwd_workspace_bytes(ctypes.byref(_problem(q_shape, k_shape, dtype, dropout_prob))))
+    return n + _SCRATCH_SLACK
 
 
 def _operands(q, bias, attention_mask):
@@ -96,21 +102,29 @@ def _seed_operand(q, dropout_seed):
     return jnp.stack([s, jnp.zeros((), jnp.uint32)]), 0
 
 
-def _attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, offsets):
+def _offsets_operand(q, offsets):
+    """(batch offset, head offset) of this shard inside the unsharded problem as an int32 [2]
+    operand (a traced value under shard_map); None means (0, 0)."""
+    if offsets is None:
+        return jnp.zeros((1,), q.dtype)
+    return jnp.asarray(offsets, dtype=jnp.int32).reshape((2,))
+
+
+def _attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, heads_q_global):
     return dict(
         softmax_scale=np.float32(1.0 / math.sqrt(q.shape[-1]) if softmax_scale is None else softmax_scale),
         dropout_p=np.float32(dropout_prob),
         causal=bool(causal),
         dropout_seed=np.int64(0 if dropout_seed is None else dropout_seed),
-        batch_offset=np.int32(offsets[0]),
-        head_offset=np.int32(offsets[1]),
-        heads_q_global=np.int32(offsets[2] or q.shape[2]),
+        batch_offset=np.int32(0),          # shards pass their position as the `offsets` operand
+        head_offset=np.int32(0),
+        heads_q_global=np.int32(heads_q_global or q.shape[2]),
     )
 
 
 def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_scale=None,
                                dropout_prob=0.0, causal=False, dropout_seed=None, varlen_mode=True,
-                               *, offsets=(0, 0, None)):
+                               *, offsets=None, heads_q_global=None):
     del varlen_mode
     assert q.shape[2] % k.shape[2] == 0, f"nheads_q = {q.shape[2]} is not divisible by nheads_kv = {k.shape[2]}"
     assert q.dtype == k.dtype == v.dtype, "All tensors must have the same type"
@@ -121,48 +135,62 @@ def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_
     out_types = (
         jax.ShapeDtypeStruct(q.shape, q.dtype),
         jax.ShapeDtypeStruct((batch, hq, -(-sq // 128) * 128), jnp.float32),
-        jax.ShapeDtypeStruct((max(1, _fwd_workspace_bytes(q.shape, k.shape, q.dtype, dropout_prob)),), jnp.uint8),
+        jax.ShapeDtypeStruct((_fwd_workspace_bytes(q.shape, k.shape, q.dtype, dropout_prob),), jnp.uint8),
     )
     out, lse, _ = jax.ffi.ffi_call("fa2_b200_fwd", out_types)(
-        q, k, v, bias_, mask_, seqlens, seed_op,
-        **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, offsets))
+        q, k, v, bias_, mask_, seqlens, seed_op, _offsets_operand(q, offsets),
+        **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, heads_q_global))
     return out, lse
 
 
 def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_prob, causal,
-                               softmax_scale, dropout_seed, varlen_mode=True, *, offsets=(0, 0, None)):
+                               softmax_scale, dropout_seed, varlen_mode=True, *, offsets=None,
+                               heads_q_global=None, bias_grad=False):
     del varlen_mode
     bias_, mask_, seqlens = _operands(q, bias, attention_mask)
     seed_op, seed_attr = _seed_operand(q, dropout_seed)
+    want_dbias = bias_grad and bias is not None
     out_types = (
         jax.ShapeDtypeStruct(q.shape, q.dtype),
         jax.ShapeDtypeStruct(k.shape, k.dtype),
         jax.ShapeDtypeStruct(v.shape, v.dtype),
+        jax.ShapeDtypeStruct(bias.shape if want_dbias else (1,), jnp.float32),
         jax.ShapeDtypeStruct((_workspace_bytes(q.shape, k.shape, q.dtype),), jnp.uint8),
     )
-    dq, dk, dv, _ = jax.ffi.ffi_call("fa2_b200_bwd", out_types)(
-        dO, q, k, v, bias_, mask_, o, M, seqlens, seed_op,
-        **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, offsets))
-    return dq, dk, dv
+    dq, dk, dv, dbias, _ = jax.ffi.ffi_call("fa2_b200_bwd", out_types)(
+        dO, q, k, v, bias_, mask_, o, M, seqlens, seed_op, _offsets_operand(q, offsets),
+        **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, heads_q_global))
+    return dq, dk, dv, (dbias.astype(bias.dtype) if want_dbias else None)
 
 
-@functools.partial(jax.custom_vjp, nondiff_argnums=(5, 6, 7, 8))
-def flash_attention_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed):
+# Static (re-trace on change): softmax_scale, dropout_prob, causal, varlen_mode, as in the reference
+# (flash_attention_triton/_flash_attention.py:91-92, nondiff_argnums=(5, 6, 7, 9)), plus the two
+# static additions at the end. dropout_seed (8) and offsets (10) are traced operands: they take the
+# place of differentiable arguments and get a None cotangent, like the seed in the reference (:88).
+@functools.partial(jax.custom_vjp, nondiff_argnums=(5, 6, 7, 9, 11, 12))
+def flash_attention_call(q, k, v, attention_mask=None, bias=None, softmax_scale=None, dropout_prob=0.0,
+                         causal=False, dropout_seed=None, varlen_mode=True, offsets=None,
+                         heads_q_global=None, bias_grad=False):
     return _fwd_attention_kernel_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal,
-                                      dropout_seed)[0]
+                                      dropout_seed, varlen_mode, offsets=offsets,
+                                      heads_q_global=heads_q_global)[0]
 
 
-def _vjp_fwd(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed):
+def _vjp_fwd(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, varlen_mode,
+             offsets, heads_q_global, bias_grad):
     out, lse = _fwd_attention_kernel_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob,
-                                          causal, dropout_seed)
-    return out, (q, k, v, bias, attention_mask, out, lse)
+                                          causal, dropout_seed, varlen_mode, offsets=offsets,
+                                          heads_q_global=heads_q_global)
+    return out, (q, k, v, bias, attention_mask, out, lse, dropout_seed, offsets)
 
 
-def _vjp_bwd(softmax_scale, dropout_prob, causal, dropout_seed, residuals, dO):
-    q, k, v, bias, attention_mask, out, lse = residuals
-    dq, dk, dv = _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, out, lse, dropout_prob,
-                                            causal, softmax_scale, dropout_seed)
-    return dq, dk, dv, None, None
+def _vjp_bwd(softmax_scale, dropout_prob, causal, varlen_mode, heads_q_global, bias_grad, residual, dO):
+    q, k, v, bias, attention_mask, out, lse, dropout_seed, offsets = residual
+    dq, dk, dv, dbias = _bwd_attention_kernel_call(
+        dO, q, k, v, bias, attention_mask, out, lse, dropout_prob, causal, softmax_scale, dropout_seed,
+        varlen_mode, offsets=offsets, heads_q_global=heads_q_global, bias_grad=bias_grad)
+    # cotangents of (q, k, v, attention_mask, bias, dropout_seed, offsets)
+    return dq, dk, dv, None, dbias, None, None
 
 
 flash_attention_call.defvjp(_vjp_fwd, _vjp_bwd)
@@ -172,8 +200,10 @@ def sharded_flash_attention(q, k, v, *, causal=False, softmax_scale=None, dropou
                             dropout_seed=None, mesh_shape: tp.Optional[tp.Tuple[int, int]] = None):
     """One call spread over the local GPUs by (batch, kv head): every device runs the single-GPU
     kernels on its slice, no collective is issued (the query heads of a kv head are contiguous, so
-    q's head axis shards consistently with k / v). The offsets keep the dropout bits those of the
-    unsharded call."""
+    q's head axis shards consistently with k / v). Each shard hands its position in the mesh to the
+    kernels as a traced int32 [2] operand, which keeps the dropout bits those of the unsharded call
+    and needs one trace for all mesh positions; the body is the custom_vjp above, so jax.grad works
+    through the sharded call and the backward sees the same offsets."""
     from jax.experimental.shard_map import shard_map
     from jax.sharding import Mesh, PartitionSpec as P
 
@@ -185,16 +215,8 @@ def sharded_flash_attention(q, k, v, *, causal=False, softmax_scale=None, dropou
     pb, ph = q.shape[0] // nb, q.shape[2] // nh
 
     def local(q_, k_, v_):
-        # static offsets are needed by the FFI attributes, so every (b, h) position gets its own
-        # trace of the call; the mesh is small (at most the 8 GPUs of a box)
-        ib, ih = jax.lax.axis_index("b"), jax.lax.axis_index("h")
-        branches = [
-            functools.partial(
-                lambda qq, kk, vv, off: _fwd_attention_kernel_call(
-                    qq, kk, vv, None, None, softmax_scale, dropout_prob, causal, dropout_seed, offsets=off)[0],
-                off=(b * pb, h * ph, hq_global))
-            for b in range(nb) for h in range(nh)
-        ]
-        return jax.lax.switch(ib * nh + ih, branches, q_, k_, v_)
+        offsets = jnp.stack([jax.lax.axis_index("b") * pb, jax.lax.axis_index("h") * ph]).astype(jnp.int32)
+        return flash_attention_call(q_, k_, v_, None, None, softmax_scale, dropout_prob, causal, dropout_seed,
+                                    True, offsets, hq_global, False)
 
     return shard_map(local, mesh, in_specs=(spec, spec, spec), out_specs=spec, check_rep=False)(q, k, v)
