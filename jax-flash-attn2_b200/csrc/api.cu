@@ -11,6 +11,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -174,6 +175,35 @@ int make_score_term(ScoreTermDev* out, const fa2_score_term& t, const fa2_proble
   return FA2_OK;
 }
 
+// Tensor map of an additive score term for the kernels that stage it in shared memory: the 4-D
+// tensor (Sk, Sq, heads, batch) of 16-bit elements, broadcast dimensions with extent 1, box
+// (64 keys, box_rows query rows). Sets t->staged when the term qualifies: the q dtype, a real query
+// dimension, 16-byte aligned base and strides (the TMA unit's rules). Otherwise the term stays on
+// the direct-load path and the map is left untouched.
+void try_stage_term(CUtensorMap* tm, ScoreTermDev* t, const fa2_problem& p, int box_rows) {
+  t->staged = 0;
+  if (!t->ptr || t->is_f32 || t->sq <= 0) return;
+  if ((reinterpret_cast<uintptr_t>(t->ptr) & 15) || (t->sq % 8) || (t->sh % 8) || (t->sb % 8)) return;
+  if (p.seqlen_k < 8) return;
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return;
+  const cuuint64_t nh = t->sh ? static_cast<cuuint64_t>(p.heads_q / t->head_div) : 1;
+  const cuuint64_t nb = t->sb ? static_cast<cuuint64_t>(p.batch) : 1;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(p.seqlen_k), static_cast<cuuint64_t>(p.seqlen_q), nh, nb};
+  // a dimension of extent 1 still needs a legal stride: the natural one
+  const cuuint64_t s_q = static_cast<cuuint64_t>(t->sq) * 2;
+  const cuuint64_t s_h = t->sh ? static_cast<cuuint64_t>(t->sh) * 2 : s_q * dims[1];
+  const cuuint64_t s_b = t->sb ? static_cast<cuuint64_t>(t->sb) * 2 : s_h * nh;
+  const cuuint64_t strides[3] = {s_q, s_h, s_b};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r =
+      enc(tm, p.dtype == FA2_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+          const_cast<void*>(t->ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) t->staged = 1;
+}
+
 void make_dropout(DropoutDev* d, const fa2_problem& p) {
   std::memset(d, 0, sizeof(*d));
   d->enabled = p.dropout_p > 0.f;
@@ -258,6 +288,16 @@ SplitPlan plan_splits(const fa2_problem& p, const HeadDim& hd, bool pack_heads) 
   const size_t sq_pad = static_cast<size_t>((s.sq_k + 127) / 128) * 128;
   s.total = s.part_lse_off + align_up(static_cast<size_t>(s.n_splits) * p.batch * s.hq_k * sq_pad * 4, 256);
   return s;
+}
+
+// FA2_B200_DISABLE_PAIR_MMA=1 in the environment keeps the forward on the single-CTA kernel where
+// the CTA-pair kernel would be chosen (same results; for comparing the two and as a fallback).
+bool pair_mma_disabled() {
+  static const bool off = [] {
+    const char* v = std::getenv("FA2_B200_DISABLE_PAIR_MMA");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return off;
 }
 
 bool can_pack_heads(const fa2_problem& p) {
@@ -394,6 +434,19 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   L.causal = causal;
   // The plain path assumes a positive scale (it takes the row maximum before scaling).
   L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled || !(p.softmax_scale > 0.f);
+  if (L.feat && D == 64) {
+    // the head-dim-64 kernel streams 16-bit bias / mask tiles through shared memory
+    try_stage_term(&L.tmBias, &kp.bias, p, 32);
+    try_stage_term(&L.tmMask, &kp.mask, p, 32);
+  }
+  // Head dim 128 without score terms, an even number of query heads per key/value head, no
+  // key split: two heads of a group share every K/V tile on a pair of CTAs (2-CTA MMAs).
+  L.pair = D == 128 && !L.feat && !split && !pack_heads && (kp.G % 2 == 0) && !pair_mma_disabled();
+  if (L.pair) {
+    if ((rc = make_tmap(&L.tmKh, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 64, "k")) ||
+        (rc = make_tmap(&L.tmVh, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v", 1)))
+      return rc;
+  }
 
   cudaError_t e = launch_fwd(L, static_cast<cudaStream_t>(cuda_stream));
   if (e != cudaSuccess)
@@ -509,6 +562,11 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   L.bf16 = bf16;
   L.causal = p.causal != 0;
   L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled;
+  if (L.feat && D == 64) {
+    // the head-dim-64 kernel brings 16-bit bias / mask tiles in through the TMA unit
+    try_stage_term(&L.tmBias, &kp.bias, p, 128);
+    try_stage_term(&L.tmMask, &kp.mask, p, 128);
+  }
   if (a->dbias.ptr) {
     const long long plane = static_cast<long long>(p.seqlen_q) * p.seqlen_k;
     kp.dbias.ptr = a->dbias.ptr;

@@ -9,6 +9,9 @@ namespace fa2 {
 
 struct BwdLaunch {
   CUtensorMap tmQ, tmK, tmV, tmdO, tmdK, tmdV;
+  // bias / mask as 4-D tensors (Sk, Sq, heads, batch), box 64 keys x 128 query rows: used by the
+  // head-dim-64 kernel when it stages these terms in shared memory (kp.bias.staged / kp.mask.staged)
+  CUtensorMap tmBias, tmMask;
   BwdKernelParams kp;
   int head_dim;        // 64, 128 or 256: the kernel's (padded) head dim
   int head_dim_real;   // the operands' head dim

@@ -50,7 +50,10 @@ struct BwdRoles {
   static constexpr int kWarpDrain = 4 * kPW, kWarpMma = 4 * kPW + 4, kWarpTma = 4 * kPW + 5;
 };
 
-template <int D>
+// kStaged (score terms / dropout at head dim 64): bias and mask tiles of a step, [128 queries][128
+// keys] 16-bit each, are brought in by the TMA unit one step ahead (single-buffered: they are read
+// at the very start of a step) instead of being gathered column by column from global memory.
+template <int D, bool kStaged = false>
 struct BwdSmem {
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kBlockBytes = 128 * 128;   // one [128 rows][64 elements] block
@@ -63,8 +66,10 @@ struct BwdSmem {
   static constexpr int kStageOff = kdOOff + kTileBytes;
   static constexpr int kdSOff = kStageOff + 2 * kChunkBytes;   // [128 keys][128 queries] 16 bit
   static constexpr int kStatsOff = kdSOff + 128 * 128 * 2; // 2 stages x (lse2[128], delta[128])
-  static constexpr int kBarOff = kStatsOff + 2 * 1024;
-  static constexpr int kNumBars = 17;
+  static constexpr int kTermBytes = 128 * 128 * 2;          // one term tile: two [128 q][64 keys] blocks
+  static constexpr int kTermOff = kStatsOff + 2 * 1024;     // bias tile, mask tile
+  static constexpr int kBarOff = kTermOff + (kStaged ? 2 * kTermBytes : 0);
+  static constexpr int kNumBars = 17 + 4;                   // + term_full[2], term_empty[2]
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = (kTotal + 1024 <= kMaxDynSmem) ? kTotal + 1024 : kMaxDynSmem;
@@ -133,8 +138,10 @@ __global__ void __launch_bounds__(BwdRoles<D>::kThreads, 1)
 bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
+                const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
                 const float* __restrict__ stats, const BwdKernelParams p) {
-  using L = BwdSmem<D>;
+  constexpr bool kStaged = kFeat && D == 64;
+  using L = BwdSmem<D, kStaged>;
   using R = BwdRoles<D>;
   constexpr int kPW = R::kPW, kCW = R::kCW;
   constexpr int kWarpDrain = R::kWarpDrain, kWarpMma = R::kWarpMma, kWarpTma = R::kWarpTma;
@@ -160,6 +167,8 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t bar_dq_full = bars + 8u * 13, bar_dq_drained = bars + 8u * 14;
   const uint32_t bar_dkv_full = bars + 8u * 15;
   const uint32_t bar_kv_tmem = bars + 8u * 16;   // D = 64: K and V have been copied into tensor memory
+  auto bar_term_full = [&](int x) { return bars + 8u * (17 + x); };    // x = 0: bias, 1: mask
+  auto bar_term_empty = [&](int x) { return bars + 8u * (19 + x); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
@@ -207,6 +216,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     mbar_init(bar_dq_drained, 128);
     mbar_init(bar_dkv_full, 1);
     mbar_init(bar_kv_tmem, 256);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(bar_term_full(x), 1);
+      mbar_init(bar_term_empty(x), 128 * kPW);
+    }
     fence_mbar_init();
   }
   if (warp == kWarpTma && lane == 0) {
@@ -214,6 +227,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmdO);
+    if constexpr (kStaged) {
+      if (p.bias.staged) tma_prefetch_desc(&tmBias);
+      if (p.mask.staged) tma_prefetch_desc(&tmMask);
+    }
   }
   if (warp == 0) {
     __syncwarp();
@@ -261,6 +278,22 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         bulk_load_1d(sStats + st * 1024,
                      stats + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * 256, 1024,
                      bar_q_full(st));
+        if constexpr (kStaged) {
+          // the step's bias / mask tiles: their buffers were read at the start of the previous step
+#pragma unroll
+          for (int x = 0; x < 2 && ok; ++x) {
+            const ScoreTermDev& tt = x ? p.mask : p.bias;
+            if (!tt.staged) continue;
+            ok = mbar_wait(bar_term_empty(x), (it & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar_term_full(x), L::kTermBytes);
+            const uint32_t dst = smem_base + L::kTermOff + x * L::kTermBytes;
+            const int hx = tt.sh ? h / tt.head_div : 0, bx = tt.sb ? b : 0;
+            tma_load_4d(dst, x ? &tmMask : &tmBias, bar_term_full(x), n * kBN, i * kBM, hx, bx);
+            tma_load_4d(dst + L::kBlockBytes, x ? &tmMask : &tmBias, bar_term_full(x), n * kBN + 64, i * kBM, hx, bx);
+          }
+          if (!ok) break;
+        }
         ok = mbar_wait(bar_do_empty, (it & 1) ^ 1, abort_flag);
         if (!ok) break;
         mbar_arrive_expect_tx(bar_do_full, L::kTileBytes);
@@ -526,8 +559,33 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if constexpr (kFeat) {
 #pragma unroll
           for (int c = 0; c < kCW; ++c) s[c] = __float_as_uint(__uint_as_float(s[c]) * p.scale_log2);
-          add_term_column<kBf16, kCW>(p.bias, b, h, q_first, kv, p.Sq, p.Sk, s);
-          add_term_column<kBf16, kCW>(p.mask, b, h, q_first, kv, p.Sq, p.Sk, s);
+          if constexpr (kStaged) {
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+              const ScoreTermDev& tt = x ? p.mask : p.bias;
+              if (!tt.staged) continue;
+              if (ok) ok = mbar_wait(bar_term_full(x), it & 1, abort_flag);
+              if (ok) {
+                // column r of the staged [128 queries][128 keys] tile: element (query, key r) sits in
+                // block r / 64, row `query`, 16-byte chunk (r % 64) / 8 (swizzled with the row)
+                const uint32_t col = smem_base + L::kTermOff + x * L::kTermBytes + (r >> 6) * L::kBlockBytes +
+                                     (r & 7) * 2;
+                const uint32_t chunk = static_cast<uint32_t>((r & 63) >> 3);
+#pragma unroll
+                for (int c = 0; c < kCW; ++c) {
+                  const int qrow = kCW * w + c;
+                  const uint16_t v = lds16(col + qrow * 128 + ((chunk ^ (qrow & 7)) << 4));
+                  s[c] = __float_as_uint(fmaf(to_float16bit<kBf16>(v), kLog2e, __uint_as_float(s[c])));
+                }
+              }
+              mbar_arrive(bar_term_empty(x));
+            }
+            if (!p.bias.staged) add_term_column<kBf16, kCW>(p.bias, b, h, q_first, kv, p.Sq, p.Sk, s);
+            if (!p.mask.staged) add_term_column<kBf16, kCW>(p.mask, b, h, q_first, kv, p.Sq, p.Sk, s);
+          } else {
+            add_term_column<kBf16, kCW>(p.bias, b, h, q_first, kv, p.Sq, p.Sk, s);
+            add_term_column<kBf16, kCW>(p.mask, b, h, q_first, kv, p.Sq, p.Sk, s);
+          }
         }
 #pragma unroll
         for (int c4 = 0; c4 < kCW / 4; ++c4) {
@@ -679,14 +737,14 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // ---------------------------------------------------------------------------------------------
 template <int D, bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch_main(const BwdLaunch& a, cudaStream_t stream) {
-  using L = BwdSmem<D>;
+  using L = BwdSmem<D, kFeat && D == 64>;
   auto kern = bwd_main_kernel<D, kBf16, kCausal, kFeat>;
   static bool smem_opted_in[64] = {};
   cudaError_t e = opt_in_dynamic_smem(kern, L::kDynamicBytes, smem_opted_in);
   if (e != cudaSuccess) return e;
   const long long nblocks = static_cast<long long>(a.kp.n_kvblk) * a.kp.B * a.kp.Hkv;
   kern<<<static_cast<unsigned>(nblocks), BwdRoles<D>::kThreads, L::kDynamicBytes, stream>>>(
-      a.tmQ, a.tmK, a.tmV, a.tmdO, a.tmdK, a.tmdV, a.delta, a.kp);
+      a.tmQ, a.tmK, a.tmV, a.tmdO, a.tmdK, a.tmdV, a.tmBias, a.tmMask, a.delta, a.kp);
   return cudaGetLastError();
 }
 

@@ -234,6 +234,13 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const float sc = kFeat ? 1.0f : p.scale_log2;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    // dropout keep bits of this row: those of tile j + 1 are drawn after P of tile j has gone out
+    const bool drop_on = kFeat && p.drop.enabled;
+    uint32_t key_lo = 0u, key_hi = 0u;
+    if (drop_on) dropout_key(p.drop, key_lo, key_hi);
+    const uint32_t bh_glob = drop_on ? dropout_bh_index(p.drop, b, h) : 0u;
+    KeepBitsDropout keep{drop_on, make_uint4(0u, 0u, 0u, 0u)};
+    if (drop_on && nt > 0) keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, j0 * kBN);
 
     for (int j = 0; j < nt; ++j) {
       const int buf = j & 1;
@@ -245,9 +252,12 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag)) ok = false;
         tc_fence_after();
       };
-      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j0 + j, j > 0, p, b, h, qi, row_lim, sc, m, l, wait_pv,
-                                         [&](int half) { mbar_arrive(bar_p_full(buf, half)); });
+      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j0 + j, j > 0, p, row_lim, sc, m, l, wait_pv,
+                                         [&](int half) { mbar_arrive(bar_p_full(buf, half)); },
+                                         DirectTerms<kBf16>{p, b, h, qi}, keep);
       if (!ok) break;
+      if (drop_on && j + 1 < nt)
+        keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (j0 + j + 1) * kBN);
     }
 
     if (ok) ok = mbar_wait(bar_q_full, 0, abort_flag);

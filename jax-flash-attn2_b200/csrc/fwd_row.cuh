@@ -66,6 +66,63 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 }
 
 
+// Where the score terms of a row come from. The default reads them straight from global memory; a
+// kernel with shared memory to spare passes a provider that reads pieces staged by the TMA unit.
+template <bool kBf16>
+struct DirectTerms {
+  const FwdKernelParams& p;
+  int b, h, qi;
+  __device__ __forceinline__ void operator()(float (&x)[kBN], int kv0) const {
+    if (qi < p.Sq) {
+      if (p.bias.ptr) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk);
+      if (p.mask.ptr) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk);
+    }
+  }
+};
+// Dropout keep bits of one query row for the 128 keys of one K/V tile: bit c of the result says
+// "keep key kv0 + c". One Philox-4x32-10 call covers eight adjacent keys (counter = (key / 8, query
+// row, batch * heads + head, 0); every 32-bit output word holds two 16-bit draws, the lower key in
+// the low half; keep iff draw >= threshold). The sixteen calls are independent, so the softmax
+// threads draw the bits of their NEXT tile right after handing P of the current one to the MMA
+// warp: the scores' registers are free then, the calls interleave, and the work overlaps the
+// tensor core instead of sitting between S and P.
+__device__ __forceinline__ uint4 draw_row_keep_bits(const DropoutDev& d, uint32_t key_lo, uint32_t key_hi,
+                                                    uint32_t bh_glob, int qi, int kv0) {
+  uint32_t w[4];
+#pragma unroll
+  for (int wd = 0; wd < 4; ++wd) {
+    uint32_t word = 0u;
+#pragma unroll
+    for (int g4 = 0; g4 < 4; ++g4) {
+      uint32_t rnd[4];
+      philox4x32_10(static_cast<uint32_t>(kv0 >> 3) + 4 * wd + g4, static_cast<uint32_t>(qi), bh_glob, 0u,
+                    key_lo, key_hi, rnd);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        word |= ((rnd[k] & 0xffffu) >= d.threshold ? 1u : 0u) << (8 * g4 + 2 * k);
+        word |= ((rnd[k] >> 16) >= d.threshold ? 1u : 0u) << (8 * g4 + 2 * k + 1);
+      }
+    }
+    w[wd] = word;
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Zeroes the dropped weights of one piece (64 keys) of a row from its keep bits.
+struct KeepBitsDropout {
+  bool enabled;
+  uint4 bits;
+  __device__ __forceinline__ void operator()(float (&x)[kBN], int half, int) const {
+    if (!enabled) return;
+    const uint32_t w0 = half == 0 ? bits.x : bits.z, w1 = half == 0 ? bits.y : bits.w;
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      if (!((w0 >> c) & 1u)) x[64 * half + c] = 0.f;
+      if (!((w1 >> c) & 1u)) x[64 * half + 32 + c] = 0.f;
+    }
+  }
+};
+
 // One K/V tile of the online softmax for this thread's row:
 //   S (tensor memory, 128 fp32 columns at tS) -> scores in the log2 domain (+ bias / mask),
 //   causal / padding mask, running maximum with lazy rescaling of O (D columns at tO, only if
@@ -74,12 +131,13 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 // whose P.V MMA may still be running can wait for it there.
 // `after_half(h)` is called after piece h (keys [kPCols h, kPCols (h+1))) of P has been stored and
 // fenced: the caller signals the MMA warp there.
-template <int D, bool kBf16, bool kFeat, class BeforeRescale, class AfterHalf>
+// `terms(x, kv0)` adds log2(e) * (bias + mask) to the scaled scores and `dropout(x, half, kv0)`
+// zeroes the dropped weights of one piece (both only with kFeat; see DirectTerms / KeepBitsDropout).
+template <int D, bool kBf16, bool kFeat, class BeforeRescale, class AfterHalf, class Terms, class Dropout>
 __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j, bool have_o,
-                                                 const FwdKernelParams& p, int b, int h, int qi,
-                                                 int row_lim, float sc, float& m, float& l,
-                                                 BeforeRescale before_o_rescale,
-                                                 AfterHalf after_half) {
+                                                 const FwdKernelParams& p, int row_lim, float sc,
+                                                 float& m, float& l, BeforeRescale before_o_rescale,
+                                                 AfterHalf after_half, Terms terms, Dropout dropout) {
   tc_fence_after();
   float x[kBN];
   {
@@ -93,10 +151,7 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
   if constexpr (kFeat) {
 #pragma unroll
     for (int c = 0; c < kBN; ++c) x[c] *= p.scale_log2;
-    if (qi < p.Sq) {
-      if (p.bias.ptr) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk);
-      if (p.mask.ptr) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk);
-    }
+    terms(x, kv0);
   }
   if (kv0 + kBN - 1 > row_lim) {   // boundary tile for this row: causal edge or key padding
 #pragma unroll
@@ -153,26 +208,7 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
       add2(l0, l1, l0, l1, x[c], x[c + 1]);
       add2(l2, l3, l2, l3, x[c + 2], x[c + 3]);
     }
-    if constexpr (kFeat) {
-      if (p.drop.enabled) {
-        const uint32_t bh_glob = dropout_bh_index(p.drop, b, h);
-        uint32_t key_lo, key_hi;
-        dropout_key(p.drop, key_lo, key_hi);
-        // one Philox call covers eight adjacent keys of this row: each 32-bit output word
-        // holds two 16-bit draws, the lower key in the low half
-#pragma unroll
-        for (int c = half * kPCols; c < (half + 1) * kPCols; c += 8) {
-          uint32_t rnd[4];
-          philox4x32_10(static_cast<uint32_t>((kv0 + c) >> 3), static_cast<uint32_t>(qi),
-                        bh_glob, 0u, key_lo, key_hi, rnd);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if ((rnd[k] & 0xffffu) < p.drop.threshold) x[c + 2 * k] = 0.f;
-            if ((rnd[k] >> 16) < p.drop.threshold) x[c + 2 * k + 1] = 0.f;
-          }
-        }
-      }
-    }
+    if constexpr (kFeat) dropout(x, half, kv0);
     uint32_t pk[kPCols / 2];
 #pragma unroll
     for (int c = 0; c < kPCols / 2; ++c)

@@ -19,6 +19,15 @@
 // core runs the MMAs of the other tile. Across items the roles run ahead of each other: the
 // producer refills a Q tile as soon as its last S MMA has completed and the K/V ring never drains,
 // so the next item's first MMAs overlap the epilogue (O -> shared memory -> TMA store) of this one.
+//
+// Bias, mask and dropout (`kFeat`) are kept off the S -> softmax -> P.V chain of a tile:
+//   * dropout: a softmax thread draws the Philox keep bits of its row for the NEXT K/V tile right
+//     after it has handed P of the current tile to the MMA warp (128 bits in four registers);
+//   * bias / mask at head dim 64, where shared memory has room: every softmax warp streams the
+//     [32 rows x 64 keys] pieces of the tiles it needs through its own ring of three 4 KiB slots;
+//     lane 0 issues the TMA copy of piece n + 3 as soon as the warp has read piece n, so a piece has
+//     most of a tile period to arrive from L2. At head dim 128 the K/V ring leaves no room for
+//     that and the terms are read straight from global memory.
 #include "fwd_launch.cuh"
 #include "fwd_row.cuh"
 #include "launch_util.cuh"
@@ -30,22 +39,29 @@ namespace {
 
 constexpr int kTilesPerCta = 2;
 constexpr int kThreads = 384;
-constexpr int kRegsSoftmax = 208;   // per scheduler: 2 softmax warps + 1 other warp share the 3 * 168 registers of the launch
-constexpr int kRegsOther = 88;
+// per scheduler: 2 softmax warps + 1 other warp share the 3 * 168 registers of the launch; the
+// kernel that stages score terms keeps more state per softmax thread
+template <bool kStaged> constexpr int kRegsSoftmax = kStaged ? 216 : 208;
+template <bool kStaged> constexpr int kRegsOther = kStaged ? 72 : 88;
 
-template <int D>
+template <int D, bool kStaged>
 struct FwdSmem {
   static constexpr int kQTileBytes = kBM * D * 2;
   static constexpr int kKVTileBytes = kBN * D * 2;
-  static constexpr int kStages = (D == 64) ? 8 : 4;
+  static constexpr int kStages = kStaged ? 4 : (D == 64) ? 8 : 4;
   static constexpr int kBlockBytes = kBM * 128;       // one [128 rows][64 elements] block
+  // staged score terms: per softmax warp a ring of [32 rows][64 keys] 16-bit pieces
+  static constexpr int kTermSlots = 3;
+  static constexpr int kTermPieceBytes = 32 * 128;
   static constexpr int kQOff = 0;
   static constexpr int kOOff = kQOff + kTilesPerCta * kQTileBytes;     // O staging: one 64-column block per tile
   static constexpr int kKVOff = kOOff + kTilesPerCta * kBlockBytes;
-  static constexpr int kBarOff = kKVOff + kStages * kKVTileBytes;
+  static constexpr int kTermOff = kKVOff + kStages * kKVTileBytes;
+  static constexpr int kBarOff = kTermOff + (kStaged ? 8 * kTermSlots * kTermPieceBytes : 0);
   // barriers: q_full[2], q_free[2], kv_full[S], kv_empty[S], s_full[2], p_full[2][kPSplit],
-  // o_full[2], o_free[2]
-  static constexpr int kNumBars = 4 + 2 * kStages + 2 + 2 * kPSplit + 4;
+  // o_full[2], o_free[2]; staged: term_full[8 warps][kTermSlots]
+  static constexpr int kNumBarsBase = 4 + 2 * kStages + 2 + 2 * kPSplit + 4;
+  static constexpr int kNumBars = kNumBarsBase + (kStaged ? 8 * kTermSlots : 0);
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamicBytes = kTotal + 1024;  // room to align the base to 1024 B
@@ -108,8 +124,10 @@ template <int D, bool kBf16, bool kCausal, bool kFeat>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO1,
+           const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
            const FwdKernelParams p) {
-  using L = FwdSmem<D>;
+  constexpr bool kStaged = kFeat && D == 64;
+  using L = FwdSmem<D, kStaged>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -126,6 +144,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   auto bar_p_full = [&](int t, int hh) { return bars + 8u * (6 + 2 * L::kStages + kPSplit * t + hh); };
   auto bar_o_full = [&](int t) { return bars + 8u * (6 + 2 * L::kStages + 2 * kPSplit + t); };
   auto bar_o_free = [&](int t) { return bars + 8u * (8 + 2 * L::kStages + 2 * kPSplit + t); };
+  auto bar_term_full = [&](int wi, int s) { return bars + 8u * (L::kNumBarsBase + wi * L::kTermSlots + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kMiscOff + 4);
 
@@ -149,6 +168,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       mbar_init(bar_kv_full(s), 1);
       mbar_init(bar_kv_empty(s), 1);
     }
+    if constexpr (kStaged) {
+      for (int wi = 0; wi < 8; ++wi)
+        for (int s = 0; s < L::kTermSlots; ++s) mbar_init(bar_term_full(wi, s), 1);
+    }
     fence_mbar_init();
   }
   if (warp == 9 && lane == 0) {
@@ -156,6 +179,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
     tma_prefetch_desc(&tmO1);
+    if constexpr (kStaged) {
+      if (p.bias.staged) tma_prefetch_desc(&tmBias);
+      if (p.mask.staged) tma_prefetch_desc(&tmMask);
+    }
   }
   if (warp == 0) {
     __syncwarp();
@@ -169,7 +196,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   if (warp >= 8) {
     // One warpgroup, one instruction: all four warps release their registers here.
-    setmaxnreg_dec<kRegsOther>();
+    setmaxnreg_dec<kRegsOther<kStaged>>();
   }
   if (warp >= 10) {
     // idle
@@ -314,7 +341,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     __syncwarp();
   } else if (warp < 8) {
     // =========================== softmax + epilogue ==========================================
-    setmaxnreg_inc<kRegsSoftmax>();
+    setmaxnreg_inc<kRegsSoftmax<kStaged>>();
     const int t = warp >> 2;                   // query tile of this warpgroup
     const int r = tid & (kBM - 1);             // row inside the tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -324,6 +351,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     uint32_t it_cnt = 0;       // tile-iterations so far: phase of s_full / p_full
     uint32_t o_cnt = 0;        // items so far: phase of o_full
     bool ok = true;
+    // staged terms: pieces this warp has loaded so far (slot and phase of its ring)
+    uint32_t term_cnt = 0;
+    const int n_staged = kStaged ? (p.bias.staged ? 1 : 0) + (p.mask.staged ? 1 : 0) : 0;
+    const int per_tile = 2 * n_staged;   // pieces per K/V tile: two halves of 64 keys per term
+    // dropout: Philox key of the call
+    uint32_t key_lo = 0u, key_hi = 0u;
+    const bool drop_on = kFeat && p.drop.enabled;
+    if (drop_on) dropout_key(p.drop, key_lo, key_hi);
 
     for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
       FwdItem it;
@@ -339,11 +374,86 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       float m = -INFINITY;   // running (possibly stale) row maximum, in the units of x[]
       float l = 0.f;         // running row sum of exp2(x*sc - m*sc)
 
-      for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
-        ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
-        if (!ok) break;
-        softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, b, h, qi, row_lim, sc, m, l, [] {},
-                                          [&](int hh) { mbar_arrive(bar_p_full(t, hh)); });
+      // keep bits of this row for the tile about to be processed; those of tile j + 1 are drawn
+      // after P of tile j has been handed over
+      KeepBitsDropout keep{drop_on, make_uint4(0u, 0u, 0u, 0u)};
+      const uint32_t bh_glob = drop_on ? dropout_bh_index(p.drop, b, h) : 0u;
+      if (drop_on && nt > 0) keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, it.j0 * kBN);
+
+      if constexpr (kStaged) {
+        // ---- this warp's stream of term pieces for the item: piece n = (K/V tile n / per_tile,
+        // term (n % per_tile) / 2, half n % 2); lane 0 keeps kTermSlots copies in flight
+        const int wi = warp;                       // 0..7
+        const int n_pieces = nt * per_tile;
+        const uint32_t term_smem = smem_base + L::kTermOff + wi * (L::kTermSlots * L::kTermPieceBytes);
+        const int row0 = it.q0 + t * kBM + 32 * (warp & 3);   // first query row of this warp
+        auto issue_piece = [&](int n, uint32_t cnt) {          // lane 0 only
+          const int jj = n / per_tile, rr = n - jj * per_tile;
+          const bool second = (rr >> 1) == 1 || !p.bias.staged;   // which of the staged terms
+          const ScoreTermDev& tt = second ? p.mask : p.bias;
+          const int slot = cnt % L::kTermSlots;
+          mbar_arrive_expect_tx(bar_term_full(wi, slot), L::kTermPieceBytes);
+          tma_load_4d(term_smem + slot * L::kTermPieceBytes, second ? &tmMask : &tmBias,
+                      bar_term_full(wi, slot), (it.j0 + jj) * kBN + 64 * (rr & 1), row0,
+                      tt.sh ? h / tt.head_div : 0, tt.sb ? b : 0);
+        };
+        if (lane == 0 && ok)
+          for (int n = 0; n < n_pieces && n < L::kTermSlots; ++n) issue_piece(n, term_cnt + n);
+        int piece = 0;                             // next piece this warp reads
+
+        auto terms = [&](float (&x)[kBN], int kv0) {
+#pragma unroll 1
+          for (int tt = 0; tt < n_staged; ++tt) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half, ++piece, ++term_cnt) {
+              const int slot = term_cnt % L::kTermSlots;
+              if (ok) ok = mbar_wait(bar_term_full(wi, slot), (term_cnt / L::kTermSlots) & 1u, abort_flag);
+              if (ok) {
+                // this lane's row of the piece: 64 keys = 8 chunks of 16 bytes, 128-byte swizzle
+                const uint32_t line = term_smem + slot * L::kTermPieceBytes + lane * 128;
+#pragma unroll
+                for (int c8 = 0; c8 < 8; ++c8) {
+                  const uint4 v = lds128(line + ((c8 ^ (lane & 7)) << 4));
+                  const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    float& x0 = x[64 * half + 8 * c8 + 2 * e];
+                    float& x1 = x[64 * half + 8 * c8 + 2 * e + 1];
+                    fma2(x0, x1, unpack_lo<kBf16>(wv[e]), unpack_hi<kBf16>(wv[e]), kLog2e, kLog2e, x0, x1);
+                  }
+                }
+              }
+              __syncwarp();
+              if (lane == 0 && ok && piece + L::kTermSlots < n_pieces) {
+                fence_proxy_async_smem();          // the warp's reads of the slot precede the copy
+                issue_piece(piece + L::kTermSlots, term_cnt + L::kTermSlots);
+              }
+            }
+          }
+          // terms that cannot be staged (fp32, a key-padding row, unaligned) are read directly
+          if (qi < p.Sq) {
+            if (p.bias.ptr && !p.bias.staged) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk);
+            if (p.mask.ptr && !p.mask.staged) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk);
+          }
+        };
+        for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
+          ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
+          if (!ok) break;
+          softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, m, l, [] {},
+                                            [&](int hh) { mbar_arrive(bar_p_full(t, hh)); }, terms, keep);
+          if (drop_on && j + 1 < nt)
+            keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (it.j0 + j + 1) * kBN);
+        }
+      } else {
+        for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
+          ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
+          if (!ok) break;
+          softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, m, l, [] {},
+                                            [&](int hh) { mbar_arrive(bar_p_full(t, hh)); },
+                                            DirectTerms<kBf16>{p, b, h, qi}, keep);
+          if (drop_on && j + 1 < nt)
+            keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (it.j0 + j + 1) * kBN);
+        }
       }
 
       // ---- epilogue: O / l -> 16 bit -> swizzled shared memory -> TMA store; LSE -------------
@@ -404,7 +514,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 // ---------------------------------------------------------------------------------------------
 template <int D, bool kBf16, bool kCausal, bool kFeat>
 static cudaError_t launch_one(const FwdLaunch& a, cudaStream_t stream) {
-  using L = FwdSmem<D>;
+  using L = FwdSmem<D, kFeat && D == 64>;
   auto kern = fwd_kernel<D, kBf16, kCausal, kFeat>;
   static bool smem_opted_in[64] = {};
   cudaError_t e = opt_in_dynamic_smem(kern, L::kDynamicBytes, smem_opted_in);
@@ -412,7 +522,7 @@ static cudaError_t launch_one(const FwdLaunch& a, cudaStream_t stream) {
   const long long items = static_cast<long long>(a.kp.n_qblk) * a.kp.B * a.kp.Hq * a.kp.n_splits;
   if (items <= 0) return cudaSuccess;
   const unsigned grid = static_cast<unsigned>(items < sm_count() ? items : sm_count());
-  kern<<<grid, kThreads, L::kDynamicBytes, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmO1, a.kp);
+  kern<<<grid, kThreads, L::kDynamicBytes, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmO1, a.tmBias, a.tmMask, a.kp);
   return cudaGetLastError();
 }
 
@@ -432,6 +542,7 @@ static cudaError_t launch_d(const FwdLaunch& a, cudaStream_t stream) {
 }
 
 cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream) {
+  if (a.pair) return launch_fwd_pair(a, stream);
   switch (a.head_dim) {
     case 64: return launch_d<64>(a, stream);
     case 128: return launch_d<128>(a, stream);

@@ -11,6 +11,8 @@ struct ScoreTermDev {
   int is_f32;           // 1: float32 elements, 0: the 16-bit dtype of q
   int vec_ok;           // 1: rows can be read with 16-byte loads (pointer and strides aligned)
   int head_div;         // >= 1: query head h reads head h / head_div of the term
+  int staged;           // 1: the kernel reads this term through its tensor map (TMA-staged tiles in
+                        // shared memory) instead of with loads from ptr
 };
 
 // Gradient of the bias: float32 [batch, heads, Sq, Sk], added into with atomics (several batch

@@ -303,6 +303,41 @@ def test_seeded_random_shapes(case):
              p={"drop": 0.15, "all": 0.1}.get(feat, 0.0))
 
 
+@pytest.mark.parametrize("shape,dtype,causal", [
+    ((1, 256, 256, 2, 1), torch.bfloat16, True),       # one pair item
+    ((3, 700, 700, 8, 2), torch.float16, True),        # ragged rows, several groups
+    ((2, 300, 513, 4, 2), torch.bfloat16, False),      # Sq != Sk, ragged keys
+    ((1, 640, 64, 6, 1), torch.bfloat16, True),        # more query rows than keys: tiles without work
+    ((2, 2048, 2048, 16, 4), torch.bfloat16, True),    # 128 pair items: more than CTA pairs on the GPU
+    ((1, 1024, 1024, 2, 2), torch.float16, True),      # one head per group: the single-CTA kernel
+])
+def test_head_dim_128_forward_on_cta_pairs(shape, dtype, causal):
+    """Head dim 128 without score terms and an even number of query heads per key/value head runs
+    two heads of a group on a pair of CTAs (2-CTA MMAs, each CTA loading half of every K / V tile).
+    Every row of both heads, and the backward fed with its output, must match the oracle."""
+    B, Sq, Sk, Hq, Hkv = shape
+    run_case(B, Sq, Sk, Hq, Hkv, 128, dtype, causal, scale=128 ** -0.25)
+
+
+def test_cta_pair_forward_with_per_batch_lengths():
+    J = _J()
+    B, S, Hq, Hkv, D, dtype = 3, 512, 4, 2, 128, torch.bfloat16
+    lengths = [512, 130, 0]
+    q, k, v, _ = W.make_qkv(B, S, S, Hq, Hkv, D, dtype, D ** -0.25)
+    seqlens = torch.tensor(lengths, dtype=torch.int32).cuda()
+    out, lse = J.fwd_attention_kernel_call(q.cuda(), k.cuda(), v.cuda(), None, None, None, 0.0, True, None,
+                                           seqlens=seqlens)
+    assert J.device_status() == 0
+    out, lse = out.cpu(), lse.cpu()
+    blk = BlockAttention()
+    for b, n in enumerate(lengths):
+        assert torch.all(out[b, n:] == 0) and torch.all(lse[b, :, n:S] == float("-inf"))
+        if n:
+            ro, rl = blk.forward(q[b:b + 1, :n], k[b:b + 1, :n], v[b:b + 1, :n], causal=True)
+            assert (out[b:b + 1, :n].float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
+            assert (lse[b:b + 1, :, :n] - rl).abs().max().item() <= LSE_TOL
+
+
 @pytest.mark.parametrize("G", [1, 2, 4, 8])
 def test_gqa_groups(G):
     run_case(1, 256, 256, 8, 8 // G, 64, torch.float16, True)
