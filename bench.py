@@ -166,11 +166,29 @@ def cpu_sample(workload, seconds_budget=20.0):
     return unit_flops * units / dt / 1e12, units, dt, torch.get_num_threads(), (Sq_s, Sk_s, G)
 
 
+def make_config(workload_name, workload, world, batch_override=0):
+    """The `config` record of the JSON line: the same for the product arm and the reference arm."""
+    B, Sq, Sk, Hq, Hkv, D, dtype, causal, _ = workload
+    per_step = 2 * (2 * B * Sq * Hq * D + 2 * B * Sk * Hkv * D)      # q, dO, k, v in 16 bit
+    return {
+        "workload": workload_name + (f" (batch {batch_override})" if batch_override > 0 else ""),
+        "shape_per_gpu": f"B={B} Sq={Sq} Sk={Sk} Hq={Hq} Hkv={Hkv} D={D} causal={causal}",
+        "global_batch": B * world,
+        "parallelism": f"{world} x independent (batch, kv-head) shards, no collective",
+        "extras": WORKLOAD_EXTRAS.get(workload_name, {}),
+        "l2": f"inputs ({per_step // (1 << 20)} MiB per step) vs the 126 MB L2; no explicit flush",
+        "flops": "fwd 4*B*Hq*Sq*Sk*D (x0.5 causal), bwd 2.5x fwd",
+    }
+
+
 def run_reference(args, workload_name):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     wl = WORKLOADS[workload_name]
+    if args.batch > 0:
+        wl = (args.batch,) + wl[1:]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     B, Sq, Sk, Hq, Hkv, D, dtype, causal, _ = wl
     torch.set_num_threads(os.cpu_count() or 1)
     budget = max(2.0, 20.0 / max(1, args.steps + args.warmup))
@@ -189,7 +207,7 @@ def run_reference(args, workload_name):
         "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": statistics.mean(ms), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 (cpu)", "data": "synthetic",
-        "config": {"workload": workload_name, "shape": f"B={B} Sq={Sq} Sk={Sk} Hq={Hq} Hkv={Hkv} D={D} causal={causal}"},
+        "config": make_config(workload_name, wl, world, args.batch),
         "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample_desc},
         "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -555,15 +573,7 @@ def main():
         "vs_baseline": None,
         "dtype": "bf16" if dtype == torch.bfloat16 else "fp16",
         "data": "synthetic",
-        "config": {
-            "workload": args.workload + (f" (batch {args.batch})" if args.batch > 0 else ""),
-            "shape_per_gpu": f"B={B} Sq={Sq} Sk={Sk} Hq={Hq} Hkv={Hkv} D={D} causal={causal}",
-            "global_batch": B * world,
-            "parallelism": f"{world} x independent (batch, kv-head) shards, no collective",
-            "extras": extras,
-            "l2": f"inputs ({(h2d) // (1 << 20)} MiB per step) vs the 126 MB L2; no explicit flush",
-            "flops": "fwd 4*B*Hq*Sq*Sk*D (x0.5 causal), bwd 2.5x fwd",
-        },
+        "config": make_config(args.workload, workload, world, args.batch),
         "per_gpu": {
             "fwd_bwd_tflops": value / world,
             "fwd_tflops": fwd_tflops / world,

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_PATH = os.path.join(HERE, "libfa2_b200.so")
-SOURCES = ["api.cu", "fwd_sm100.cu", "fwd_pair_sm100.cu", "fwd256_sm100.cu", "fwd_combine.cu", "bwd_sm100.cu", "bwd256_sm100.cu"]
+SOURCES = ["api.cu", "fwd_sm100.cu", "fwd256_sm100.cu", "fwd_combine.cu", "bwd_sm100.cu", "bwd256_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -11,7 +11,6 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -290,16 +289,6 @@ SplitPlan plan_splits(const fa2_problem& p, const HeadDim& hd, bool pack_heads) 
   return s;
 }
 
-// FA2_B200_DISABLE_PAIR_MMA=1 in the environment keeps the forward on the single-CTA kernel where
-// the CTA-pair kernel would be chosen (same results; for comparing the two and as a fallback).
-bool pair_mma_disabled() {
-  static const bool off = [] {
-    const char* v = std::getenv("FA2_B200_DISABLE_PAIR_MMA");
-    return v != nullptr && v[0] != '\0' && v[0] != '0';
-  }();
-  return off;
-}
-
 bool can_pack_heads(const fa2_problem& p) {
   const int group = p.heads_kv > 0 ? p.heads_q / p.heads_kv : 0;
   return p.seqlen_q == 1 && group > 1 && group <= 128 && !(p.dropout_p > 0.f);
@@ -438,14 +427,6 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
     // the head-dim-64 kernel streams 16-bit bias / mask tiles through shared memory
     try_stage_term(&L.tmBias, &kp.bias, p, 32);
     try_stage_term(&L.tmMask, &kp.mask, p, 32);
-  }
-  // Head dim 128 without score terms, an even number of query heads per key/value head, no
-  // key split: two heads of a group share every K/V tile on a pair of CTAs (2-CTA MMAs).
-  L.pair = D == 128 && !L.feat && !split && !pack_heads && (kp.G % 2 == 0) && !pair_mma_disabled();
-  if (L.pair) {
-    if ((rc = make_tmap(&L.tmKh, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 64, "k")) ||
-        (rc = make_tmap(&L.tmVh, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides, 128, "v", 1)))
-      return rc;
   }
 
   cudaError_t e = launch_fwd(L, static_cast<cudaStream_t>(cuda_stream));

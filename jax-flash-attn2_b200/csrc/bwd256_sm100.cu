@@ -447,6 +447,21 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
 
+    // Dropout keep bits of this key row for the step's 32 query columns, drawn one step ahead (after
+    // dS of the previous step has been handed over) so that the Philox rounds overlap the MMAs.
+    uint32_t keep_bits[1] = {0xffffffffu};
+    auto draw_keep = [&](int step) {
+      if constexpr (kFeat) {
+        if (p.drop.enabled && step < T) {
+          int hh, ii;
+          step_coords(step, hh, ii);
+          dropout_keep_bits_transposed<32>(p.drop, dropout_bh_index(p.drop, b, hh), kv, ii * kBQ + 32 * w, lane,
+                                           keep_bits);
+        }
+      }
+    };
+    draw_keep(0);
+
     for (int it = 0; it < T && ok; ++it) {
       const int stg = it & 1;
       int h, i;
@@ -463,20 +478,11 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int q_lim = kv >= sk_b ? 0x7fffffff : (kCausal ? kv - p.causal_off : -0x7fffffff - 1);
 
       uint32_t pk[16];
-      uint32_t keep = 0xffffffffu;
+      const uint32_t keep = keep_bits[0];
       {
         uint32_t s[32];
         tmem_ld32(tS, s);
         tc_wait_ld();
-        if constexpr (kFeat) {
-          if (p.drop.enabled) {
-            const uint32_t bh_glob =
-                dropout_bh_index(p.drop, b, h);
-            uint32_t bits[1];
-            dropout_keep_bits_transposed<32>(p.drop, bh_glob, kv, q_first, lane, bits);
-            keep = bits[0];
-          }
-        }
         if constexpr (kFeat) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) s[c] = __float_as_uint(__uint_as_float(s[c]) * p.scale_log2);
@@ -567,6 +573,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             add_bias_grad<kBf16, 32>(p.dbias, b, h, q_first, kv, p.Sq, p.Sk, dp, do_scale);
         }
       }
+      draw_keep(it + 1);
     }
 
     // ---- epilogue: warpgroup 0 writes dK[:, half] (scaled), warpgroup 1 writes dV[:, half] ----

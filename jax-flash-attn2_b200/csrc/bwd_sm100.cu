@@ -521,6 +521,24 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
 
+    // Dropout keep bits of this key row for the step's kCW query columns. They are drawn one step
+    // ahead, after dS of the previous step has been handed over, so that the Philox rounds overlap
+    // the MMAs instead of sitting between S^T and P^T.
+    uint32_t keep[kCW / 32];
+#pragma unroll
+    for (int k = 0; k < kCW / 32; ++k) keep[k] = 0xffffffffu;
+    auto draw_keep = [&](int step) {
+      if constexpr (kFeat) {
+        if (p.drop.enabled && step < T) {
+          int hh, ii;
+          step_coords(step, hh, ii);
+          dropout_keep_bits_transposed<kCW>(p.drop, dropout_bh_index(p.drop, b, hh), kv, ii * kBM + kCW * w,
+                                            lane, keep);
+        }
+      }
+    };
+    draw_keep(0);
+
     for (int it = 0; it < T && ok; ++it) {
       const int st = it & 1;
       int h, i;
@@ -540,22 +558,12 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
       // ---- P^T = exp2(S^T * scale*log2e - lse*log2e): kCW query columns of this key row ------
       uint32_t pk[kCW / 2];                     // P as 16-bit pairs; also the input of dS below
-      uint32_t keep[kCW / 32];
-#pragma unroll
-      for (int k = 0; k < kCW / 32; ++k) keep[k] = 0xffffffffu;
       {
         uint32_t s[kCW];
 #pragma unroll
         for (int c = 0; c < kCW / 32; ++c)
           tmem_ld32(tS + 32 * c, reinterpret_cast<uint32_t(&)[32]>(s[32 * c]));
         tc_wait_ld();
-        if constexpr (kFeat) {
-          if (p.drop.enabled) {
-            const uint32_t bh_glob =
-                dropout_bh_index(p.drop, b, h);
-            dropout_keep_bits_transposed<kCW>(p.drop, bh_glob, kv, q_first, lane, keep);
-          }
-        }
         if constexpr (kFeat) {
 #pragma unroll
           for (int c = 0; c < kCW; ++c) s[c] = __float_as_uint(__uint_as_float(s[c]) * p.scale_log2);
@@ -677,6 +685,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             add_bias_grad<kBf16, kCW>(p.dbias, b, h, q_first, kv, p.Sq, p.Sk, dp, do_scale);
         }
       }
+      draw_keep(it + 1);
     }
 
     // ---- epilogue: the first half of the warpgroups writes dK (scaled), the second half dV ----

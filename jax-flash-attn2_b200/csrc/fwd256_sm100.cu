@@ -231,7 +231,9 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tO = tmem_base + lane_base + kColO;
     const int row_lim = qi < sq_b ? (kCausal ? min(sk_b - 1, qi + p.causal_off) : sk_b - 1) : -1;
-    const float sc = kFeat ? 1.0f : p.scale_log2;
+    const FeatScale fs(p.scale_log2);
+    const float sc = kFeat ? fs.sc : p.scale_log2;
+    const bool prescale = kFeat && fs.prescale;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     // dropout keep bits of this row: those of tile j + 1 are drawn after P of tile j has gone out
@@ -252,9 +254,9 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         if (!mbar_wait(bar_pv_done, (j - 1) & 1, abort_flag)) ok = false;
         tc_fence_after();
       };
-      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j0 + j, j > 0, p, row_lim, sc, m, l, wait_pv,
+      softmax_tile_row<kD, kBf16, kFeat>(tS, tO, j0 + j, j > 0, p, row_lim, sc, prescale, m, l, wait_pv,
                                          [&](int half) { mbar_arrive(bar_p_full(buf, half)); },
-                                         DirectTerms<kBf16>{p, b, h, qi}, keep);
+                                         DirectTerms<kBf16>{p, b, h, qi, fs.coef}, keep);
       if (!ok) break;
       if (drop_on && j + 1 < nt)
         keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (j0 + j + 1) * kBN);

@@ -18,10 +18,6 @@ struct FwdLaunch {
   // bias / mask as 4-D tensors (Sk, Sq, heads, batch) with a box of 64 keys x 32 query rows: used
   // by the kernels that stage these terms in shared memory (kp.bias.staged / kp.mask.staged)
   CUtensorMap tmBias, tmMask;
-  // head dim 128 on CTA pairs: K with a box of 64 keys (both 64-dim blocks), V with a box of all
-  // 128 keys and one 64-dim block: the halves one CTA of a pair loads
-  CUtensorMap tmKh, tmVh;
-  bool pair;          // run the CTA-pair kernel (fwd_pair_sm100.cu)
   FwdKernelParams kp;
   int head_dim;
   bool bf16, causal, feat;
@@ -44,9 +40,6 @@ cudaError_t launch_fwd_combine(const FwdCombine& c, cudaStream_t stream);
 
 // Launches the forward kernel specialised for (head_dim, dtype, causal, score terms/dropout).
 cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream);
-
-// Head dim 128, plain, even group size: two query heads of a group on a CTA pair with 2-CTA MMAs.
-cudaError_t launch_fwd_pair(const FwdLaunch& a, cudaStream_t stream);
 
 // Head dim 256 variant (one query tile per CTA, two S buffers); called by launch_fwd.
 cudaError_t launch_fwd256(const FwdLaunch& a, cudaStream_t stream);

@@ -21,7 +21,7 @@ constexpr int kPCols = kBN / kPSplit;   // keys per piece
 
 template <bool kBf16>
 __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermDev& t, int b,
-                                               int h, int qi, int kv0, int Sk) {
+                                               int h, int qi, int kv0, int Sk, float coef) {
   const long long base = static_cast<long long>(b) * t.sb + static_cast<long long>(h / t.head_div) * t.sh +
                          static_cast<long long>(qi) * t.sq + kv0;
   const bool full = (kv0 + kBN <= Sk);
@@ -31,15 +31,15 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 #pragma unroll
       for (int c4 = 0; c4 < kBN / 4; ++c4) {
         const float4 v = __ldg(reinterpret_cast<const float4*>(p) + c4);
-        x[4 * c4 + 0] = fmaf(v.x, kLog2e, x[4 * c4 + 0]);
-        x[4 * c4 + 1] = fmaf(v.y, kLog2e, x[4 * c4 + 1]);
-        x[4 * c4 + 2] = fmaf(v.z, kLog2e, x[4 * c4 + 2]);
-        x[4 * c4 + 3] = fmaf(v.w, kLog2e, x[4 * c4 + 3]);
+        x[4 * c4 + 0] = fmaf(v.x, coef, x[4 * c4 + 0]);
+        x[4 * c4 + 1] = fmaf(v.y, coef, x[4 * c4 + 1]);
+        x[4 * c4 + 2] = fmaf(v.z, coef, x[4 * c4 + 2]);
+        x[4 * c4 + 3] = fmaf(v.w, coef, x[4 * c4 + 3]);
       }
     } else {
 #pragma unroll
       for (int c = 0; c < kBN; ++c)
-        if (kv0 + c < Sk) x[c] = fmaf(__ldg(p + c), kLog2e, x[c]);
+        if (kv0 + c < Sk) x[c] = fmaf(__ldg(p + c), coef, x[c]);
     }
   } else {
     const uint16_t* p = static_cast<const uint16_t*>(t.ptr) + base;
@@ -51,16 +51,16 @@ __device__ __forceinline__ void add_score_term(float (&x)[kBN], const ScoreTermD
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           x[8 * c8 + 2 * k + 0] =
-              fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(w[k] & 0xffff)), kLog2e,
+              fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(w[k] & 0xffff)), coef,
                    x[8 * c8 + 2 * k + 0]);
           x[8 * c8 + 2 * k + 1] = fmaf(to_float16bit<kBf16>(static_cast<uint16_t>(w[k] >> 16)),
-                                       kLog2e, x[8 * c8 + 2 * k + 1]);
+                                       coef, x[8 * c8 + 2 * k + 1]);
         }
       }
     } else {
 #pragma unroll
       for (int c = 0; c < kBN; ++c)
-        if (kv0 + c < Sk) x[c] = fmaf(to_float16bit<kBf16>(__ldg(p + c)), kLog2e, x[c]);
+        if (kv0 + c < Sk) x[c] = fmaf(to_float16bit<kBf16>(__ldg(p + c)), coef, x[c]);
     }
   }
 }
@@ -72,22 +72,43 @@ template <bool kBf16>
 struct DirectTerms {
   const FwdKernelParams& p;
   int b, h, qi;
+  float coef;   // what a term is multiplied with before it is added (see FeatScale)
   __device__ __forceinline__ void operator()(float (&x)[kBN], int kv0) const {
     if (qi < p.Sq) {
-      if (p.bias.ptr) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk);
-      if (p.mask.ptr) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk);
+      if (p.bias.ptr) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk, coef);
+      if (p.mask.ptr) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk, coef);
     }
   }
 };
-// Dropout keep bits of one query row for the 128 keys of one K/V tile: bit c of the result says
-// "keep key kv0 + c". One Philox-4x32-10 call covers eight adjacent keys (counter = (key / 8, query
-// row, batch * heads + head, 0); every 32-bit output word holds two 16-bit draws, the lower key in
-// the low half; keep iff draw >= threshold). The sixteen calls are independent, so the softmax
-// threads draw the bits of their NEXT tile right after handing P of the current one to the MMA
-// warp: the scores' registers are free then, the calls interleave, and the work overlaps the
-// tensor core instead of sitting between S and P.
+
+// Units of the score registers x[] in the kernels with score terms. The softmax computes
+// exp2(x * sc - m * sc). With a positive softmax scale x holds the raw dot products, sc is
+// scale * log2(e) as in the plain kernels, and a term enters as term / scale (coef = 1 / scale), so
+// that no separate scaling pass over the 128 scores is needed. A zero or negative scale cannot be
+// factored out of the row maximum: then x is first multiplied by scale * log2(e) (`prescale`),
+// sc is 1 and a term enters as term * log2(e).
+struct FeatScale {
+  float sc, coef;
+  bool prescale;
+  __device__ __forceinline__ explicit FeatScale(float scale_log2) {
+    prescale = !(scale_log2 > 0.f);
+    sc = prescale ? 1.f : scale_log2;
+    coef = prescale ? kLog2e : kLog2e / scale_log2;
+  }
+};
+// Dropout keep bits of one query row for the 128 keys of one K/V tile. One Philox-4x32-10 call
+// covers eight adjacent keys (counter = (key / 8, query row, batch * heads + head, 0); every 32-bit
+// output word holds two 16-bit draws, the lower key in the low half; keep iff draw >= threshold).
+// The sixteen calls are independent, so the softmax threads draw the bits of their NEXT tile right
+// after handing P of the current one to the MMA warp: the scores' registers are free then, the
+// calls interleave, and the work overlaps the tensor core instead of sitting between S and P.
+// Layout of the result: word w covers keys [32 w, 32 w + 32) as sixteen pairs; bit p holds the flag
+// of the even key 32 w + 2 p, bit 16 + p that of the odd key 32 w + 2 p + 1 (the two halves of the
+// 16-bit pair P is packed into), which is what KeepBitsDropout needs to mask a pair in three
+// integer instructions.
 __device__ __forceinline__ uint4 draw_row_keep_bits(const DropoutDev& d, uint32_t key_lo, uint32_t key_hi,
                                                     uint32_t bh_glob, int qi, int kv0) {
+  const uint32_t thr_hi = d.threshold << 16;    // draw in the high half >= threshold
   uint32_t w[4];
 #pragma unroll
   for (int wd = 0; wd < 4; ++wd) {
@@ -99,8 +120,8 @@ __device__ __forceinline__ uint4 draw_row_keep_bits(const DropoutDev& d, uint32_
                     key_lo, key_hi, rnd);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        word |= ((rnd[k] & 0xffffu) >= d.threshold ? 1u : 0u) << (8 * g4 + 2 * k);
-        word |= ((rnd[k] >> 16) >= d.threshold ? 1u : 0u) << (8 * g4 + 2 * k + 1);
+        if ((rnd[k] & 0xffffu) >= d.threshold) word |= 1u << (4 * g4 + k);
+        if (rnd[k] >= thr_hi) word |= 1u << (16 + 4 * g4 + k);
       }
     }
     w[wd] = word;
@@ -108,17 +129,22 @@ __device__ __forceinline__ uint4 draw_row_keep_bits(const DropoutDev& d, uint32_
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Zeroes the dropped weights of one piece (64 keys) of a row from its keep bits.
+// Zeroes the dropped weights of one piece (64 keys) of a row: `pk` holds the piece's P as 32 words
+// of two 16-bit values (even key in the low half). Per pair: shift the pair's two flags to the
+// sign bits of bytes 1 and 3, let a byte permute replicate them over the two halves, and mask.
 struct KeepBitsDropout {
   bool enabled;
   uint4 bits;
-  __device__ __forceinline__ void operator()(float (&x)[kBN], int half, int) const {
+  __device__ __forceinline__ void operator()(uint32_t (&pk)[kBN / 4], int half) const {
     if (!enabled) return;
     const uint32_t w0 = half == 0 ? bits.x : bits.z, w1 = half == 0 ? bits.y : bits.w;
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      if (!((w0 >> c) & 1u)) x[64 * half + c] = 0.f;
-      if (!((w1 >> c) & 1u)) x[64 * half + 32 + c] = 0.f;
+    for (int pr = 0; pr < 16; ++pr) {
+      uint32_t m0, m1;
+      asm("prmt.b32 %0, %1, %1, 0xBB99;" : "=r"(m0) : "r"(w0 << (15 - pr)));
+      asm("prmt.b32 %0, %1, %1, 0xBB99;" : "=r"(m1) : "r"(w1 << (15 - pr)));
+      pk[pr] &= m0;
+      pk[16 + pr] &= m1;
     }
   }
 };
@@ -131,13 +157,15 @@ struct KeepBitsDropout {
 // whose P.V MMA may still be running can wait for it there.
 // `after_half(h)` is called after piece h (keys [kPCols h, kPCols (h+1))) of P has been stored and
 // fenced: the caller signals the MMA warp there.
-// `terms(x, kv0)` adds log2(e) * (bias + mask) to the scaled scores and `dropout(x, half, kv0)`
-// zeroes the dropped weights of one piece (both only with kFeat; see DirectTerms / KeepBitsDropout).
+// `terms(x, kv0)` adds coef * (bias + mask) to the scores (see FeatScale) and `dropout(pk, half)`
+// zeroes the dropped weights of one packed piece (both only with kFeat; see DirectTerms /
+// KeepBitsDropout).
 template <int D, bool kBf16, bool kFeat, class BeforeRescale, class AfterHalf, class Terms, class Dropout>
 __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j, bool have_o,
                                                  const FwdKernelParams& p, int row_lim, float sc,
-                                                 float& m, float& l, BeforeRescale before_o_rescale,
-                                                 AfterHalf after_half, Terms terms, Dropout dropout) {
+                                                 bool prescale, float& m, float& l,
+                                                 BeforeRescale before_o_rescale, AfterHalf after_half,
+                                                 Terms terms, Dropout dropout) {
   tc_fence_after();
   float x[kBN];
   {
@@ -149,8 +177,10 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
   }
   const int kv0 = j * kBN;
   if constexpr (kFeat) {
+    if (prescale) {
 #pragma unroll
-    for (int c = 0; c < kBN; ++c) x[c] *= p.scale_log2;
+      for (int c = 0; c < kBN; ++c) x[c] *= p.scale_log2;
+    }
     terms(x, kv0);
   }
   if (kv0 + kBN - 1 > row_lim) {   // boundary tile for this row: causal edge or key padding
@@ -208,11 +238,11 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
       add2(l0, l1, l0, l1, x[c], x[c + 1]);
       add2(l2, l3, l2, l3, x[c + 2], x[c + 3]);
     }
-    if constexpr (kFeat) dropout(x, half, kv0);
     uint32_t pk[kPCols / 2];
 #pragma unroll
     for (int c = 0; c < kPCols / 2; ++c)
       pk[c] = pack2<kBf16>(x[half * kPCols + 2 * c], x[half * kPCols + 2 * c + 1]);
+    if constexpr (kFeat) dropout(pk, half);
     static_assert(kPCols == 64, "one 32-column store per piece");
     tmem_st32(tS + 32 * half, reinterpret_cast<const uint32_t(&)[32]>(pk[0]));
     tc_wait_st();

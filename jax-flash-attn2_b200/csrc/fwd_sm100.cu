@@ -39,9 +39,8 @@ namespace {
 
 constexpr int kTilesPerCta = 2;
 constexpr int kThreads = 384;
-// per scheduler: 2 softmax warps + 1 other warp share the 3 * 168 registers of the launch; the
-// kernel that stages score terms keeps more state per softmax thread
-template <bool kStaged> constexpr int kRegsSoftmax = kStaged ? 216 : 208;
+// per scheduler: 2 softmax warps + 1 other warp share the 3 * 168 registers of the launch
+template <bool kStaged> constexpr int kRegsSoftmax = kStaged ? 216 : 208;   // staged score terms keep more state per softmax thread
 template <bool kStaged> constexpr int kRegsOther = kStaged ? 72 : 88;
 
 template <int D, bool kStaged>
@@ -347,7 +346,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + kColS + t * kBN;
     const uint32_t tO = tmem_base + lane_base + kColO + t * D;
-    const float sc = kFeat ? 1.0f : p.scale_log2;   // multiplies the values held in x[]
+    const FeatScale fs(p.scale_log2);
+    const float sc = kFeat ? fs.sc : p.scale_log2;   // multiplies the values held in x[]
+    const bool prescale = kFeat && fs.prescale;
     uint32_t it_cnt = 0;       // tile-iterations so far: phase of s_full / p_full
     uint32_t o_cnt = 0;        // items so far: phase of o_full
     bool ok = true;
@@ -419,7 +420,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                   for (int e = 0; e < 4; ++e) {
                     float& x0 = x[64 * half + 8 * c8 + 2 * e];
                     float& x1 = x[64 * half + 8 * c8 + 2 * e + 1];
-                    fma2(x0, x1, unpack_lo<kBf16>(wv[e]), unpack_hi<kBf16>(wv[e]), kLog2e, kLog2e, x0, x1);
+                    fma2(x0, x1, unpack_lo<kBf16>(wv[e]), unpack_hi<kBf16>(wv[e]), fs.coef, fs.coef, x0, x1);
                   }
                 }
               }
@@ -432,14 +433,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           }
           // terms that cannot be staged (fp32, a key-padding row, unaligned) are read directly
           if (qi < p.Sq) {
-            if (p.bias.ptr && !p.bias.staged) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk);
-            if (p.mask.ptr && !p.mask.staged) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk);
+            if (p.bias.ptr && !p.bias.staged) add_score_term<kBf16>(x, p.bias, b, h, qi, kv0, p.Sk, fs.coef);
+            if (p.mask.ptr && !p.mask.staged) add_score_term<kBf16>(x, p.mask, b, h, qi, kv0, p.Sk, fs.coef);
           }
         };
         for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
           ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
           if (!ok) break;
-          softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, m, l, [] {},
+          softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, prescale, m, l, [] {},
                                             [&](int hh) { mbar_arrive(bar_p_full(t, hh)); }, terms, keep);
           if (drop_on && j + 1 < nt)
             keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (it.j0 + j + 1) * kBN);
@@ -448,9 +449,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
           ok = mbar_wait(bar_s_full(t), it_cnt & 1u, abort_flag);
           if (!ok) break;
-          softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, m, l, [] {},
+          softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, prescale, m, l, [] {},
                                             [&](int hh) { mbar_arrive(bar_p_full(t, hh)); },
-                                            DirectTerms<kBf16>{p, b, h, qi}, keep);
+                                            DirectTerms<kBf16>{p, b, h, qi, fs.coef}, keep);
           if (drop_on && j + 1 < nt)
             keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (it.j0 + j + 1) * kBN);
         }
@@ -542,7 +543,6 @@ static cudaError_t launch_d(const FwdLaunch& a, cudaStream_t stream) {
 }
 
 cudaError_t launch_fwd(const FwdLaunch& a, cudaStream_t stream) {
-  if (a.pair) return launch_fwd_pair(a, stream);
   switch (a.head_dim) {
     case 64: return launch_d<64>(a, stream);
     case 128: return launch_d<128>(a, stream);

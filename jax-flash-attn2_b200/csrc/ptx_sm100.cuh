@@ -286,95 +286,6 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// CTA pairs (clusters of two): tcgen05 with cta_group::2. One thread of the even CTA of a pair
-// issues an MMA that runs on both SMs: each CTA contributes its own 128 rows of A and of the
-// accumulator (its own tensor memory) and one half of the B operand's N extent (its own shared
-// memory), so a B tile is loaded and read once per pair instead of once per CTA.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// The shared::cluster address of this CTA's shared-memory address `addr` in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Arrival on an mbarrier that may live in the other CTA of the cluster (shared::cluster address).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
-}
-// Tiled 5-D copy into this CTA's shared memory whose completion bytes are counted on an mbarrier
-// of either CTA of the pair (`bar_cluster`: shared::cluster address). No multicast: every CTA
-// fetches its own piece.
-__device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar_cluster,
-                                                 int c0, int c1, int c2, int c3, int c4) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2),
-        "r"(c3), "r"(c4)
-      : "memory");
-}
-// Tensor memory of both CTAs of a pair: the same warp of each CTA executes these together.
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// Pair MMAs, issued by the elected lane of a converged warp of the even CTA.
-__device__ __forceinline__ void mma_ss_pair_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                              uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p, e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n"
-      :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_pair_e(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                              uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p, e;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "@e tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "}\n"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// When every pair MMA issued so far by this thread has completed, the mbarrier at the same
-// shared-memory offset `bar` receives one arrival in BOTH CTAs of the pair (a barrier arrival
-// delivered to two CTAs; no data is copied).
-__device__ __forceinline__ void mma_commit_pair_e(uint32_t bar) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred e;\n\t"
-      ".reg .b16 m;\n\t"
-      "mov.b16 m, 3;\n\t"
-      "elect.sync _|e, 0xffffffff;\n\t"
-      "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n\t"
-      "}\n" ::"r"(bar)
-      : "memory");
-}
-
-// ---------------------------------------------------------------------------------------------
 // tcgen05.ld / st, shape 32x32b: thread i of the warp owns TMEM lane (base lane + i); register
 // j holds column (base column + j).
 // ---------------------------------------------------------------------------------------------

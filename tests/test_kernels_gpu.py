@@ -304,22 +304,22 @@ def test_seeded_random_shapes(case):
 
 
 @pytest.mark.parametrize("shape,dtype,causal", [
-    ((1, 256, 256, 2, 1), torch.bfloat16, True),       # one pair item
+    ((1, 256, 256, 2, 1), torch.bfloat16, True),       # one work item
     ((3, 700, 700, 8, 2), torch.float16, True),        # ragged rows, several groups
     ((2, 300, 513, 4, 2), torch.bfloat16, False),      # Sq != Sk, ragged keys
     ((1, 640, 64, 6, 1), torch.bfloat16, True),        # more query rows than keys: tiles without work
-    ((2, 2048, 2048, 16, 4), torch.bfloat16, True),    # 128 pair items: more than CTA pairs on the GPU
-    ((1, 1024, 1024, 2, 2), torch.float16, True),      # one head per group: the single-CTA kernel
+    ((2, 2048, 2048, 16, 4), torch.bfloat16, True),    # 256 work items: more than one per SM
+    ((1, 1024, 1024, 2, 2), torch.float16, True),      # one head per group
 ])
-def test_head_dim_128_forward_on_cta_pairs(shape, dtype, causal):
-    """Head dim 128 without score terms and an even number of query heads per key/value head runs
-    two heads of a group on a pair of CTAs (2-CTA MMAs, each CTA loading half of every K / V tile).
-    Every row of both heads, and the backward fed with its output, must match the oracle."""
+def test_head_dim_128_grouped_heads_and_persistent_items(shape, dtype, causal):
+    """Head dim 128 with grouped query heads: few and many work items per persistent CTA, items
+    whose second query tile has no work, ragged rows and keys. Every row, and the backward fed
+    with the forward's output, must match the oracle."""
     B, Sq, Sk, Hq, Hkv = shape
     run_case(B, Sq, Sk, Hq, Hkv, 128, dtype, causal, scale=128 ** -0.25)
 
 
-def test_cta_pair_forward_with_per_batch_lengths():
+def test_grouped_heads_forward_with_per_batch_lengths():
     J = _J()
     B, S, Hq, Hkv, D, dtype = 3, 512, 4, 2, 128, torch.bfloat16
     lengths = [512, 130, 0]
