@@ -258,6 +258,10 @@ class Inputs:
                 mask[bi, :, :, int(lengths[bi]):] = torch.finfo(dtype).min
             self.mask = mask.cuda()
         self.kw = {}
+        self.drop_bits = None    # record of the dropout keep bits: written by the forward, read by the backward
+        if self.p_drop > 0:
+            from jax_flash_attn2 import dropout_bits_buffer
+            self.drop_bits = dropout_bits_buffer(self.q, self.k, self.p_drop)
         torch.cuda.synchronize()
 
     def flops_fwd(self):
@@ -283,11 +287,13 @@ class Inputs:
 
 
 def fwd_call(J, x):
-    return J.fwd_attention_kernel_call(x.q, x.k, x.v, x.mask, x.bias, None, x.p_drop, x.causal, x.seed, **x.kw)
+    return J.fwd_attention_kernel_call(x.q, x.k, x.v, x.mask, x.bias, None, x.p_drop, x.causal, x.seed,
+                                       dropout_bits=x.drop_bits, **x.kw)
 
 
 def bwd_call(J, x, o, lse):
-    return J.bwd_attention_kernel_call(x.do, x.q, x.k, x.v, x.bias, x.mask, o, lse, x.p_drop, x.causal, None, x.seed, **x.kw)
+    return J.bwd_attention_kernel_call(x.do, x.q, x.k, x.v, x.bias, x.mask, o, lse, x.p_drop, x.causal, None, x.seed,
+                                       dropout_bits=x.drop_bits, **x.kw)
 
 
 def main():

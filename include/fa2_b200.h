@@ -127,6 +127,15 @@ typedef struct {
   void* workspace;
   size_t workspace_bytes;
   const int32_t* offsets_dev;
+  /* Optional (NULL = absent) record of the dropout keep bits, written by the forward and read by
+   * the backward so that the backward need not draw them again (fa2_dropout_bits_bytes(&p) bytes,
+   * 16-byte aligned): uint32 [batch, heads_q, ceil(Sq/128), ceil(Sk/128), 4, 128]. For query tile
+   * i, key tile n, word w and row r, bit p (p < 16) says "keep key 128 n + 32 w + 2 p", bit 16 + p
+   * the same for key 128 n + 32 w + 2 p + 1, both for query row 128 i + r. Tiles no query row can
+   * see (causal, per-batch lengths) are not written. The bits are those of the Philox stream
+   * described above: the record is a cache, never a different mask. */
+  uint32_t* dropout_bits;
+  size_t dropout_bits_bytes;
 } fa2_fwd_params;
 
 typedef struct {
@@ -151,6 +160,11 @@ typedef struct {
   const uint64_t* dropout_seed_dev;            /* optional device-resident seed, see above        */
   const int32_t* offsets_dev;
   fa2_score_grad dbias;                        /* optional gradient of `bias`                     */
+  /* Optional: the record the forward call wrote (same problem, seed and offsets). Kernels that
+   * have shared memory to stage it (head dim up to 64) read the keep bits from it; the others
+   * ignore it and draw the bits again. */
+  const uint32_t* dropout_bits;
+  size_t dropout_bits_bytes;
 } fa2_bwd_params;
 
 /* Forward: o = softmax(scale q k^T + bias + mask [causal]) v with dropout on the weights, and
@@ -171,6 +185,10 @@ size_t fa2_fwd_workspace_bytes(const fa2_problem* problem);
 
 /* Bytes of scratch the backward needs for this problem (fp32 dq accumulator and the row sums). */
 size_t fa2_bwd_workspace_bytes(const fa2_problem* problem);
+
+/* Bytes of the optional dropout-bit record of this problem (0 without dropout). No counterpart in
+ * the reference, whose backward does not regenerate the mask at all (_backward_triton.py:187-188). */
+size_t fa2_dropout_bits_bytes(const fa2_problem* problem);
 
 /* Message of the last failing call on this thread ("" if none). */
 const char* fa2_last_error(void);

@@ -219,6 +219,26 @@ void make_dropout(DropoutDev* d, const fa2_problem& p) {
   d->hq_global = p.heads_q_global;
 }
 
+size_t dropout_bits_bytes(const fa2_problem& p) {
+  if (!(p.dropout_p > 0.f)) return 0;
+  const size_t nqt = (static_cast<size_t>(p.seqlen_q) + 127) / 128, nkt = (static_cast<size_t>(p.seqlen_k) + 127) / 128;
+  return static_cast<size_t>(p.batch) * p.heads_q * nqt * nkt * 2048;
+}
+
+// The optional record of the keep bits (written by the forward, read by the backward).
+int set_dropout_bits(DropoutDev* d, const fa2_problem& p, const uint32_t* bits, size_t bytes) {
+  d->bits = nullptr;
+  if (!bits || !d->enabled) return FA2_OK;
+  if (reinterpret_cast<uintptr_t>(bits) & 15)
+    return fail(FA2_ERR_INVALID_ARG, "dropout_bits must be 16-byte aligned");
+  if (bytes < dropout_bits_bytes(p))
+    return fail(FA2_ERR_INVALID_ARG, "dropout_bits must hold %zu bytes", dropout_bits_bytes(p));
+  d->bits = const_cast<uint32_t*>(bits);
+  d->bits_nqt = (p.seqlen_q + 127) / 128;
+  d->bits_nkt = (p.seqlen_k + 127) / 128;
+  return FA2_OK;
+}
+
 // The optional device-resident operands of the dropout stream (seed, shard offsets).
 int set_dropout_operands(DropoutDev* d, const uint64_t* seed_dev, const int32_t* offsets_dev) {
   if (seed_dev && (reinterpret_cast<uintptr_t>(seed_dev) & 7))
@@ -414,6 +434,9 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
   kp.seqlens = a->seqlens;
   if ((rc = set_dropout_operands(&kp.drop, a->dropout_seed_dev, a->offsets_dev))) return rc;
+  // (grouped decode rows are only packed without dropout, so the record's row / head indices are
+  // always those of the caller's problem)
+  if ((rc = set_dropout_bits(&kp.drop, p, a->dropout_bits, a->dropout_bits_bytes))) return rc;
   kp.n_qblk = (sq_k + 255) / 256;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
@@ -459,6 +482,11 @@ size_t fa2_fwd_workspace_bytes(const fa2_problem* problem) {
   size_t need = plan_splits(*problem, hd, false).total;
   if (can_pack_heads(*problem)) need = std::max(need, plan_splits(*problem, hd, true).total);
   return need;
+}
+
+size_t fa2_dropout_bits_bytes(const fa2_problem* problem) {
+  if (!problem || check_problem(*problem)) return 0;
+  return dropout_bits_bytes(*problem);
 }
 
 size_t fa2_bwd_workspace_bytes(const fa2_problem* problem) {
@@ -535,6 +563,7 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
   kp.seqlens = a->seqlens;
   if ((rc = set_dropout_operands(&kp.drop, a->dropout_seed_dev, a->offsets_dev))) return rc;
+  if ((rc = set_dropout_bits(&kp.drop, p, a->dropout_bits, a->dropout_bits_bytes))) return rc;
   kp.n_kvblk = (p.seqlen_k + 127) / 128;
   kp.status = status_ptr();
   if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");

@@ -52,7 +52,9 @@ struct BwdRoles {
 
 // kStaged (score terms / dropout at head dim 64): bias and mask tiles of a step, [128 queries][128
 // keys] 16-bit each, are brought in by the TMA unit one step ahead (single-buffered: they are read
-// at the very start of a step) instead of being gathered column by column from global memory.
+// at the very start of a step) instead of being gathered column by column from global memory, and
+// when the caller hands over the forward's record of the dropout keep bits, the step's 2 KiB of it
+// arrive with the Q tile, so that no Philox round runs in the backward.
 template <int D, bool kStaged = false>
 struct BwdSmem {
   static constexpr int kTileBytes = 128 * D * 2;
@@ -68,7 +70,10 @@ struct BwdSmem {
   static constexpr int kStatsOff = kdSOff + 128 * 128 * 2; // 2 stages x (lse2[128], delta[128])
   static constexpr int kTermBytes = 128 * 128 * 2;          // one term tile: two [128 q][64 keys] blocks
   static constexpr int kTermOff = kStatsOff + 2 * 1024;     // bias tile, mask tile
-  static constexpr int kBarOff = kTermOff + (kStaged ? 2 * kTermBytes : 0);
+  // recorded dropout bits of a step's (query tile, key tile): [4 words][128 queries], 2 stages
+  static constexpr int kBitsBytes = 4 * 128 * 4;
+  static constexpr int kBitsOff = kTermOff + (kStaged ? 2 * kTermBytes : 0);
+  static constexpr int kBarOff = kBitsOff + (kStaged ? 2 * kBitsBytes : 0);
   static constexpr int kNumBars = 17 + 4;                   // + term_full[2], term_empty[2]
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
@@ -273,8 +278,14 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         step_coords(it, h, i);
         ok = mbar_wait(bar_q_empty(st), par, abort_flag);
         if (!ok) break;
-        mbar_arrive_expect_tx(bar_q_full(st), L::kTileBytes + 1024);
+        const bool with_bits = kStaged && p.drop.bits != nullptr;
+        mbar_arrive_expect_tx(bar_q_full(st), L::kTileBytes + 1024 + (with_bits ? L::kBitsBytes : 0));
         tma_load_5d(sQ + st * L::kTileBytes, &tmQ, bar_q_full(st), 0, i * kBM, 0, h, b);
+        if constexpr (kStaged) {
+          if (with_bits)
+            bulk_load_1d(smem_base + L::kBitsOff + st * L::kBitsBytes, dropout_bits_block(p.drop, b, h, p.Hq, i, n),
+                         L::kBitsBytes, bar_q_full(st));
+        }
         bulk_load_1d(sStats + st * 1024,
                      stats + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * 256, 1024,
                      bar_q_full(st));
@@ -527,9 +538,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint32_t keep[kCW / 32];
 #pragma unroll
     for (int k = 0; k < kCW / 32; ++k) keep[k] = 0xffffffffu;
+    const bool recorded_bits = kStaged && p.drop.bits != nullptr;   // read instead of drawn
     auto draw_keep = [&](int step) {
       if constexpr (kFeat) {
-        if (p.drop.enabled && step < T) {
+        if (p.drop.enabled && !recorded_bits && step < T) {
           int hh, ii;
           step_coords(step, hh, ii);
           dropout_keep_bits_transposed<kCW>(p.drop, dropout_bh_index(p.drop, b, hh), kv, ii * kBM + kCW * w,
@@ -551,6 +563,23 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
+      if constexpr (kStaged) {
+        if (recorded_bits) {
+          // word r / 32 of every query row holds the flags of this thread's 32-key group: the even
+          // keys in the low half, the odd keys in the high half
+          const uint32_t src = smem_base + L::kBitsOff + st * L::kBitsBytes + ((r >> 5) * 128 + kCW * w) * 4;
+          const int pos = ((r & 31) >> 1) + 16 * (r & 1);
+#pragma unroll
+          for (int k = 0; k < kCW / 32; ++k) keep[k] = 0u;
+#pragma unroll
+          for (int c4 = 0; c4 < kCW / 4; ++c4) {
+            const uint4 wv = lds128(src + 16 * c4);
+            const uint32_t four = ((wv.x >> pos) & 1u) | (((wv.y >> pos) & 1u) << 1) | (((wv.z >> pos) & 1u) << 2) |
+                                  (((wv.w >> pos) & 1u) << 3);
+            keep[(4 * c4) >> 5] |= four << ((4 * c4) & 31);
+          }
+        }
+      }
       // some (query, key) pairs of this step are above the causal diagonal
       const bool diag = (kCausal && (n * kBN + kBN - 1 > i * kBM + p.causal_off)) || dead_keys;
       // masked iff query index < q_lim: every query for a key past the end

@@ -242,7 +242,11 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (drop_on) dropout_key(p.drop, key_lo, key_hi);
     const uint32_t bh_glob = drop_on ? dropout_bh_index(p.drop, b, h) : 0u;
     KeepBitsDropout keep{drop_on, make_uint4(0u, 0u, 0u, 0u)};
-    if (drop_on && nt > 0) keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, j0 * kBN);
+    auto draw_keep = [&](int jt) {     // keep bits of K/V tile jt, also recorded for the backward
+      keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, jt * kBN);
+      store_row_keep_bits(p.drop, keep.bits, b, h, p.Hq, q0 >> 7, jt, r);
+    };
+    if (drop_on && nt > 0) draw_keep(j0);
 
     for (int j = 0; j < nt; ++j) {
       const int buf = j & 1;
@@ -258,8 +262,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                                          [&](int half) { mbar_arrive(bar_p_full(buf, half)); },
                                          DirectTerms<kBf16>{p, b, h, qi, fs.coef}, keep);
       if (!ok) break;
-      if (drop_on && j + 1 < nt)
-        keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (j0 + j + 1) * kBN);
+      if (drop_on && j + 1 < nt) draw_keep(j0 + j + 1);
     }
 
     if (ok) ok = mbar_wait(bar_q_full, 0, abort_flag);

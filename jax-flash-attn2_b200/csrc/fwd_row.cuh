@@ -129,6 +129,18 @@ __device__ __forceinline__ uint4 draw_row_keep_bits(const DropoutDev& d, uint32_
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Writes a row's keep bits of one (query tile, key tile) into the caller's record, from which the
+// backward reads them instead of drawing them again: word w of row r at [w][r] of the tile's block.
+__device__ __forceinline__ void store_row_keep_bits(const DropoutDev& d, const uint4& bits, int b, int h,
+                                                    int Hq, int q_tile, int kv_tile, int r) {
+  if (d.bits == nullptr) return;
+  uint32_t* dst = dropout_bits_block(d, b, h, Hq, q_tile, kv_tile) + r;
+  dst[0] = bits.x;
+  dst[128] = bits.y;
+  dst[256] = bits.z;
+  dst[384] = bits.w;
+}
+
 // Zeroes the dropped weights of one piece (64 keys) of a row: `pk` holds the piece's P as 32 words
 // of two 16-bit values (even key in the low half). Per pair: shift the pair's two flags to the
 // sign bits of bytes 1 and 3, let a byte permute replicate them over the two halves, and mask.

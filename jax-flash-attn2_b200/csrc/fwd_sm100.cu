@@ -379,7 +379,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       // after P of tile j has been handed over
       KeepBitsDropout keep{drop_on, make_uint4(0u, 0u, 0u, 0u)};
       const uint32_t bh_glob = drop_on ? dropout_bh_index(p.drop, b, h) : 0u;
-      if (drop_on && nt > 0) keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, it.j0 * kBN);
+      auto draw_keep = [&](int jt) {     // keep bits of K/V tile jt, also recorded for the backward
+        keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, jt * kBN);
+        store_row_keep_bits(p.drop, keep.bits, b, h, p.Hq, (it.q0 >> 7) + t, jt, r);
+      };
+      if (drop_on && nt > 0) draw_keep(it.j0);
 
       if constexpr (kStaged) {
         // ---- this warp's stream of term pieces for the item: piece n = (K/V tile n / per_tile,
@@ -442,8 +446,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           if (!ok) break;
           softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, prescale, m, l, [] {},
                                             [&](int hh) { mbar_arrive(bar_p_full(t, hh)); }, terms, keep);
-          if (drop_on && j + 1 < nt)
-            keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (it.j0 + j + 1) * kBN);
+          if (drop_on && j + 1 < nt) draw_keep(it.j0 + j + 1);
         }
       } else {
         for (int j = 0; j < nt && ok; ++j, ++it_cnt) {
@@ -452,8 +455,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           softmax_tile_row<D, kBf16, kFeat>(tS, tO, it.j0 + j, j > 0, p, row_lim, sc, prescale, m, l, [] {},
                                             [&](int hh) { mbar_arrive(bar_p_full(t, hh)); },
                                             DirectTerms<kBf16>{p, b, h, qi, fs.coef}, keep);
-          if (drop_on && j + 1 < nt)
-            keep.bits = draw_row_keep_bits(p.drop, key_lo, key_hi, bh_glob, qi, (it.j0 + j + 1) * kBN);
+          if (drop_on && j + 1 < nt) draw_keep(it.j0 + j + 1);
         }
       }
 

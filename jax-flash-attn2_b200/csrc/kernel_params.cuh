@@ -33,8 +33,17 @@ struct DropoutDev {
   int b_off, h_off, hq_global;
   // optional: (batch offset, head offset) read from this device address instead of b_off / h_off
   const int* offsets_dev;
+  // optional record of the keep bits: uint32 [B, Hq, bits_nqt, bits_nkt, 4, 128]; written by the
+  // forward, read by the backward kernels that stage it
+  uint32_t* bits;
+  int bits_nqt, bits_nkt;
   int enabled;
 };
+
+// First word of the record's block for (batch b, head h, query tile qt, key tile kt).
+__device__ __forceinline__ uint32_t* dropout_bits_block(const DropoutDev& d, int b, int h, int Hq, int qt, int kt) {
+  return d.bits + (((static_cast<long long>(b) * Hq + h) * d.bits_nqt + qt) * d.bits_nkt + kt) * 512;
+}
 
 // The Philox key of a call: (low, high) half of the seed.
 __device__ __forceinline__ void dropout_key(const DropoutDev& d, uint32_t& lo, uint32_t& hi) {

@@ -10,6 +10,7 @@ from ._flash_attention import flash_attention as triton_flash_attention
 from ._kernel_calls import (
     bwd_attention_kernel_call,
     device_status,
+    dropout_bits_buffer,
     fwd_attention_kernel_call,
 )
 
@@ -23,5 +24,6 @@ __all__ = (
     "fwd_attention_kernel_call",
     "bwd_attention_kernel_call",
     "device_status",
+    "dropout_bits_buffer",
 )
 __version__ = "0.1.0"

@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "fa2_debug_device_status",
     "fa2_debug_bwd_stage_events",
     "fa2_bwd_static_scratch",
+    "fa2_dropout_bits_bytes",
 )
 FA2_BWD_STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 # FA2_ABI_VERSION of the header these structures were written against (major * 1000 + minor)
@@ -87,6 +88,8 @@ class FwdParams(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("offsets_dev", C.c_void_p),
+        ("dropout_bits", C.c_void_p),
+        ("dropout_bits_bytes", C.c_size_t),
     ]
 
 
@@ -111,6 +114,8 @@ class BwdParams(C.Structure):
         ("dropout_seed_dev", C.c_void_p),
         ("offsets_dev", C.c_void_p),
         ("dbias", ScoreGrad),
+        ("dropout_bits", C.c_void_p),
+        ("dropout_bits_bytes", C.c_size_t),
     ]
 
 
@@ -153,6 +158,8 @@ def load() -> C.CDLL:
     lib.fa2_fwd_workspace_bytes.restype = C.c_size_t
     lib.fa2_bwd_workspace_bytes.argtypes = [C.POINTER(Problem)]
     lib.fa2_bwd_workspace_bytes.restype = C.c_size_t
+    lib.fa2_dropout_bits_bytes.argtypes = [C.POINTER(Problem)]
+    lib.fa2_dropout_bits_bytes.restype = C.c_size_t
     lib.fa2_last_error.argtypes = []
     lib.fa2_last_error.restype = C.c_char_p
     lib.fa2_debug_device_status.argtypes = [C.c_void_p]

@@ -15,6 +15,7 @@ import torch
 
 from ._kernel_calls import (
     bwd_attention_kernel_call,
+    dropout_bits_buffer,
     fwd_attention_kernel_call,
     normalise_attention_mask,
     seqlens_from_padding_mask,
@@ -24,10 +25,15 @@ from ._kernel_calls import (
 class _FlashAttentionCall(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard):
+        # one more residual than the reference keeps: the record of the dropout keep bits, so that
+        # the backward reads them instead of running Philox again (None without dropout)
+        bits = dropout_bits_buffer(q, k, dropout_prob)
         out, lse = fwd_attention_kernel_call(
-            q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, **shard
+            q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed,
+            dropout_bits=bits, **shard
         )   # `shard` also carries the per-batch lengths, when there are any
         ctx.save_for_backward(q, k, v, out, lse)
+        ctx.dropout_bits = bits
         ctx.extras = (attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard)
         ctx.bias_grad = bias is not None and bias.requires_grad
         return out
@@ -38,7 +44,7 @@ class _FlashAttentionCall(torch.autograd.Function):
         attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, shard = ctx.extras
         grads = bwd_attention_kernel_call(
             dO, q, k, v, bias, attention_mask, out, lse, dropout_prob, causal, softmax_scale, dropout_seed,
-            bias_grad=ctx.bias_grad, **shard
+            bias_grad=ctx.bias_grad, dropout_bits=ctx.dropout_bits, **shard
         )
         dbias = grads[3].to(bias.dtype) if ctx.bias_grad else None
         return grads[0], grads[1], grads[2], None, dbias, None, None, None, None, None

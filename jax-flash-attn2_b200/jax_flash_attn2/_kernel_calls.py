@@ -168,6 +168,30 @@ def _offsets_ptr(offsets_dev, q: torch.Tensor):
     return offsets_dev.data_ptr(), offsets_dev
 
 
+def dropout_bits_buffer(q: torch.Tensor, k: torch.Tensor, dropout_prob: float,
+                        max_bytes: int = 1 << 30) -> tp.Optional[torch.Tensor]:
+    """An uninitialised buffer for the record of dropout keep bits of a (q, k) problem: pass it as
+    `dropout_bits` to the forward call, which fills it, and to the backward call of the same
+    problem, which then reads the bits instead of drawing them again. None without dropout, or
+    when the record (Sq * Sk / 8 bytes per batch element and head, rounded up to whole tiles)
+    would exceed `max_bytes`."""
+    if not dropout_prob > 0.0:
+        return None
+    batch, sq, hq, _ = q.shape
+    nbytes = batch * hq * ((sq + 127) // 128) * ((k.shape[1] + 127) // 128) * 2048
+    if nbytes > max_bytes:
+        return None
+    return torch.empty((nbytes // 4,), dtype=torch.int32, device=q.device)
+
+
+def _dropout_bits_ptr(dropout_bits, q: torch.Tensor):
+    if dropout_bits is None:
+        return None, 0
+    if dropout_bits.dtype != torch.int32 or dropout_bits.device != q.device or not dropout_bits.is_contiguous():
+        raise ValueError("dropout_bits must be a contiguous int32 tensor on the device of q (see dropout_bits_buffer)")
+    return dropout_bits.data_ptr(), dropout_bits.numel() * 4
+
+
 def _problem(q, k, softmax_scale, dropout_prob, causal, dropout_seed, batch_offset, head_offset, heads_q_global):
     batch, sq, hq, d = q.shape
     _, sk, hkv, _ = k.shape
@@ -218,13 +242,15 @@ def fwd_attention_kernel_call(
     seqlens: tp.Optional[torch.Tensor] = None,
     split_kv: bool = True,
     offsets_dev: tp.Optional[torch.Tensor] = None,
+    dropout_bits: tp.Optional[torch.Tensor] = None,
 ) -> tp.Tuple[torch.Tensor, torch.Tensor]:
     """Forward launch. q [B,Sq,Hq,D]; k, v [B,Sk,Hkv,D]; `attention_mask` here is already an
     additive 4-D term (see normalise_attention_mask); `seqlens` (int32 [B], device) gives every
     batch element its own length, the reference's varlen mode without packing; `split_kv=False`
     withholds the scratch with which the library splits low-occupancy problems along the key
     sequence (same result, computed by fewer SMs); `offsets_dev` (int32 [2], device) carries
-    (batch_offset, head_offset) as a device operand. Returns
+    (batch_offset, head_offset) as a device operand; `dropout_bits` (from `dropout_bits_buffer`)
+    receives the record of the keep bits for the backward call. Returns
     (out [B,Sq,Hq,D] in q.dtype, lse [B,Hq,ceil(Sq/128)*128] float32, natural log; columns >= Sq
     are not written)."""
     _check_qkv(q, k, v)
@@ -248,6 +274,7 @@ def fwd_attention_kernel_call(
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
     a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
     a.offsets_dev, _keep_f = _offsets_ptr(offsets_dev, q)
+    a.dropout_bits, a.dropout_bits_bytes = _dropout_bits_ptr(dropout_bits, q)
     # low-occupancy problems (decode steps) are split along the key sequence if scratch is offered
     nbytes = lib.fa2_fwd_workspace_bytes(C.byref(a.p)) if split_kv else 0
     if nbytes:
@@ -277,6 +304,7 @@ def bwd_attention_kernel_call(
     seqlens: tp.Optional[torch.Tensor] = None,
     offsets_dev: tp.Optional[torch.Tensor] = None,
     bias_grad: bool = False,
+    dropout_bits: tp.Optional[torch.Tensor] = None,
 ):
     """Backward launch; `M` is the lse returned by the forward. Returns (dq, dk, dv) in the input
     dtype; dk and dv are already reduced over the query heads of each key/value head. With
@@ -321,6 +349,7 @@ def bwd_attention_kernel_call(
     a.seqlens, _keep_s = _seqlens_ptr(seqlens, q, sk)
     a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
     a.offsets_dev, _keep_f = _offsets_ptr(offsets_dev, q)
+    a.dropout_bits, a.dropout_bits_bytes = _dropout_bits_ptr(dropout_bits, q)
     _launch(lib.fa2_bwd, a, q.device)
     if bias_grad:
         return dq, dk, dv, dbias

@@ -1,7 +1,8 @@
 """GPU tests of what the library adds around the bias: its gradient (the reference returns none,
 flash_attention_triton/_flash_attention.py:88), a bias with one head per key/value head read by
-index instead of being repeated (the reference repeats it, flash_attention.py:161-164), and the
-shard offsets of the dropout stream given as a device operand."""
+index instead of being repeated (the reference repeats it, flash_attention.py:161-164), the
+shard offsets of the dropout stream given as a device operand, and the record of the dropout keep
+bits that the forward can write for the backward."""
 import pytest
 import torch
 
@@ -133,3 +134,70 @@ def test_shard_offsets_read_from_device_memory_give_the_same_bits():
                                          offsets_dev=off)
         assert torch.equal(g1[1], g2[1]) and torch.equal(g1[2], g2[2]) and rel_l2(g1[0], g2[0]) < 1e-3
     assert J.device_status() == 0
+
+
+def _decode_bit_record(bits, B, H, Sq, Sk):
+    """uint32 record [B, H, ceil(Sq/128), ceil(Sk/128), 4, 128] -> bool [B, H, Sq, Sk]: word w of row
+    r holds the flag of key 32 w + 2 p in bit p and that of key 32 w + 2 p + 1 in bit 16 + p."""
+    nqt, nkt = (Sq + 127) // 128, (Sk + 127) // 128
+    rec = bits.cpu().view(B, H, nqt, nkt, 4, 128).to(torch.int64) & 0xFFFFFFFF
+    keep = torch.zeros(B, H, nqt * 128, nkt * 128, dtype=torch.bool)
+    for w in range(4):
+        words = rec[:, :, :, :, w, :]                      # [B, H, nqt, nkt, 128 rows]
+        for p in range(16):
+            for e in range(2):
+                flag = ((words >> (p + 16 * e)) & 1).bool()   # key 32 w + 2 p + e of every tile
+                col = 32 * w + 2 * p + e
+                keep.view(B, H, nqt, 128, nkt, 128)[:, :, :, :, :, col] = flag.permute(0, 1, 2, 4, 3)
+    return keep[:, :, :Sq, :Sk]
+
+
+@pytest.mark.parametrize("D", [64, 128, 256])
+def test_dropout_bit_record_holds_the_oracle_mask(D):
+    """The forward's optional record of the keep bits must be the Philox mask of the oracle, bit for
+    bit, for every head-dim kernel (non-causal: every tile is written)."""
+    import jax_flash_attn2 as J
+    from oracle import philox
+    B, Sq, Sk, Hq, Hkv, p, seed = 2, 200, 328, 4, 2, 0.3, 99
+    q, k, v, _ = (x.cuda() for x in W.make_qkv(B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, D ** -0.25))
+    bits = J.dropout_bits_buffer(q, k, p)
+    bits.fill_(-1)
+    o1, _ = J.fwd_attention_kernel_call(q, k, v, None, None, None, p, False, seed, dropout_bits=bits,
+                                        batch_offset=1, head_offset=4, heads_q_global=12)
+    o2, _ = J.fwd_attention_kernel_call(q, k, v, None, None, None, p, False, seed,
+                                        batch_offset=1, head_offset=4, heads_q_global=12)
+    assert torch.equal(o1, o2) and J.device_status() == 0
+    want = torch.from_numpy(philox.keep_mask(seed, p, B, Hq, Sq, Sk, 1, 4, 12))
+    assert torch.equal(_decode_bit_record(bits, B, Hq, Sq, Sk), want)
+    assert J.dropout_bits_buffer(q, k, 0.0) is None
+
+
+@pytest.mark.parametrize("D,causal,extras", [(64, True, False), (64, False, True), (32, True, False), (128, True, False)])
+def test_backward_with_the_bit_record_equals_backward_that_redraws(D, causal, extras):
+    """Given the forward's record, the head-dim-64 backward reads the keep bits from it instead of
+    running Philox; the gradients must be those of the backward that draws the bits again (dk / dv
+    bit for bit). Kernels that cannot stage the record (head dim 128) ignore it."""
+    import jax_flash_attn2 as J
+    B, S, Hq, Hkv, p, seed, dtype = 2, 300, 4, 2, 0.2, 5, torch.bfloat16
+    q, k, v, do = (x.cuda() for x in W.make_qkv(B, S, S, Hq, Hkv, D, dtype, D ** -0.25))
+    bias = _bias((B, 1, S, S), dtype).cuda() if extras else None
+    seqlens = torch.tensor([300, 131], dtype=torch.int32).cuda() if extras else None
+    bits = J.dropout_bits_buffer(q, k, p)
+    out, lse = J.fwd_attention_kernel_call(q, k, v, None, bias, None, p, causal, seed, dropout_bits=bits, seqlens=seqlens)
+    g1 = J.bwd_attention_kernel_call(do, q, k, v, bias, None, out, lse, p, causal, None, seed, dropout_bits=bits,
+                                     seqlens=seqlens)
+    g2 = J.bwd_attention_kernel_call(do, q, k, v, bias, None, out, lse, p, causal, None, seed, seqlens=seqlens)
+    assert J.device_status() == 0
+    assert torch.equal(g1[1], g2[1]) and torch.equal(g1[2], g2[2]) and rel_l2(g1[0], g2[0]) < 1e-3
+
+
+def test_class_api_with_dropout_matches_the_dense_oracle_gradients():
+    import jax_flash_attn2 as J
+    fa = J.create_flash_attention("gpu", "triton")
+    q, k, v, do = W.make_qkv(2, 256, 256, 4, 2, 64, torch.bfloat16, 0.35)
+    qd, kd, vd = (x.cuda().requires_grad_(True) for x in (q, k, v))
+    out = fa(qd, kd, vd, causal=True, dropout_prob=0.15, dropout_seed=21)
+    out.backward(do.cuda())
+    want = dense.attention_grads(do, q, k, v, causal=True, dropout_p=0.15, dropout_seed=21)
+    for mine, ref in zip((qd.grad, kd.grad, vd.grad), want):
+        assert rel_l2(mine.cpu().double(), ref) <= 2 * GRAD_TOL
