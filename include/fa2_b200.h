@@ -19,6 +19,8 @@
  *     broadcast bias / mask dimensions, stride 0) need no copy. The head-dim stride must be 1.
  *   - Return value: 0 on success, a negative fa2_status otherwise. fa2_last_error() returns a
  *     thread-local message for the last failing call. Validation happens before any launch.
+ *   - Two hooks for tests and measurements (device status word, per-kernel events of the backward)
+ *     are declared apart, in fa2_b200_debug.h: no caller of the attention path needs them.
  */
 #ifndef FA2_B200_H_
 #define FA2_B200_H_
@@ -199,10 +201,6 @@ const char* fa2_last_error(void);
 #define FA2_ABI_VERSION 2000
 int fa2_version(void);
 
-/* Reads and clears the device status word written by a kernel whose bounded wait ran out
- * (0 = no time-out seen). Synchronises the stream; meant for tests and debugging. */
-int fa2_debug_device_status(void* cuda_stream);
-
 /* Size of the scratch array built into the library for fa2_bwd_static_scratch (32 MiB). */
 #define FA2_BWD_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
 
@@ -233,12 +231,6 @@ int fa2_debug_device_status(void* cuda_stream);
  *    from two threads) race on the array and give wrong gradients: keep calls on one device in
  *    stream order. fa2_bwd with caller-owned workspaces has no such restriction. */
 int fa2_bwd_static_scratch(const fa2_bwd_params* params, void* cuda_stream);
-
-/* Profiling hook: arms four CUDA events (cudaEvent_t cast to void*) for the next fa2_bwd call on
- * this thread. They are recorded on that call's stream before the rowsum pre-pass, before the
- * main kernel, after it and after the dq conversion, so a caller can time each kernel of the
- * backward (the three launches that replace _backward_triton.py:1049-1154). NULL disarms. */
-int fa2_debug_bwd_stage_events(void* const* events);
 
 #ifdef __cplusplus
 }

@@ -35,6 +35,7 @@ def _nvcc() -> str:
 def _newest_input() -> float:
     paths = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     paths.append(os.path.join(HERE, "..", "include", "fa2_b200.h"))
+    paths.append(os.path.join(HERE, "..", "include", "fa2_b200_debug.h"))
     paths.append(os.path.abspath(__file__))
     return max(os.path.getmtime(p) for p in paths)
 

@@ -15,6 +15,7 @@
 #include <mutex>
 
 #include "../../include/fa2_b200.h"
+#include "../../include/fa2_b200_debug.h"
 #include "bwd_launch.cuh"
 #include "fwd_launch.cuh"
 #include "launch_util.cuh"
@@ -254,6 +255,12 @@ int set_dropout_operands(DropoutDev* d, const uint64_t* seed_dev, const int32_t*
 // what allocators of every framework (XLA's sub-allocated temporaries included) guarantee.
 constexpr uintptr_t kWorkspaceAlign = 128;
 
+// Bytes of Q, dO and dq-accumulator tiles that one chunk of the backward's launch order may span.
+// Measured on B=8, S=4096, Hq=32, Hkv=8, D=128 causal (16 MiB per group): main kernel 2.76 ms with
+// chunks of 1 or 2 groups, 2.58-2.63 ms with 4, 8 or 16; only a few of a chunk's key tiles run at
+// any time, so the live set stays well below this figure.
+constexpr size_t kSchedL2Bytes = 128u << 20;
+
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct BwdWorkspace {
@@ -352,6 +359,11 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
     return fail(FA2_ERR_INVALID_ARG, "q, k, v, o and lse must be non-null");
   if (a->lse_stride_h < p.seqlen_q || a->lse_stride_b < 0)
     return fail(FA2_ERR_INVALID_ARG, "lse_stride_h must be at least seqlen_q");
+  // First CUDA call of the entry point, on purpose a runtime call: it makes the device's primary
+  // context current on a host thread that has not touched the runtime yet (a framework's worker
+  // thread served from a memory cache), which the driver-level tensor-map encoder below needs.
+  int* const status_word = status_ptr();
+  if (!status_word) return fail(FA2_ERR_CUDA, "status word is not addressable");
 
   FwdLaunch L;
   std::memset(&L, 0, sizeof(L));
@@ -438,8 +450,7 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   // always those of the caller's problem)
   if ((rc = set_dropout_bits(&kp.drop, p, a->dropout_bits, a->dropout_bits_bytes))) return rc;
   kp.n_qblk = (sq_k + 255) / 256;
-  kp.status = status_ptr();
-  if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
+  kp.status = status_word;
 
   L.head_dim = D;
   L.bf16 = bf16;
@@ -518,6 +529,10 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
       return fail(FA2_ERR_INVALID_ARG, "dbias must be 4-byte aligned");
   }
 
+  // a runtime call before the driver-level tensor-map encoder: see fa2_fwd
+  int* const status_word = status_ptr();
+  if (!status_word) return fail(FA2_ERR_CUDA, "status word is not addressable");
+
   BwdLaunch L;
   std::memset(&L, 0, sizeof(L));
   const bool bf16 = p.dtype == FA2_BF16;
@@ -565,8 +580,17 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   if ((rc = set_dropout_operands(&kp.drop, a->dropout_seed_dev, a->offsets_dev))) return rc;
   if ((rc = set_dropout_bits(&kp.drop, p, a->dropout_bits, a->dropout_bits_bytes))) return rc;
   kp.n_kvblk = (p.seqlen_k + 127) / 128;
-  kp.status = status_ptr();
-  if (!kp.status) return fail(FA2_ERR_CUDA, "status word is not addressable");
+  // Launch order (bwd_work_item): causal problems take as many (batch, kv head) groups per chunk as
+  // keep a chunk's Q, dO and fp32 dq accumulator tiles within a share of L2; uniform problems keep
+  // the group-after-group order.
+  kp.sched_groups = 1;
+  if (p.causal) {
+    const size_t per_group = static_cast<size_t>(kp.G) * p.seqlen_q * D * (2 + 2 + 4);
+    const size_t budget = kSchedL2Bytes;
+    const long long groups = static_cast<long long>(p.batch) * p.heads_kv;
+    kp.sched_groups = static_cast<int>(std::max<long long>(1, std::min<long long>(groups, budget / std::max<size_t>(per_group, 1))));
+  }
+  kp.status = status_word;
 
   L.head_dim = D;
   L.bf16 = bf16;

@@ -135,8 +135,8 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   // ---- work item: (batch, kv head, key tile, half of the head dim) ---------------------------
   const int half = blockIdx.x & 1;
   const int rest = blockIdx.x >> 1;
-  const int n = rest % p.n_kvblk;
-  const int bhk = rest / p.n_kvblk;
+  int n, bhk;
+  bwd_work_item(rest, p.B * p.Hkv, p.n_kvblk, p.sched_groups, bhk, n);
   const int b = bhk / p.Hkv;
   const int hk = bhk - b * p.Hkv;
   const int nQ64 = (p.Sq + kBQ - 1) / kBQ;      // tiles in the accumulator layout

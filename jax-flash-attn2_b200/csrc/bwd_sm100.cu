@@ -182,8 +182,8 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int lane = tid & 31;
 
   // ---- work item: (batch, kv head, key tile); later key tiles (fewest steps when causal) last
-  const int n = blockIdx.x % p.n_kvblk;
-  const int bhk = blockIdx.x / p.n_kvblk;
+  int n, bhk;
+  bwd_work_item(blockIdx.x, p.B * p.Hkv, p.n_kvblk, p.sched_groups, bhk, n);
   const int b = bhk / p.Hkv;
   const int hk = bhk - b * p.Hkv;
   const int nQ = (p.Sq + kBM - 1) / kBM;   // query tiles in the statistics / accumulator layout

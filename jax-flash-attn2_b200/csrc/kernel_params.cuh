@@ -89,6 +89,24 @@ struct FwdKernelParams {
   int* status;          // device status word (bounded-wait time-outs)
 };
 
+struct BwdKernelParams;
+// Which (batch * kv head) group and key tile block index `idx` works on. With causal masking a key
+// tile's work shrinks with its index (tile 0 is seen by every query tile, the last one by a single
+// one). Blocks are dispatched in index order as SMs become free, so the order decides how ragged the
+// end of the launch is: group after group (every group's heavy tiles arrive late in its turn)
+// leaves SMs idle at the end for about one heavy tile's duration (8 % of the headline launch), all
+// tiles of all groups heaviest first balances best but makes every group's Q / dO tiles live in L2
+// for the whole launch. Chunks of `sched_groups` groups, key-tile-major inside a chunk, keep the
+// working set of a chunk in L2 and leave only the last chunk's tail.
+__device__ __forceinline__ void bwd_work_item(int idx, int groups, int n_kvblk, int sched_groups, int& bhk, int& n) {
+  const int per_chunk = sched_groups * n_kvblk;
+  const int chunk = idx / per_chunk;
+  const int rem = idx - chunk * per_chunk;
+  const int in_chunk = min(sched_groups, groups - chunk * sched_groups);   // the last chunk may be short
+  n = rem / in_chunk;
+  bhk = chunk * sched_groups + (rem - n * in_chunk);
+}
+
 struct BwdKernelParams {
   int B, Sq, Sk, Hq, Hkv, G;
   int causal_off;
@@ -102,6 +120,10 @@ struct BwdKernelParams {
   ScoreTermDev bias, mask;
   DropoutDev drop;
   int n_kvblk;          // number of 128-row key blocks
+  // Launch order of the (batch, kv head, key tile) work items: the (batch, kv head) groups are taken
+  // `sched_groups` at a time, and inside such a chunk the key tiles of all its groups come
+  // heaviest first (see bwd_work_item).
+  int sched_groups;     // >= 1
   const int* seqlens;   // optional per-batch lengths (Sq == Sk), as in the forward
   // fp16 only: bit pattern of max|dO| over the whole call (written by the pre-pass); dS is
   // scaled by a power of two derived from it so that small cotangents do not underflow in fp16.

@@ -15,7 +15,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "fa2_b200.h")).read()
-    declared = set(re.findall(r"\b(fa2_[a-z_0-9]+)\s*\(", header))
+    debug_header = open(os.path.join(ROOT, "include", "fa2_b200_debug.h")).read()
+    assert "fa2_debug" not in header      # test / measurement hooks stay out of the attention ABI
+    declared = set(re.findall(r"\b(fa2_[a-z_0-9]+)\s*\(", header + debug_header))
     assert declared, "no declarations found"
     lib = _capi.load()
     for name in declared:

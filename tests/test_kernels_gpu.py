@@ -520,3 +520,39 @@ def test_unsupported_arguments_raise_before_launch():
     with pytest.raises(Fa2Error, match="dropout_p"):
         J.fwd_attention_kernel_call(q, q, q, dropout_prob=1.5)
     assert J.device_status() == 0
+
+
+def test_entry_points_work_on_a_host_thread_that_never_called_cuda():
+    """A framework may call the library from a worker thread that has made no CUDA runtime call yet
+    (torch's autograd thread when every allocation is served from the cache). The entry points must
+    make the device context current themselves before they build their tensor maps."""
+    import ctypes as C
+    import threading
+    J = _J()
+    from jax_flash_attn2 import _capi
+    from jax_flash_attn2._kernel_calls import _strides
+    lib = _capi.load()
+    q, k, v, _ = (x.cuda() for x in W.make_qkv(1, 256, 256, 2, 1, 64, torch.bfloat16, 0.35))
+    ref, ref_lse = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)
+    out, lse = torch.empty_like(ref), torch.empty_like(ref_lse)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    a = _capi.FwdParams()
+    a.p.batch, a.p.seqlen_q, a.p.seqlen_k, a.p.heads_q, a.p.heads_kv, a.p.head_dim = 1, 256, 256, 2, 1, 64
+    a.p.dtype, a.p.causal, a.p.softmax_scale, a.p.heads_q_global = _capi.FA2_BF16, 1, 64 ** -0.5, 2
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", out)):
+        setattr(a, name, t.data_ptr())
+        setattr(a, name + "_strides", _strides(t))
+    a.lse, a.lse_stride_b, a.lse_stride_h = lse.data_ptr(), lse.stride(0), lse.stride(1)
+    result = {}
+
+    def worker():       # no torch call in here: only the C ABI
+        result["rc"] = lib.fa2_fwd(C.byref(a), C.c_void_p(stream))
+        result["msg"] = lib.fa2_last_error()
+
+    t = threading.Thread(target=worker)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert result["rc"] == 0, result["msg"]
+    assert torch.equal(out, ref) and torch.equal(lse[:, :, :256], ref_lse[:, :, :256])
