@@ -233,6 +233,9 @@ def test_decode_rows_with_grouped_heads(D, dtype, B, Sk, Hq, Hkv, causal):
     dict(B=1, Sq=2048, Sk=2048, Hq=4, Hkv=4, D=128, dtype=torch.bfloat16, causal=True),   # some splits see no key
     dict(B=1, Sq=1, Sk=9000, Hq=16, Hkv=4, D=256, dtype=torch.bfloat16, causal=False),    # decode, head dim 256
     dict(B=1, Sq=384, Sk=2500, Hq=2, Hkv=2, D=192, dtype=torch.float16, causal=True, p=0.1),
+    # head dim 64: the bias tiles are staged through shared memory, also by the split items
+    dict(B=1, Sq=256, Sk=4096, Hq=2, Hkv=1, D=64, dtype=torch.bfloat16, causal=True, p=0.1, bias_heads=2),
+    dict(B=1, Sq=300, Sk=2048, Hq=2, Hkv=2, D=48, dtype=torch.float16, causal=False, bias_heads=1),
 ])
 def test_split_kv_low_occupancy_problems(case):
     """Problems with few (batch, head, query tile) items are cut along the key sequence and merged
@@ -271,6 +274,15 @@ def test_split_kv_low_occupancy_problems(case):
                                         dropout_p=p, dropout_seed=5, out_dtype=torch.float32)
         for mine, want in zip(grads, ref):
             assert rel_l2(mine.cpu(), want) <= GRAD_TOL
+        if p > 0:
+            # the record of the keep bits written by split items serves the backward like any other
+            bits = J.dropout_bits_buffer(dev(q), dev(k), p)
+            o_r, l_r = J.fwd_attention_kernel_call(dev(q), dev(k), dev(v), None, dev(bias), None, p, causal, 5,
+                                                   dropout_bits=bits)
+            assert torch.equal(o_r, o_s)
+            g_r = J.bwd_attention_kernel_call(dev(do), dev(q), dev(k), dev(v), dev(bias), None, o_s, l_s, p, causal,
+                                              None, 5, dropout_bits=bits)
+            assert torch.equal(g_r[1], grads[1]) and torch.equal(g_r[2], grads[2])
 
 
 def _fuzz_cases(n, seed):
@@ -350,6 +362,40 @@ def test_gqa_groups(G):
 @pytest.mark.parametrize("causal", [False, True])
 def test_bias_mask_dropout(bias_heads, mask_kind, p, causal):
     run_case(2, 256, 320, 4, 2, 64, torch.bfloat16, causal, bias_heads=bias_heads, mask_kind=mask_kind, p=p)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bias_shape,mask_shape", [
+    ((2, 4, 256, 320), None), ((1, 1, 256, 320), (2, 1, 256, 320)), ((2, 2, 256, 320), (1, 4, 256, 320)),
+])
+def test_staged_score_terms_every_broadcast_pattern(dtype, bias_shape, mask_shape):
+    """Head dim 64 streams 16-bit bias / mask tiles through shared memory (forward: per-warp TMA
+    rings, backward: one tile per step). Every broadcast pattern of the two terms (batch 1 or B;
+    heads 1, Hkv or Hq), both dtypes, with dropout on top, against the oracle."""
+    J = _J()
+    B, Sq, Sk, Hq, Hkv, D, p, seed = 2, 256, 320, 4, 2, 64, 0.1, 8
+    q, k, v, do = W.make_qkv(B, Sq, Sk, Hq, Hkv, D, dtype, D ** -0.25)
+    g = torch.Generator().manual_seed(6)
+    bias = (0.5 * torch.randn(*bias_shape, generator=g)).to(dtype)
+    mask = None
+    if mask_shape is not None:
+        mask = torch.zeros(*mask_shape, dtype=dtype)
+        mask.masked_fill_(torch.rand(*mask_shape, generator=g) < 0.2, float("-inf"))
+        mask[..., 0] = 0
+    dev = lambda x: None if x is None else x.cuda()
+    out, lse = J.fwd_attention_kernel_call(dev(q), dev(k), dev(v), dev(mask), dev(bias), None, p, True, seed)
+    dq, dk, dv = J.bwd_attention_kernel_call(dev(do), dev(q), dev(k), dev(v), dev(bias), dev(mask), out, lse, p, True,
+                                             None, seed)
+    assert J.device_status() == 0
+    kw = dict(bias=bias, mask=mask, causal=True, dropout_p=p, dropout_seed=seed)
+    blk = BlockAttention()
+    ro, rl = blk.forward(q, k, v, **kw)
+    assert (out.cpu().float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
+    fin = torch.isfinite(rl)
+    assert (lse.cpu()[:, :, :Sq][fin] - rl[fin]).abs().max().item() <= LSE_TOL
+    ref = blk.backward(do, q, k, v, out.cpu(), lse.cpu()[:, :, :Sq], out_dtype=torch.float32, **kw)
+    for name, mine, want in zip(("dq", "dk", "dv"), (dq, dk, dv), ref):
+        assert rel_l2(mine.cpu(), want) <= GRAD_TOL, (name, rel_l2(mine.cpu(), want))
 
 
 def test_bias_misaligned_rows_take_the_scalar_path():
