@@ -142,7 +142,7 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
                    ffi::AnyBuffer offsets, float softmax_scale, float dropout_p, bool causal,
                    int64_t dropout_seed, int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
                    ffi::Result<ffi::AnyBuffer> o, ffi::Result<ffi::AnyBuffer> lse,
-                   ffi::Result<ffi::AnyBuffer> workspace) {
+                   ffi::Result<ffi::AnyBuffer> dropout_bits, ffi::Result<ffi::AnyBuffer> workspace) {
   if (!AbiMatches()) return ffi::Error::InvalidArgument("fa2_b200_fwd: libfa2_b200.so has another ABI version");
   fa2_fwd_params a = {};
   if (!Problem(q, k, causal, softmax_scale, dropout_p, dropout_seed, batch_offset, head_offset,
@@ -160,6 +160,12 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
   a.seqlens = SeqlensOrNull(seqlens, a.p.batch);
   a.dropout_seed_dev = SeedOrNull(seed);
   a.offsets_dev = OffsetsOrNull(offsets);
+  // record of the dropout keep bits for the backward: a uint32 result of
+  // fa2_dropout_bits_bytes(problem) / 4 elements, or a one-element dummy when it is not wanted
+  if (dropout_bits->element_type() == ffi::DataType::U32 && dropout_bits->element_count() > 1) {
+    a.dropout_bits = static_cast<uint32_t*>(dropout_bits->untyped_data());
+    a.dropout_bits_bytes = static_cast<size_t>(dropout_bits->element_count()) * 4;
+  }
   // scratch for split-KV: a uint8 result of fa2_fwd_workspace_bytes(problem) + kScratchSlack bytes
   // (just the slack when the problem is not split); fa2_fwd ignores scratch that is too small
   const Scratch ws = AlignedScratch(workspace->untyped_data(), static_cast<size_t>(workspace->element_count()));
@@ -172,7 +178,7 @@ ffi::Error FwdImpl(cudaStream_t stream, ffi::AnyBuffer q, ffi::AnyBuffer k, ffi:
 ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ffi::AnyBuffer k,
                    ffi::AnyBuffer v, ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer o,
                    ffi::AnyBuffer lse, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed, ffi::AnyBuffer offsets,
-                   float softmax_scale, float dropout_p, bool causal, int64_t dropout_seed,
+                   ffi::AnyBuffer dropout_bits, float softmax_scale, float dropout_p, bool causal, int64_t dropout_seed,
                    int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
                    ffi::Result<ffi::AnyBuffer> dq, ffi::Result<ffi::AnyBuffer> dk,
                    ffi::Result<ffi::AnyBuffer> dv, ffi::Result<ffi::AnyBuffer> dbias,
@@ -213,6 +219,10 @@ ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ff
   a.seqlens = SeqlensOrNull(seqlens, a.p.batch);
   a.dropout_seed_dev = SeedOrNull(seed);
   a.offsets_dev = OffsetsOrNull(offsets);
+  if (dropout_bits.element_type() == ffi::DataType::U32 && dropout_bits.element_count() > 1) {
+    a.dropout_bits = static_cast<const uint32_t*>(dropout_bits.untyped_data());
+    a.dropout_bits_bytes = static_cast<size_t>(dropout_bits.element_count()) * 4;
+  }
   if (fa2_bwd(&a, stream) != FA2_OK) return Failed("fa2_b200_bwd");
   return ffi::Error::Success();
 }
@@ -240,6 +250,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Attr<int32_t>("heads_q_global")
         .Ret<ffi::AnyBuffer>()    // o
         .Ret<ffi::AnyBuffer>()    // lse
+        .Ret<ffi::AnyBuffer>()    // dropout bits: uint32 record for the backward (or a one-element dummy)
         .Ret<ffi::AnyBuffer>());  // workspace (uint8)
 
 XLA_FFI_DEFINE_HANDLER_SYMBOL(
@@ -257,6 +268,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Arg<ffi::AnyBuffer>()   // seqlens
         .Arg<ffi::AnyBuffer>()   // seed
         .Arg<ffi::AnyBuffer>()   // offsets
+        .Arg<ffi::AnyBuffer>()   // dropout bits written by the forward (or a one-element dummy)
         .Attr<float>("softmax_scale")
         .Attr<float>("dropout_p")
         .Attr<bool>("causal")

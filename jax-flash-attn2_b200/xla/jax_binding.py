@@ -46,7 +46,7 @@ class _Problem(ctypes.Structure):   # fa2_problem of include/fa2_b200.h
     ]
 
 
-for _fn in (_core.fa2_bwd_workspace_bytes, _core.fa2_fwd_workspace_bytes):
+for _fn in (_core.fa2_bwd_workspace_bytes, _core.fa2_fwd_workspace_bytes, _core.fa2_dropout_bits_bytes):
     _fn.restype = ctypes.c_size_t
     _fn.argtypes = [ctypes.POINTER(_Problem)]
 
@@ -74,6 +74,13 @@ def _fwd_workspace_bytes(q_shape, k_shape, dtype, dropout_prob) -> int:
     (nothing for most problems: only the alignment slack is declared then)."""
     n = int(_core.fa2_fwd_workspace_bytes(ctypes.byref(_problem(q_shape, k_shape, dtype, dropout_prob))))
     return n + _SCRATCH_SLACK
+
+
+def _dropout_bits_words(q_shape, k_shape, dtype, dropout_prob, max_bytes=1 << 30) -> int:
+    """Elements of the uint32 record of dropout keep bits the forward writes for the backward (1: no
+    record, the backward draws the bits again: no dropout, or a record above max_bytes)."""
+    n = int(_core.fa2_dropout_bits_bytes(ctypes.byref(_problem(q_shape, k_shape, dtype, dropout_prob))))
+    return n // 4 if 0 < n <= max_bytes else 1
 
 
 def _operands(q, bias, attention_mask):
@@ -124,7 +131,7 @@ def _attrs(q, softmax_scale, dropout_prob, causal, dropout_seed, heads_q_global)
 
 def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_scale=None,
                                dropout_prob=0.0, causal=False, dropout_seed=None, varlen_mode=True,
-                               *, offsets=None, heads_q_global=None):
+                               *, offsets=None, heads_q_global=None, return_dropout_bits=False):
     del varlen_mode
     assert q.shape[2] % k.shape[2] == 0, f"nheads_q = {q.shape[2]} is not divisible by nheads_kv = {k.shape[2]}"
     assert q.dtype == k.dtype == v.dtype, "All tensors must have the same type"
@@ -135,17 +142,20 @@ def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_
     out_types = (
         jax.ShapeDtypeStruct(q.shape, q.dtype),
         jax.ShapeDtypeStruct((batch, hq, -(-sq // 128) * 128), jnp.float32),
+        jax.ShapeDtypeStruct((_dropout_bits_words(q.shape, k.shape, q.dtype, dropout_prob),), jnp.uint32),
         jax.ShapeDtypeStruct((_fwd_workspace_bytes(q.shape, k.shape, q.dtype, dropout_prob),), jnp.uint8),
     )
-    out, lse, _ = jax.ffi.ffi_call("fa2_b200_fwd", out_types)(
+    out, lse, bits, _ = jax.ffi.ffi_call("fa2_b200_fwd", out_types)(
         q, k, v, bias_, mask_, seqlens, seed_op, _offsets_operand(q, offsets),
         **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, heads_q_global))
+    if return_dropout_bits:
+        return out, lse, bits
     return out, lse
 
 
 def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_prob, causal,
                                softmax_scale, dropout_seed, varlen_mode=True, *, offsets=None,
-                               heads_q_global=None, bias_grad=False):
+                               heads_q_global=None, bias_grad=False, dropout_bits=None):
     del varlen_mode
     bias_, mask_, seqlens = _operands(q, bias, attention_mask)
     seed_op, seed_attr = _seed_operand(q, dropout_seed)
@@ -159,6 +169,7 @@ def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_
     )
     dq, dk, dv, dbias, _ = jax.ffi.ffi_call("fa2_b200_bwd", out_types)(
         dO, q, k, v, bias_, mask_, o, M, seqlens, seed_op, _offsets_operand(q, offsets),
+        jnp.zeros((1,), jnp.uint32) if dropout_bits is None else dropout_bits,
         **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, heads_q_global))
     return dq, dk, dv, (dbias.astype(bias.dtype) if want_dbias else None)
 
@@ -178,17 +189,18 @@ def flash_attention_call(q, k, v, attention_mask=None, bias=None, softmax_scale=
 
 def _vjp_fwd(q, k, v, attention_mask, bias, softmax_scale, dropout_prob, causal, dropout_seed, varlen_mode,
              offsets, heads_q_global, bias_grad):
-    out, lse = _fwd_attention_kernel_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob,
-                                          causal, dropout_seed, varlen_mode, offsets=offsets,
-                                          heads_q_global=heads_q_global)
-    return out, (q, k, v, bias, attention_mask, out, lse, dropout_seed, offsets)
+    out, lse, bits = _fwd_attention_kernel_call(q, k, v, attention_mask, bias, softmax_scale, dropout_prob,
+                                                causal, dropout_seed, varlen_mode, offsets=offsets,
+                                                heads_q_global=heads_q_global, return_dropout_bits=True)
+    # one residual more than the reference keeps: the record of the dropout keep bits
+    return out, (q, k, v, bias, attention_mask, out, lse, dropout_seed, offsets, bits)
 
 
 def _vjp_bwd(softmax_scale, dropout_prob, causal, varlen_mode, heads_q_global, bias_grad, residual, dO):
-    q, k, v, bias, attention_mask, out, lse, dropout_seed, offsets = residual
+    q, k, v, bias, attention_mask, out, lse, dropout_seed, offsets, bits = residual
     dq, dk, dv, dbias = _bwd_attention_kernel_call(
         dO, q, k, v, bias, attention_mask, out, lse, dropout_prob, causal, softmax_scale, dropout_seed,
-        varlen_mode, offsets=offsets, heads_q_global=heads_q_global, bias_grad=bias_grad)
+        varlen_mode, offsets=offsets, heads_q_global=heads_q_global, bias_grad=bias_grad, dropout_bits=bits)
     # cotangents of (q, k, v, attention_mask, bias, dropout_seed, offsets)
     return dq, dk, dv, None, dbias, None, None
 
