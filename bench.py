@@ -378,10 +378,20 @@ def main():
     barrier()
 
     # ---- timed region: K steps of fwd + bwd, device-resident inputs ----------------------------
+    # An event between the forward and the backward of every step gives the forward's share inside
+    # the step (the forward-only loop further down runs in another power state).
+    marks = [(ev(), ev()) for _ in range(args.steps)]
+    def marked_steps():
+        for m0, m1 in marks:
+            m0.record()
+            o_, lse_ = fwd_call(J, x)
+            m1.record()
+            bwd_call(J, x, o_, lse_)
     sampler = ClockSampler(gpu_index)
     sampler.start()
-    ms_step = time_steps(step, args.steps)
+    ms_step = time_steps(marked_steps, 1) / args.steps
     clocks = sampler.stop()
+    ms_fwd_in_step = max_over_ranks(statistics.mean(m0.elapsed_time(m1) for m0, m1 in marks))
     status = J.device_status()
 
     # ---- forward alone, and the kernels of the backward (same K, separate loops) ---------------
@@ -584,6 +594,9 @@ def main():
             "fwd_bwd_tflops": value / world,
             "fwd_tflops": fwd_tflops / world,
             "fwd_ms": ms_fwd,
+            "fwd_in_step_ms": ms_fwd_in_step,
+            "fwd_in_step_tflops": f_fwd / (ms_fwd_in_step * 1e-3) / 1e12,
+            "fwd_in_step_frac_of_peak": f_fwd / (ms_fwd_in_step * 1e-3) / 1e12 / peak_burst,
             "bwd_pre_ms": statistics.mean(pre_ms),
             "bwd_main_ms": ms_main,
             "bwd_dq_convert_ms": statistics.mean(conv_ms),
