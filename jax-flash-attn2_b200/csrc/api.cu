@@ -309,7 +309,7 @@ SplitPlan plan_splits(const fa2_problem& p, const HeadDim& hd, bool pack_heads) 
     return s;
   }
   const size_t rows = static_cast<size_t>(s.n_splits) * p.batch * s.sq_k * s.hq_k;
-  s.part_o_bytes = align_up(rows * p.head_dim * 2, 256);
+  s.part_o_bytes = align_up(rows * hd.padded * sizeof(float), 256);
   s.part_lse_off = s.part_o_bytes;
   const size_t sq_pad = static_cast<size_t>((s.sq_k + 127) / 128) * 128;
   s.total = s.part_lse_off + align_up(static_cast<size_t>(s.n_splits) * p.batch * s.hq_k * sq_pad * 4, 256);
@@ -392,31 +392,22 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
     causal = false;
   }
   // Split-KV: the kernel writes per-split partial results into the workspace (as batch elements
-  // split * B + b of a contiguous [n_splits * B, Sq, Hq, D] output and its lse), merged afterwards.
+  // split * B + b of a contiguous fp32 [n_splits * B, Sq, Hq, kernel head dim] output and its lse),
+  // merged afterwards; o itself is written by the merge alone.
   SplitPlan sp = plan_splits(p, hd, pack_heads);
   if (sp.n_splits > 1 && (!a->workspace || a->workspace_bytes < sp.total ||
                           (reinterpret_cast<uintptr_t>(a->workspace) & (kWorkspaceAlign - 1))))
     sp.n_splits = 1;   // not enough scratch: run unsplit
   const bool split = sp.n_splits > 1;
   uint8_t* ws = static_cast<uint8_t*>(a->workspace);
-  void* o_ptr = a->o;
-  int o_batch = p.batch;
-  const fa2_strides o_final = o_st;
-  if (split) {
-    o_ptr = ws;
-    o_batch = sp.n_splits * p.batch;
-    o_st.h = p.head_dim;
-    o_st.s = static_cast<int64_t>(hq_k) * p.head_dim;
-    o_st.b = static_cast<int64_t>(sq_k) * o_st.s;
-  }
   // head dim 256: K arrives in halves of the head dim, V in halves of the 128 key rows
   if ((rc = make_tmap(&L.tmQ, a->q, bf16, p.batch, sq_k, hq_k, hd, q_st, 128, "q")) ||
       (rc = make_tmap(&L.tmK, a->k, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->k_strides, 128, "k",
                       D == 256 ? 4 / kKV256Parts : 0)) ||
       (rc = make_tmap(&L.tmV, a->v, bf16, p.batch, p.seqlen_k, p.heads_kv, hd, a->v_strides,
                       D == 256 ? 128 / kKV256Parts : 128, "v")) ||
-      (rc = make_tmap(&L.tmO, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
-      (rc = make_tmap(&L.tmO1, o_ptr, bf16, o_batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
+      (rc = make_tmap(&L.tmO, a->o, bf16, p.batch, sq_k, hq_k, hd, o_st, 128, "o")) ||
+      (rc = make_tmap(&L.tmO1, a->o, bf16, p.batch, sq_k, hq_k, hd, o_st, 128, "o", 1)))
     return rc;
 
   FwdKernelParams& kp = L.kp;
@@ -427,10 +418,12 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
   kp.lse = a->lse; kp.lse_sb = a->lse_stride_b; kp.lse_sh = lse_sh; kp.lse_sq = lse_sq;
   kp.n_splits = 1;
   kp.split_tiles = 0;
+  kp.part_o = nullptr;
   const int sq_pad = (sq_k + 127) / 128 * 128;
   if (split) {
     kp.n_splits = sp.n_splits;
     kp.split_tiles = sp.split_tiles;
+    kp.part_o = reinterpret_cast<float*>(ws);
     kp.lse = reinterpret_cast<float*>(ws + sp.part_lse_off);
     kp.lse_sq = 1;
     kp.lse_sh = sq_pad;
@@ -468,13 +461,15 @@ int fa2_fwd(const fa2_fwd_params* a, void* cuda_stream) {
     return fail(FA2_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
   if (split) {
     FwdCombine c{};
-    c.part_o = ws;
+    c.part_o = reinterpret_cast<const float*>(ws);
     c.part_lse = reinterpret_cast<const float*>(ws + sp.part_lse_off);
     c.o = a->o;
-    c.o_strides[0] = o_final.b; c.o_strides[1] = o_final.s; c.o_strides[2] = o_final.h;
+    c.o_strides[0] = o_st.b; c.o_strides[1] = o_st.s; c.o_strides[2] = o_st.h;
     c.lse = a->lse;
     c.lse_sb = a->lse_stride_b; c.lse_sh = lse_sh; c.lse_sq = lse_sq;
     c.n_splits = sp.n_splits; c.B = p.batch; c.Sq = sq_k; c.Hq = hq_k; c.D = p.head_dim;
+    c.D_part = D;
+    c.d_blk = hd.blk;
     c.sq_pad = sq_pad;
     c.bf16 = bf16;
     e = launch_fwd_combine(c, static_cast<cudaStream_t>(cuda_stream));

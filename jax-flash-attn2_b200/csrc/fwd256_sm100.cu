@@ -272,7 +272,7 @@ fwd256_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
       epilogue_row<kD, kBf16, kFeat>(tO, nt > 0, smem_gen + L::kQOff, r, p, b_out, h, qi, sc, m, l);
     }
     named_bar_sync(1, kBM);
-    if (ok && r == 0 && !*abort_flag) {
+    if (ok && r == 0 && !*abort_flag && !p.part_o) {
       tma_store_5d(&tmO, sQ, 0, q0, 0, h, b_out);
       tma_store_commit();
       tma_store_wait_read0();

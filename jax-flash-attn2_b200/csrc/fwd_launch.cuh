@@ -27,13 +27,15 @@ struct FwdLaunch {
 //   part_o   [n_splits, B, Sq, Hq, D]  normalised partial outputs (the q dtype, contiguous)
 //   part_lse [n_splits, B, Hq, sq_pad] natural-log lse of every split (-inf: the split saw no key)
 struct FwdCombine {
-  const void* part_o;
+  const float* part_o;        // [n_splits * B][Sq][Hq][D_part], fp32
   const float* part_lse;
   void* o;
   long long o_strides[3];     // (batch, sequence, head) element strides of o
   float* lse;
   long long lse_sb, lse_sh, lse_sq;
   int n_splits, B, Sq, Hq, D, sq_pad;
+  int D_part;                 // row length of part_o: the kernel's (padded) head dim
+  int d_blk;                  // real columns in each 64-column block of a part_o row
   bool bf16;
 };
 cudaError_t launch_fwd_combine(const FwdCombine& c, cudaStream_t stream);

@@ -264,8 +264,24 @@ __device__ __forceinline__ void softmax_tile_row(uint32_t tS, uint32_t tO, int j
   l += (l0 + l1) + (l2 + l3);
 }
 
+// Split-KV: N scaled accumulator values of this thread's row go to the fp32 partial buffer.
+template <int N>
+__device__ __forceinline__ void store_partial_row(float* dst, const uint32_t (&o)[N], float inv) {
+#pragma unroll
+  for (int c = 0; c < N / 4; ++c)
+    reinterpret_cast<float4*>(dst)[c] =
+        make_float4(__uint_as_float(o[4 * c + 0]) * inv, __uint_as_float(o[4 * c + 1]) * inv,
+                    __uint_as_float(o[4 * c + 2]) * inv, __uint_as_float(o[4 * c + 3]) * inv);
+}
+// Row `qi` of head `h`, "batch element" `b` (split * B + b) in the fp32 partial buffer.
+template <int D>
+__device__ __forceinline__ float* partial_row(const FwdKernelParams& p, int b, int h, int qi) {
+  return p.part_o + ((static_cast<long long>(b) * p.Sq + qi) * p.Hq + h) * D;
+}
+
 // Final scaling of this thread's output row: O / l (and 1/(1-p)) -> 16 bit -> 128-byte-swizzled
-// tile in shared memory at `so_gen` (D/64 blocks of [128][64]); stores the row's log-sum-exp.
+// tile in shared memory at `so_gen` (D/64 blocks of [128][64]), or, for a split-KV part, in fp32
+// straight to the partial buffer; stores the row's log-sum-exp.
 template <int D, bool kBf16, bool kFeat>
 __device__ __forceinline__ void epilogue_row(uint32_t tO, bool has_acc, uint8_t* so_gen, int r,
                                              const FwdKernelParams& p, int b, int h, int qi, float sc,
@@ -285,6 +301,10 @@ __device__ __forceinline__ void epilogue_row(uint32_t tO, bool has_acc, uint8_t*
     } else {
 #pragma unroll
       for (int k = 0; k < 32; ++k) o[k] = 0u;
+    }
+    if (p.part_o) {
+      if (qi < p.Sq) store_partial_row(partial_row<D>(p, b, h, qi) + c * 32, o, inv);
+      continue;
     }
     // 32 columns = 64 bytes = four 16-byte chunks of this row's 128-byte line
     uint8_t* line = so_gen + (c >> 1) * kBlockBytes + r * 128;

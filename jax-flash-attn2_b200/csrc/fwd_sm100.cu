@@ -473,6 +473,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
 
       // ---- epilogue: O / l -> 16 bit -> swizzled shared memory -> TMA store; LSE -------------
+      // (a split-KV part instead goes to the partial buffer in fp32, row by row)
       if (ok) ok = mbar_wait(bar_o_full(t), o_cnt & 1u, abort_flag);   // once per item, work or not
       ++o_cnt;
       // One 64-column block at a time through this tile's 16 KiB staging block. O_t is handed
@@ -499,11 +500,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           mbar_arrive(bar_o_free(t));
         }
         if (ok && tile_valid) {
-          epilogue_block<kBf16>(o, stage_gen, r, inv);
-          fence_proxy_async_smem();
+          if (p.part_o) {   // split-KV part: fp32, rounded to 16 bit once, by the merge
+            if (qi < p.Sq) store_partial_row(partial_row<D>(p, b_out, h, qi) + blk * 64, o, inv);
+          } else {
+            epilogue_block<kBf16>(o, stage_gen, r, inv);
+            fence_proxy_async_smem();
+          }
         }
         named_bar_sync(1 + t, kBM);
-        if (ok && tile_valid && r == 0 && !*abort_flag) {
+        if (ok && tile_valid && r == 0 && !*abort_flag && !p.part_o) {
           tma_store_5d(&tmO1, sO + t * L::kBlockBytes, 0, it.q0 + t * kBM, blk, h, b_out);
           tma_store_commit();
         }

@@ -86,6 +86,9 @@ struct FwdKernelParams {
   // "batch element" s * B + b of the partial buffers that o / lse then point to.
   int n_splits;         // >= 1
   int split_tiles;
+  // Split-KV only, else null: the partial outputs in fp32, contiguous
+  // [n_splits * B][Sq][Hq][kernel head dim]; the 16-bit output is then written by the merge alone.
+  float* part_o;
   int* status;          // device status word (bounded-wait time-outs)
 };
 

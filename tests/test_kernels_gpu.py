@@ -265,6 +265,10 @@ def test_split_kv_low_occupancy_problems(case):
         assert (o.cpu().float() - ro.float()).abs().max().item() <= OUT_TOL[dtype]
         assert (l.cpu()[:, :, :Sq] - rl).abs().max().item() <= LSE_TOL
     assert (o_s.float() - o_u.float()).abs().max().item() <= OUT_TOL[dtype] / 2
+    # The parts are kept and merged in fp32 and rounded to 16 bit once. What separates split from
+    # unsplit is then the rounding of P against different running maxima: about one last place
+    # of the 16-bit type (measured 2.8e-3 bf16, 3.7e-4 fp16 on these cases).
+    assert rel_l2(o_s.cpu(), o_u.cpu().float()) <= {torch.bfloat16: 5e-3, torch.float16: 7e-4}[dtype]
     if Sq > 1:
         # the merged output and lse feed the backward like those of an unsplit forward
         do = torch.randn(B, Sq, Hq, D, generator=g).to(dtype)
