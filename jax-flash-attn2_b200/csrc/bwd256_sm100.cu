@@ -654,7 +654,7 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax,
-      a.head_dim_real, kp.seqlens);
+      a.head_dim_real, kp.seqlens, nullptr, 0.f);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   mark(1);

@@ -1,6 +1,7 @@
 // Pieces shared by the backward kernels of all head dims: bulk-copy wrappers, the fp16 cotangent
 // scale, score-term loads and the pre-pass kernel.
 #pragma once
+#include <cuda_bf16.h>
 #include "kernel_params.cuh"
 #include "ptx_sm100.cuh"
 
@@ -137,6 +138,28 @@ __device__ __forceinline__ void add_bias_grad(const ScoreGradDev& g, int b, int 
 // ---------------------------------------------------------------------------------------------
 // stats layout: [B, Hq, nQ, 2, 128] float: (-lse * log2e | -inf for rows that take no gradient,
 // delta). dq_acc layout: [B, Hq, nQ, D/4, 128, 4] float.
+//
+// xstats (optional, bf16 kernels without score terms): the same two statistics as operand tiles
+// for the tensor cores, so that the main kernel adds them to its accumulators with one MMA k-step
+// each instead of every thread loading all 128 of them from shared memory in every step (a
+// broadcast load moves 4 bytes per shared-memory cycle: 4 KiB per step over the 8 warps, a fifth
+// of the shared-memory cycles of a kernel that is bound by them). Per (batch, head, query tile)
+// one [128 rows][16] bf16 tile in the unswizzled K-major core-matrix layout (row r: 16 bytes at
+// (r / 8) * 256 + (r % 8) * 16 for columns 0-7, the same + 128 for columns 8-15). Row r holds
+//   columns 0-2:  -lse / softmax_scale as a sum of three bf16 terms (24 mantissa bits),
+//   columns 8-10: -delta, likewise,    all other columns: zero.
+// Multiplied by a tile of ones in columns 0-2 (or 8-10) this adds -lse / scale to every S^T entry
+// of the row's query (so P = exp2(scale * log2e * S')), or -delta to every dP^T entry.
+__device__ __forceinline__ void split3_bf16(float x, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
+  const __nv_bfloat16 h = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(h);
+  const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+  const __nv_bfloat16 l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+  hi = __bfloat16_as_ushort(h);
+  mid = __bfloat16_as_ushort(m);
+  lo = __bfloat16_as_ushort(l);
+}
+
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(128)
 bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
@@ -144,7 +167,7 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                long long do_sh, const float* __restrict__ lse, long long lse_sb, long long lse_sh,
                float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ,
                unsigned* __restrict__ do_absmax_bits, int d_real,
-               const int* __restrict__ seqlens) {
+               const int* __restrict__ seqlens, uint4* __restrict__ xstats, float inv_scale_log2) {
   // one-dimensional grid (the y and z extents of a grid stop at 65535): tile index fastest
   const int i = blockIdx.x % nQ;
   const int bh = blockIdx.x / nQ;
@@ -191,6 +214,16 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
       }
       st[r] = l2;
       st[128 + r] = (row < sq_b) ? acc : 0.f;
+      if (xstats != nullptr) {
+        // a row without gradient gets a finite, huge negative shift: exp2 of it is 0, and the
+        // zero columns of the ones tile still multiply it to 0 rather than to NaN
+        uint32_t lh, lm, ll, dh, dm, dl;
+        split3_bf16(l2 > -INFINITY ? l2 * inv_scale_log2 : -1e30f, lh, lm, ll);
+        split3_bf16((row < sq_b) ? -acc : 0.f, dh, dm, dl);
+        uint4* xr = xstats + tile * 256 + (r >> 3) * 16 + (r & 7);
+        xr[0] = make_uint4(lh | (lm << 16), ll, 0u, 0u);
+        xr[8] = make_uint4(dh | (dm << 16), dl, 0u, 0u);
+      }
     }
   }
   float4* acc4 = reinterpret_cast<float4*>(dq_acc + tile * (kBM * D));

@@ -55,7 +55,16 @@ struct BwdRoles {
 // at the very start of a step) instead of being gathered column by column from global memory, and
 // when the caller hands over the forward's record of the dropout keep bits, the step's 2 KiB of it
 // arrive with the Q tile, so that no Philox round runs in the backward.
-template <int D, bool kStaged = false>
+//
+// kFold (bf16, no score terms, head dim 128): the row statistics arrive as a [128 queries][16] bf16
+// operand tile per step and are added to S^T and dP^T by one extra MMA k-step each against
+// constant ones (see bwd_pre_kernel), so the P / dS threads load no statistics at all. The ones
+// are three 128-byte core matrices (ones in columns 0-2 | zeros | ones in columns 0-2) that a
+// descriptor with a zero row-group stride repeats down all 128 rows: started at the first one it
+// selects columns 0-2 of the statistics tile, started at the second one columns 8-10. The 8 KiB of
+// the two statistics stages come out of the dQ staging, which becomes a ring of three eighths of a
+// tile instead of two quarters.
+template <int D, bool kStaged = false, bool kFold = false>
 struct BwdSmem {
   static constexpr int kTileBytes = 128 * D * 2;
   static constexpr int kBlockBytes = 128 * 128;   // one [128 rows][64 elements] block
@@ -63,13 +72,20 @@ struct BwdSmem {
   static constexpr int kVOff = kKOff + kTileBytes;
   static constexpr int kQOff = kVOff + kTileBytes;         // 2 stages
   static constexpr int kdOOff = kQOff + 2 * kTileBytes;    // 1 stage
-  // dQ leaves through two staging chunks of [D/16][128 rows][4 floats] (a quarter tile each)
-  static constexpr int kChunkBytes = kTileBytes / 2;
+  // dQ leaves through two staging chunks of [D/4/kChunks][128 rows][4 floats]
+  static constexpr int kChunks = kFold ? 8 : 4;            // chunks per fp32 tile
+  static constexpr int kStageBufs = kFold ? 3 : 2;
+  static constexpr int kChunkBytes = 2 * kTileBytes / kChunks;
   static constexpr int kStageOff = kdOOff + kTileBytes;
-  static constexpr int kdSOff = kStageOff + 2 * kChunkBytes;   // [128 keys][128 queries] 16 bit
-  static constexpr int kStatsOff = kdSOff + 128 * 128 * 2; // 2 stages x (lse2[128], delta[128])
+  static constexpr int kdSOff = kStageOff + kStageBufs * kChunkBytes;   // [128 keys][128 queries] 16 bit
+  // 2 stages x (lse2[128], delta[128]) floats; kFold: 2 stages x one statistics tile, then the
+  // three core matrices of the ones operand
+  static constexpr int kStatsOff = kdSOff + 128 * 128 * 2;
+  static constexpr int kFoldTileBytes = 128 * 16 * 2;
+  static constexpr int kStatsStage = kFold ? kFoldTileBytes : 1024;
+  static constexpr int kOnesOff = kStatsOff + 2 * kStatsStage;
   static constexpr int kTermBytes = 128 * 128 * 2;          // one term tile: two [128 q][64 keys] blocks
-  static constexpr int kTermOff = kStatsOff + 2 * 1024;     // bias tile, mask tile
+  static constexpr int kTermOff = kOnesOff + (kFold ? 512 : 0);   // bias tile, mask tile
   // recorded dropout bits of a step's (query tile, key tile): [4 words][128 queries], 2 stages
   static constexpr int kBitsBytes = 4 * 128 * 4;
   static constexpr int kBitsOff = kTermOff + (kStaged ? 2 * kTermBytes : 0);
@@ -146,7 +162,8 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
                 const float* __restrict__ stats, const BwdKernelParams p) {
   constexpr bool kStaged = kFeat && D == 64;
-  using L = BwdSmem<D, kStaged>;
+  constexpr bool kFold = kBf16 && !kFeat && D == 128;
+  using L = BwdSmem<D, kStaged, kFold>;
   using R = BwdRoles<D>;
   constexpr int kPW = R::kPW, kCW = R::kCW;
   constexpr int kWarpDrain = R::kWarpDrain, kWarpMma = R::kWarpMma, kWarpTma = R::kWarpTma;
@@ -237,6 +254,13 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (p.mask.staged) tma_prefetch_desc(&tmMask);
     }
   }
+  if constexpr (kFold) {
+    // three core matrices of 8 rows x 16 bytes: 1.0 (bf16) in columns 0-2 | zeros | like the first
+    if (tid < 24)
+      reinterpret_cast<uint4*>(smem_gen + L::kOnesOff)[tid] =
+          (tid >> 3) == 1 ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
+    fence_proxy_async_smem();
+  }
   if (warp == 0) {
     __syncwarp();
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
@@ -279,16 +303,21 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ok = mbar_wait(bar_q_empty(st), par, abort_flag);
         if (!ok) break;
         const bool with_bits = kStaged && p.drop.bits != nullptr;
-        mbar_arrive_expect_tx(bar_q_full(st), L::kTileBytes + 1024 + (with_bits ? L::kBitsBytes : 0));
+        mbar_arrive_expect_tx(bar_q_full(st), L::kTileBytes + L::kStatsStage + (with_bits ? L::kBitsBytes : 0));
         tma_load_5d(sQ + st * L::kTileBytes, &tmQ, bar_q_full(st), 0, i * kBM, 0, h, b);
         if constexpr (kStaged) {
           if (with_bits)
             bulk_load_1d(smem_base + L::kBitsOff + st * L::kBitsBytes, dropout_bits_block(p.drop, b, h, p.Hq, i, n),
                          L::kBitsBytes, bar_q_full(st));
         }
-        bulk_load_1d(sStats + st * 1024,
-                     stats + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * 256, 1024,
-                     bar_q_full(st));
+        if constexpr (kFold)
+          bulk_load_1d(sStats + st * L::kStatsStage,
+                       p.xstats + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * (L::kFoldTileBytes / 16),
+                       L::kFoldTileBytes, bar_q_full(st));
+        else
+          bulk_load_1d(sStats + st * 1024,
+                       stats + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * 256, 1024,
+                       bar_q_full(st));
         if constexpr (kStaged) {
           // the step's bias / mask tiles: their buffers were read at the start of the previous step
 #pragma unroll
@@ -331,20 +360,29 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint64_t ddO_k = make_sdesc(sdO, 16, 1024), ddO_mn = make_sdesc(sdO, L::kBlockBytes, 1024);
       const uint64_t ddS_k = make_sdesc(sdS, 16, 1024), ddS_mn = make_sdesc(sdS, L::kBlockBytes, 1024);
 
+      // kFold: the ones (A; every 8-row group reads the same core matrices) and the statistics
+      // tiles of the two stages (B), unswizzled
+      const uint64_t dOnes = make_sdesc_plain(smem_base + L::kOnesOff, 128, 0);
+      const uint64_t dStat = make_sdesc_plain(sStats, 128, 256);
+
       // D[kv, q] = A[kv, d] * B[q, d]^T, both operands K-major over the head dim; at D = 64 the A
-      // operand (K for S^T, V for dP^T) comes from tensor memory: 8 columns per 16 dims
-      auto issue_kd = [&](uint32_t d_col, uint64_t a_desc, uint64_t b_desc) {
+      // operand (K for S^T, V for dP^T) comes from tensor memory: 8 columns per 16 dims.
+      // kFold: the accumulator starts from the statistic of stage `st` (-lse / scale for S^T,
+      // -delta for dP^T), one k-step of ones times the statistics tile.
+      auto issue_kd = [&](uint32_t d_col, uint64_t a_desc, uint64_t b_desc, int st) {
+        if constexpr (kFold)
+          mma_ss_e(tmem_base + d_col, sdesc_advance(dOnes, d_col == kColS ? 0 : 128),
+                   sdesc_advance(dStat, st * L::kStatsStage), idesc_s, 0u);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;
+          const uint32_t acc = (kFold || k > 0) ? 1u : 0u;
           if constexpr (kKvInTmem) {
             const uint32_t a_col = (d_col == kColS ? kColKt : kColVt) + 8 * k;
-            mma_ts_e(tmem_base + d_col, tmem_base + a_col, sdesc_advance(b_desc, off), idesc_s,
-                     k > 0 ? 1u : 0u);
+            mma_ts_e(tmem_base + d_col, tmem_base + a_col, sdesc_advance(b_desc, off), idesc_s, acc);
             continue;
           }
-          mma_ss_e(tmem_base + d_col, sdesc_advance(a_desc, off), sdesc_advance(b_desc, off), idesc_s,
-                 k > 0 ? 1u : 0u);
+          mma_ss_e(tmem_base + d_col, sdesc_advance(a_desc, off), sdesc_advance(b_desc, off), idesc_s, acc);
         }
       };
       auto issue_dv = [&](bool first) {
@@ -379,13 +417,13 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (ok) ok = mbar_wait_warp(bar_q_full(0), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        issue_kd(kColS, dK_k, dQ_k0);
+        issue_kd(kColS, dK_k, dQ_k0, 0);
         mma_commit_e(bar_s_full);
         ok = mbar_wait_warp(bar_do_full, 0, abort_flag);
       }
       if (ok) {
         tc_fence_after();
-        issue_kd(kColdP, dV_k, ddO_k);
+        issue_kd(kColdP, dV_k, ddO_k, 0);
         mma_commit_e(bar_dp_full);
       }
       for (int it = 0; it < T && ok; ++it) {
@@ -402,7 +440,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ok = mbar_wait_warp(bar_q_full(nx), par_next, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          issue_kd(kColS, dK_k, sdesc_advance(dQ_k0, nx * L::kTileBytes));
+          issue_kd(kColS, dK_k, sdesc_advance(dQ_k0, nx * L::kTileBytes), nx);
           mma_commit_e(bar_s_full);
         }
         ok = mbar_wait_warp(bar_ds_full, par, abort_flag);
@@ -417,7 +455,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (ok) ok = mbar_wait_warp(bar_do_full, (it + 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          issue_kd(kColdP, dV_k, ddO_k);
+          issue_kd(kColdP, dV_k, ddO_k, nx);
           mma_commit_e(bar_dp_full);
         }
       }
@@ -432,15 +470,16 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tdQ = tmem_base + lane_base + kColdQ;
     bool ok = true;
+    uint32_t ring = 0;   // staging buffer of the next chunk
     for (int it = 0; it < T; ++it) {
       int h, i;
       step_coords(it, h, i);
       if (ok) ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
       if (!ok) {
         // No early exit: a thread that left alone would strand the other 127 at the (unbounded)
-        // named barriers of the staging loop. Keep in step with them: eight barriers per step.
+        // named barriers of the staging loop. Keep in step with them: two barriers per chunk.
 #pragma unroll 1
-        for (int k = 0; k < 8; ++k) named_bar_sync(3, 128);
+        for (int k = 0; k < 2 * L::kChunks; ++k) named_bar_sync(3, 128);
         continue;
       }
       tc_fence_after();
@@ -448,7 +487,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // early; the reductions (slow: they queue in the memory pipe) then overlap with the MMAs of
       // the next step. With four P/dS warpgroups the register file only leaves room for half a
       // D = 128 tile here, so the tile is taken in two parts and handed back after the second load.
-      // Each part leaves through the TMA unit in chunks of D/4 columns through two staging
+      // Each part leaves through the TMA unit in chunks of D/kChunks columns through two staging
       // buffers: cp.reduce.async.bulk adds a chunk to the global fp32 accumulator while the next
       // one is written. (Reductions issued from registers would queue in the memory pipe in front
       // of the tensor-memory traffic of the other warps.)
@@ -466,24 +505,30 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_before();
           mbar_arrive(bar_dq_drained);
         }
+        constexpr int kChunkVecs = D / 4 / L::kChunks;   // float4 columns per chunk
 #pragma unroll
-        for (int cl = 0; cl < 4 / kParts; ++cl) {
-          const int c = part * (4 / kParts) + cl;
-          const int buf = c & 1;
-          // at most one reduction may still be reading: the one from the other buffer
-          if (r == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        for (int cl = 0; cl < L::kChunks / kParts; ++cl) {
+          const int c = part * (L::kChunks / kParts) + cl;
+          const uint32_t buf = ring;
+          ring = (ring + 1 == L::kStageBufs) ? 0u : ring + 1;
+          // the reductions out of the other buffers may still be reading, not the one issued
+          // kStageBufs chunks ago out of this buffer
+          if (r == 0) {
+            if constexpr (L::kStageBufs == 3) asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          }
           named_bar_sync(3, 128);
           uint8_t* stage = smem_gen + L::kStageOff + buf * L::kChunkBytes;
 #pragma unroll
-          for (int c4 = 0; c4 < D / 16; ++c4) {
-            const int cc = cl * (D / 16) + c4;
+          for (int c4 = 0; c4 < kChunkVecs; ++c4) {
+            const int cc = cl * kChunkVecs + c4;
             *reinterpret_cast<uint4*>(stage + (c4 * 128 + r) * 16) =
                 make_uint4(v[4 * cc], v[4 * cc + 1], v[4 * cc + 2], v[4 * cc + 3]);
           }
           fence_proxy_async_smem();
           named_bar_sync(3, 128);
           if (r == 0) {
-            bulk_reduce_add_f32(dst_tile + c * (kBM * D / 4),
+            bulk_reduce_add_f32(dst_tile + c * (kBM * D / L::kChunks),
                                 smem_base + L::kStageOff + buf * L::kChunkBytes, L::kChunkBytes);
             tma_store_commit();
           }
@@ -559,7 +604,8 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float4* nlse4 = reinterpret_cast<const float4*>(stats_s + st * 256 + kCW * w);
       const float4* delta4 = nlse4 + 32;
       const int q_first = i * kBM + kCW * w;
-      ok = mbar_wait(bar_q_full(st), (it >> 1) & 1, abort_flag);
+      // (kFold: nothing of the Q stage is read by these threads, its statistics are in S^T already)
+      if constexpr (!kFold) ok = mbar_wait(bar_q_full(st), (it >> 1) & 1, abort_flag);
       if (ok) ok = mbar_wait(bar_s_full, it & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
@@ -626,7 +672,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
 #pragma unroll
         for (int c4 = 0; c4 < kCW / 4; ++c4) {
-          const float4 nl = nlse4[c4];
+          const float4 nl = kFold ? make_float4(0.f, 0.f, 0.f, 0.f) : nlse4[c4];
           const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
 #pragma unroll
           for (int k2 = 0; k2 < 2; ++k2) {
@@ -683,7 +729,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tc_wait_ld();
 #pragma unroll
         for (int c4 = 0; c4 < kCW / 4; ++c4) {
-          const float4 dl = delta4[c4];
+          const float4 dl = kFold ? make_float4(0.f, 0.f, 0.f, 0.f) : delta4[c4];
           const float dlv[4] = {dl.x, dl.y, dl.z, dl.w};
 #pragma unroll
           for (int k2 = 0; k2 < 2; ++k2) {
@@ -694,8 +740,8 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
               d0 = ((bits >> (c & 31)) & 1u) ? d0 * p.drop.inv_keep : 0.f;
               d1 = ((bits >> ((c + 1) & 31)) & 1u) ? d1 * p.drop.inv_keep : 0.f;
             }
-            float t0, t1;
-            add2(t0, t1, d0, d1, -dlv[2 * k2], -dlv[2 * k2 + 1]);
+            float t0 = d0, t1 = d1;
+            if constexpr (!kFold) add2(t0, t1, d0, d1, -dlv[2 * k2], -dlv[2 * k2 + 1]);
             if constexpr (!kBf16) fma2(t0, t1, t0, t1, do_scale, do_scale, 0.f, 0.f);
             const float p0 = unpack_lo<kBf16>(pk[c >> 1]), p1 = unpack_hi<kBf16>(pk[c >> 1]);
             dp[c >> 1] = pack2<kBf16>(p0 * t0, p1 * t1);     // reuse dp[0..kCW/2) for the packed dS
@@ -804,7 +850,7 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ, kBf16 ? nullptr : absmax,
-      a.head_dim_real, kp.seqlens);
+      a.head_dim_real, kp.seqlens, const_cast<uint4*>(kp.xstats), 1.f / kp.scale_log2);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);

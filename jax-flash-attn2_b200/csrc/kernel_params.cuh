@@ -118,6 +118,9 @@ struct BwdKernelParams {
   const float* lse;     // natural log, [B, Hq, >= Sq]
   long long lse_sb, lse_sh;
   const float* delta;   // rowsum(o * do), [B, Hq, Sq_pad]
+  // Row statistics as MMA operand tiles, or null: one [128 query rows][16] bf16 tile per (batch,
+  // head, query tile) that a rank-3 MMA adds to S^T and dP^T (see bwd_pre_kernel)
+  const uint4* xstats;
   float* dq_acc;        // fp32 [B, Hq, Sq_pad, D]
   int Sq_pad;           // Sq rounded up to 128
   ScoreTermDev bias, mask;

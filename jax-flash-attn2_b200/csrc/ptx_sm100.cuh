@@ -199,6 +199,13 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr, uint32_t lbo_byte
   return d;
 }
 
+// Descriptor of an operand tile without swizzle, K-major: 8-row x 16-byte core matrices, each 128
+// contiguous bytes; `lbo_bytes` apart along K, `sbo_bytes` apart along the rows (8-row groups).
+__device__ __forceinline__ uint64_t make_sdesc_plain(uint32_t saddr, uint32_t lbo_bytes,
+                                                     uint32_t sbo_bytes) {
+  return make_sdesc(saddr, lbo_bytes, sbo_bytes) & ~(static_cast<uint64_t>(7) << 61);
+}
+
 // The same descriptor for a start address `bytes` further on (bytes is a multiple of 16; the
 // address field cannot carry into the next field while the operand stays inside shared memory).
 __device__ __forceinline__ uint64_t sdesc_advance(uint64_t desc, uint32_t bytes) {
