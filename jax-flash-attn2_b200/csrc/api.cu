@@ -277,8 +277,8 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   split_head_dim(p.head_dim, &hd);   // checked by the callers
   w.absmax_off = w.dq_off + align_up(rows * hd.padded * sizeof(float), 256);
   w.xstats_off = w.absmax_off + 256;   // one word: max|dO| of the call (fp16 range guard)
-  // the row statistics once more as MMA operand tiles, 4 KiB per 128 rows (head dim 128, bf16)
-  const bool fold = hd.padded == 128 && p.dtype == FA2_BF16;
+  // the row statistics once more as MMA operand tiles, 4 KiB per 128 rows (head dim 128)
+  const bool fold = hd.padded == 128;
   w.total = w.xstats_off + (fold ? rows / 128 * 4096 : 0);
   return w;
 }
@@ -593,9 +593,9 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   L.head_dim = D;
   L.bf16 = bf16;
   L.causal = p.causal != 0;
-  // (the plain bf16 kernel divides the log-sum-exp by the scale once, in the pre-pass)
+  // (the plain head-dim-128 kernel divides the log-sum-exp by the scale once, in the pre-pass)
   L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled || !(std::fabs(p.softmax_scale) >= 1e-30f);
-  kp.xstats = (!L.feat && bf16 && D == 128) ? reinterpret_cast<const uint4*>(ws + w.xstats_off) : nullptr;
+  kp.xstats = (!L.feat && D == 128) ? reinterpret_cast<const uint4*>(ws + w.xstats_off) : nullptr;
   if (L.feat && D == 64) {
     // the head-dim-64 kernel brings 16-bit bias / mask tiles in through the TMA unit
     try_stage_term(&L.tmBias, &kp.bias, p, 128);

@@ -56,7 +56,7 @@ struct BwdRoles {
 // when the caller hands over the forward's record of the dropout keep bits, the step's 2 KiB of it
 // arrive with the Q tile, so that no Philox round runs in the backward.
 //
-// kFold (bf16, no score terms, head dim 128): the row statistics arrive as a [128 queries][16] bf16
+// kFold (no score terms, head dim 128): the row statistics arrive as a [128 queries][16] bf16
 // operand tile per step and are added to S^T and dP^T by one extra MMA k-step each against
 // constant ones (see bwd_pre_kernel), so the P / dS threads load no statistics at all. The ones
 // are three 128-byte core matrices (ones in columns 0-2 | zeros | ones in columns 0-2) that a
@@ -162,7 +162,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const __grid_constant__ CUtensorMap tmBias, const __grid_constant__ CUtensorMap tmMask,
                 const float* __restrict__ stats, const BwdKernelParams p) {
   constexpr bool kStaged = kFeat && D == 64;
-  constexpr bool kFold = kBf16 && !kFeat && D == 128;
+  constexpr bool kFold = !kFeat && D == 128;
   using L = BwdSmem<D, kStaged, kFold>;
   using R = BwdRoles<D>;
   constexpr int kPW = R::kPW, kCW = R::kCW;
@@ -364,6 +364,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // tiles of the two stages (B), unswizzled
       const uint64_t dOnes = make_sdesc_plain(smem_base + L::kOnesOff, 128, 0);
       const uint64_t dStat = make_sdesc_plain(sStats, 128, 256);
+      constexpr uint32_t idesc_fold = make_idesc(true, 128, 128, false, false);   // bf16 whatever the dtype
 
       // D[kv, q] = A[kv, d] * B[q, d]^T, both operands K-major over the head dim; at D = 64 the A
       // operand (K for S^T, V for dP^T) comes from tensor memory: 8 columns per 16 dims.
@@ -372,7 +373,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       auto issue_kd = [&](uint32_t d_col, uint64_t a_desc, uint64_t b_desc, int st) {
         if constexpr (kFold)
           mma_ss_e(tmem_base + d_col, sdesc_advance(dOnes, d_col == kColS ? 0 : 128),
-                   sdesc_advance(dStat, st * L::kStatsStage), idesc_s, 0u);
+                   sdesc_advance(dStat, st * L::kStatsStage), idesc_fold, 0u);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * L::kBlockBytes + (k & 3) * 32;

@@ -44,12 +44,12 @@ def test_validation_errors_come_before_any_launch():
         assert b"head_dim" in lib.fa2_last_error()
     a.p.head_dim = 96              # padded to 128 inside: the workspace is sized for 128 columns
     rows = 1 * 4 * 128
-    # statistics, fp32 dq accumulator, one word, and (bf16, head dim 128) 4 KiB of statistics in
+    # statistics, fp32 dq accumulator, one word, and (head dim 128) 4 KiB of statistics in
     # MMA operand form per 128 rows
     assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 128 * 4 + 256 + rows // 128 * 4096
-    a.p.dtype = _capi.FA2_FP16
-    assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 128 * 4 + 256
-    a.p.dtype = _capi.FA2_BF16
+    a.p.head_dim = 64
+    assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 64 * 4 + 256
+    a.p.head_dim = 96
     a.p.head_dim = 128
     a.p.dropout_p = 1.0
     assert lib.fa2_fwd(C.byref(a), None) == _capi.FA2_ERR_INVALID_ARG
