@@ -58,9 +58,9 @@ STRONG = ("long_context_causal_bf16", "head_dim_256_causal_fp16")
 # beyond it), dropout 0.1 with seed 42
 WORKLOAD_EXTRAS = {"mha_bias_mask_dropout_bf16": {"bias": True, "mask": True, "dropout": 0.1, "seed": 42}}
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward main kernel at the
-# default workload, from the ncu capture summarised under profiles/ (--batch 2 capture: 306.6 MB
-# read + 126.7 MB written; traffic grows with the batch, so x4 for the full launch).
-BWD_MAIN_DRAM_TRAFFIC_BYTES = 1.73e9
+# default workload, from the ncu capture summarised under profiles/ (--batch 2 capture: 365.7 MB
+# read + 149.1 MB written; traffic grows with the batch, so x4 for the full launch).
+BWD_MAIN_DRAM_TRAFFIC_BYTES = 2.06e9
 
 
 def load_peaks():

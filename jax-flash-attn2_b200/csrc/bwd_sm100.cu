@@ -29,10 +29,10 @@ namespace {
 
 constexpr int kBN = 128;   // keys per CTA
 // Warpgroups that compute P and dS: each owns 128 / kPW query columns of every step, and they come
-// first in the block, followed by the dQ drain warpgroup and the MMA / TMA warpgroup. The kernel
-// is bound by shared-memory bandwidth at D = 128 (the operands of the 128x128x16 MMAs alone take
-// all of it), where two warpgroups measured a little faster than four; at D = 64 the element-wise
-// phases weigh more and four warpgroups hide more of their latencies.
+// first in the block, followed by the dQ drain warpgroup and the MMA / TMA warpgroup. At D = 128
+// two warpgroups measured a little faster than four (the step is bound by the dQ reductions and
+// by broadcast shared-memory loads whose number does not shrink with more warps); at D = 64 the
+// element-wise phases weigh more and four warpgroups hide more of their latencies.
 // Registers per thread after setmaxnreg (the pool is the launch allocation):
 //   kPW = 2: launch 128: 2 * 128 + 152 + 104 = 4 * 128
 //   kPW = 4: launch  80, nobody trades: the MMA / TMA warps spill below 80 and the drain, which
