@@ -72,7 +72,7 @@ struct BwdSmem {
   static constexpr int kVOff = kKOff + kTileBytes;
   static constexpr int kQOff = kVOff + kTileBytes;         // 2 stages
   static constexpr int kdOOff = kQOff + 2 * kTileBytes;    // 1 stage
-  // dQ leaves through two staging chunks of [D/4/kChunks][128 rows][4 floats]
+  // dQ leaves through kStageBufs staging chunks of [D/4/kChunks][128 rows][4 floats]
   static constexpr int kChunks = kFold ? 8 : 4;            // chunks per fp32 tile
   static constexpr int kStageBufs = kFold ? 3 : 2;
   // kFold: the drain is bound by the rate at which the TMA unit gets bulk reductions into L2
@@ -494,10 +494,11 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // early; the reductions (slow: they queue in the memory pipe) then overlap with the MMAs of
       // the next step. With four P/dS warpgroups the register file only leaves room for half a
       // D = 128 tile here, so the tile is taken in two parts and handed back after the second load.
-      // Each part leaves through the TMA unit in chunks of D/kChunks columns through two staging
+      // Each part leaves through the TMA unit in chunks of D/kChunks columns through the staging
       // buffers: cp.reduce.async.bulk adds a chunk to the global fp32 accumulator while the next
-      // one is written. (Reductions issued from registers would queue in the memory pipe in front
-      // of the tensor-memory traffic of the other warps.)
+      // one is written. (All reductions issued from registers would queue in the memory pipe in
+      // front of the tensor-memory traffic of the other warps; a small share of them does not, and
+      // takes load off the TMA unit: kDirectChunks.)
       constexpr int kParts = (kPW == 4 && D == 128) ? 2 : 1;
       constexpr int kPartCols = D / kParts;
       float* dst_tile = p.dq_acc + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * (kBM * D);
