@@ -167,6 +167,13 @@ typedef struct {
    * ignore it and draw the bits again. */
   const uint32_t* dropout_bits;
   size_t dropout_bits_bytes;
+  /* Non-zero: dq is bit-reproducible from call to call, as the reference's is (its dq program owns
+   * a query tile and adds the key tiles in a loop, _backward_triton.py:438-516; here every key tile
+   * adds its part to a float32 accumulator, by default in whatever order the tiles get there). The
+   * key tiles then add their parts in descending order of their index, each waiting for the one
+   * above it, and are launched in that order; the backward takes longer. dk, dv and the forward are
+   * bit-reproducible either way. Head dims up to 128; FA2_ERR_UNSUPPORTED above. */
+  int32_t deterministic;
 } fa2_bwd_params;
 
 /* Forward: o = softmax(scale q k^T + bias + mask [causal]) v with dropout on the weights, and
@@ -198,7 +205,7 @@ const char* fa2_last_error(void);
 /* ABI version of this header: major * 1000 + minor. A change to the layout or meaning of a
  * structure is a new major version; bindings compare fa2_version() with the FA2_ABI_VERSION they
  * were written against and refuse a library whose major version differs. */
-#define FA2_ABI_VERSION 2000
+#define FA2_ABI_VERSION 3000
 int fa2_version(void);
 
 /* Size of the scratch array built into the library for fa2_bwd_static_scratch (32 MiB). */

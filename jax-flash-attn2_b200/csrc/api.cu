@@ -264,7 +264,7 @@ constexpr size_t kSchedL2Bytes = 128u << 20;
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct BwdWorkspace {
-  size_t delta_off, dq_off, absmax_off, xstats_off, total;
+  size_t delta_off, dq_off, absmax_off, xstats_off, order_off, total;
   int sq_pad;
 };
 BwdWorkspace bwd_workspace(const fa2_problem& p) {
@@ -279,7 +279,9 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   w.xstats_off = w.absmax_off + 256;   // one word: max|dO| of the call (fp16 range guard)
   // the row statistics once more as MMA operand tiles, 4 KiB per 128 rows (head dim 128)
   const bool fold = hd.padded == 128;
-  w.total = w.xstats_off + (fold ? rows / 128 * 4096 : 0);
+  w.order_off = w.xstats_off + (fold ? rows / 128 * 4096 : 0);
+  // one counter per 128-row dQ tile for the bit-reproducible mode (head dims up to 128)
+  w.total = w.order_off + (hd.padded <= 128 ? align_up(rows / 128 * sizeof(int), 256) : 0);
   return w;
 }
 
@@ -574,6 +576,8 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
     return fail(FA2_ERR_INVALID_ARG, "seqlens requires seqlen_q == seqlen_k");
   if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
+  if (a->deterministic && D > 128)
+    return fail(FA2_ERR_UNSUPPORTED, "deterministic dq is implemented for head dims up to 128");
   kp.seqlens = a->seqlens;
   if ((rc = set_dropout_operands(&kp.drop, a->dropout_seed_dev, a->offsets_dev))) return rc;
   if ((rc = set_dropout_bits(&kp.drop, p, a->dropout_bits, a->dropout_bits_bytes))) return rc;
@@ -596,6 +600,7 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
   // (the plain head-dim-128 kernel divides the log-sum-exp by the scale once, in the pre-pass)
   L.feat = kp.bias.ptr || kp.mask.ptr || kp.drop.enabled || !(std::fabs(p.softmax_scale) >= 1e-30f);
   kp.xstats = (!L.feat && D == 128) ? reinterpret_cast<const uint4*>(ws + w.xstats_off) : nullptr;
+  kp.dq_order = a->deterministic ? reinterpret_cast<int*>(ws + w.order_off) : nullptr;
   if (L.feat && D == 64) {
     // the head-dim-64 kernel brings 16-bit bias / mask tiles in through the TMA unit
     try_stage_term(&L.tmBias, &kp.bias, p, 128);

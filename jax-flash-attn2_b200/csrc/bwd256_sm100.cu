@@ -136,7 +136,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int half = blockIdx.x & 1;
   const int rest = blockIdx.x >> 1;
   int n, bhk;
-  bwd_work_item(rest, p.B * p.Hkv, p.n_kvblk, p.sched_groups, bhk, n);
+  bwd_work_item(rest, p.B * p.Hkv, p.n_kvblk, p.sched_groups, false, bhk, n);
   const int b = bhk / p.Hkv;
   const int hk = bhk - b * p.Hkv;
   const int nQ64 = (p.Sq + kBQ - 1) / kBQ;      // tiles in the accumulator layout
@@ -654,7 +654,7 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax,
-      a.head_dim_real, kp.seqlens, nullptr, 0.f);
+      a.head_dim_real, kp.seqlens, nullptr, 0.f, nullptr, 0);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   mark(1);

@@ -160,6 +160,41 @@ __device__ __forceinline__ void split3_bf16(float x, uint32_t& hi, uint32_t& mid
   lo = __bfloat16_as_ushort(l);
 }
 
+// Number of key tiles whose CTA has a step for the query tile of `tile_rows` rows with index i, in
+// a batch element with sq_b query and sk_b key rows: the step rule of the main kernels (a CTA works
+// iff its first key is below sk_b, from the first query tile that sees its first key under the
+// causal limit). The contributing key tiles are 0 .. count - 1.
+__device__ __forceinline__ int bwd_tile_contributors(bool causal, int i, int tile_rows, int sq_b, int sk_b,
+                                                     int n_kvblk, int causal_off) {
+  if (i >= (sq_b + tile_rows - 1) / tile_rows) return 0;
+  const int n_live = min(n_kvblk, (sk_b + 127) / 128);
+  if (!causal) return n_live;
+  // key tile n takes part iff n * 128 - causal_off < (i + 1) * tile_rows
+  const long long lim = static_cast<long long>(i + 1) * tile_rows + causal_off;
+  if (lim <= 0) return 0;
+  return static_cast<int>(min(static_cast<long long>(n_live), (lim + 127) / 128));
+}
+
+// Bit-reproducible dq: waits (bounded, like the mbarrier waits) until `*counter == want`, i.e. until
+// the key tiles that add before this one have added their part of the dQ tile.
+__device__ __forceinline__ bool wait_for_turn(const int* counter, int want, volatile int* abort_flag) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    int seen;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if (seen == want) return true;
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+    __nanosleep(100);
+  }
+}
+
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(128)
 bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
@@ -167,7 +202,8 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                long long do_sh, const float* __restrict__ lse, long long lse_sb, long long lse_sh,
                float* __restrict__ stats, float* __restrict__ dq_acc, int Sq, int Hq, int nQ,
                unsigned* __restrict__ do_absmax_bits, int d_real,
-               const int* __restrict__ seqlens, uint4* __restrict__ xstats, float inv_scale_log2) {
+               const int* __restrict__ seqlens, uint4* __restrict__ xstats, float inv_scale_log2,
+               int* __restrict__ dq_order, int order_per_tile) {
   // one-dimensional grid (the y and z extents of a grid stop at 65535): tile index fastest
   const int i = blockIdx.x % nQ;
   const int bh = blockIdx.x / nQ;
@@ -228,6 +264,7 @@ bwd_pre_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
   }
   float4* acc4 = reinterpret_cast<float4*>(dq_acc + tile * (kBM * D));
   for (int k = tid; k < kBM * D / 4; k += 128) acc4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (dq_order != nullptr && tid < order_per_tile) dq_order[tile * order_per_tile + tid] = 0;
   if constexpr (!kBf16) {
     // block maximum of |dO| -> one atomic per block (non-negative floats order like their bits)
     __shared__ float warp_max[4];

@@ -206,7 +206,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   // ---- work item: (batch, kv head, key tile); later key tiles (fewest steps when causal) last
   int n, bhk;
-  bwd_work_item(blockIdx.x, p.B * p.Hkv, p.n_kvblk, p.sched_groups, bhk, n);
+  bwd_work_item(blockIdx.x, p.B * p.Hkv, p.n_kvblk, p.sched_groups, p.dq_order != nullptr, bhk, n);
   const int b = bhk / p.Hkv;
   const int hk = bhk - b * p.Hkv;
   const int nQ = (p.Sq + kBM - 1) / kBM;   // query tiles in the statistics / accumulator layout
@@ -478,6 +478,10 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t tdQ = tmem_base + lane_base + kColdQ;
     bool ok = true;
     uint32_t ring = 0;   // staging buffer of the next chunk
+    // Bit-reproducible dq (p.dq_order): this key tile adds its part of a dQ tile when the
+    // contributing key tiles above it have added theirs, and says so once its own reductions have
+    // been performed. Two more named barriers per step.
+    const bool ordered = p.dq_order != nullptr;
     for (int it = 0; it < T; ++it) {
       int h, i;
       step_coords(it, h, i);
@@ -486,7 +490,7 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // No early exit: a thread that left alone would strand the other 127 at the (unbounded)
         // named barriers of the staging loop. Keep in step with them: two barriers per chunk.
 #pragma unroll 1
-        for (int k = 0; k < 2 * (L::kChunks - L::kDirectChunks); ++k) named_bar_sync(3, 128);
+        for (int k = 0; k < 2 * (L::kChunks - L::kDirectChunks) + (ordered ? 2 : 0); ++k) named_bar_sync(3, 128);
         continue;
       }
       tc_fence_after();
@@ -501,7 +505,9 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // takes load off the TMA unit: kDirectChunks.)
       constexpr int kParts = (kPW == 4 && D == 128) ? 2 : 1;
       constexpr int kPartCols = D / kParts;
-      float* dst_tile = p.dq_acc + ((static_cast<long long>(b) * p.Hq + h) * nQ + i) * (kBM * D);
+      const long long tile = (static_cast<long long>(b) * p.Hq + h) * nQ + i;
+      float* dst_tile = p.dq_acc + tile * (kBM * D);
+
 #pragma unroll
       for (int part = 0; part < kParts; ++part) {
         uint32_t v[kPartCols];
@@ -512,6 +518,15 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (part == kParts - 1) {
           tc_fence_before();
           mbar_arrive(bar_dq_drained);
+        }
+        if (ordered && part == 0) {
+          // the tensor-memory columns have been handed back: only the reductions are held back
+          // until it is this key tile's turn, not the MMAs of the next step
+          if (r == 0) {
+            const int above = bwd_tile_contributors(kCausal, i, kBM, sq_b, sk_b, p.n_kvblk, p.causal_off) - 1 - n;
+            if (!wait_for_turn(p.dq_order + tile, above, abort_flag)) atomicOr(p.status, 256);
+          }
+          named_bar_sync(3, 128);
         }
         constexpr int kChunkVecs = D / 4 / L::kChunks;   // float4 columns per chunk
         // the last kDirect chunks of a tile go out as vector reductions from registers
@@ -555,6 +570,15 @@ bwd_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                 smem_base + L::kStageOff + buf * L::kChunkBytes, L::kChunkBytes);
             tma_store_commit();
           }
+        }
+      }
+      if (ordered) {
+        if (L::kDirectChunks > 0) __threadfence();   // this thread's reductions from registers
+        named_bar_sync(3, 128);
+        if (r == 0) {
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // performed, not only read
+          __threadfence();
+          atomicAdd(p.dq_order + tile, 1);
         }
       }
     }
@@ -873,7 +897,7 @@ static cudaError_t launch_all(const BwdLaunch& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ, kBf16 ? nullptr : absmax,
-      a.head_dim_real, kp.seqlens, const_cast<uint4*>(kp.xstats), 1.f / kp.scale_log2);
+      a.head_dim_real, kp.seqlens, const_cast<uint4*>(kp.xstats), 1.f / kp.scale_log2, kp.dq_order, 1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int key = (a.causal ? 2 : 0) | (a.feat ? 1 : 0);

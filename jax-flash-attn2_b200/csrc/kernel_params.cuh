@@ -101,13 +101,17 @@ struct BwdKernelParams;
 // tiles of all groups heaviest first balances best but makes every group's Q / dO tiles live in L2
 // for the whole launch. Chunks of `sched_groups` groups, key-tile-major inside a chunk, keep the
 // working set of a chunk in L2 and leave only the last chunk's tail.
-__device__ __forceinline__ void bwd_work_item(int idx, int groups, int n_kvblk, int sched_groups, int& bhk, int& n) {
+// `descending`: the key tiles of a chunk come last tile first instead (the order in which the
+// bit-reproducible mode adds them to dQ: a block then only ever waits for blocks launched before it).
+__device__ __forceinline__ void bwd_work_item(int idx, int groups, int n_kvblk, int sched_groups, bool descending,
+                                              int& bhk, int& n) {
   const int per_chunk = sched_groups * n_kvblk;
   const int chunk = idx / per_chunk;
   const int rem = idx - chunk * per_chunk;
   const int in_chunk = min(sched_groups, groups - chunk * sched_groups);   // the last chunk may be short
   n = rem / in_chunk;
   bhk = chunk * sched_groups + (rem - n * in_chunk);
+  if (descending) n = n_kvblk - 1 - n;
 }
 
 struct BwdKernelParams {
@@ -135,6 +139,11 @@ struct BwdKernelParams {
   // scaled by a power of two derived from it so that small cotangents do not underflow in fp16.
   const unsigned* do_absmax_bits;
   ScoreGradDev dbias;
+  // Bit-reproducible dq, or null: dq_order[(b * Hq + h) * nQ + i] counts the key tiles that have
+  // added their part of dQ tile i (zeroed by the pre-pass). Key tile n adds its part when the
+  // tiles above it that contribute have, i.e. in descending order, and the launch order is
+  // descending too, so that a block only waits for blocks with a lower index.
+  int* dq_order;
   int* status;
 };
 

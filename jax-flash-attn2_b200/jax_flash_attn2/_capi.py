@@ -31,7 +31,7 @@ EXPORTED_SYMBOLS = (
 )
 FA2_BWD_STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 # FA2_ABI_VERSION of the header these structures were written against (major * 1000 + minor)
-FA2_ABI_VERSION = 2000
+FA2_ABI_VERSION = 3000
 
 
 class Strides(C.Structure):
@@ -116,6 +116,7 @@ class BwdParams(C.Structure):
         ("dbias", ScoreGrad),
         ("dropout_bits", C.c_void_p),
         ("dropout_bits_bytes", C.c_size_t),
+        ("deterministic", C.c_int32),
     ]
 
 

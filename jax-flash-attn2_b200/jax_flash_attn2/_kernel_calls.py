@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 import typing as tp
 
 import torch
@@ -305,14 +306,20 @@ def bwd_attention_kernel_call(
     offsets_dev: tp.Optional[torch.Tensor] = None,
     bias_grad: bool = False,
     dropout_bits: tp.Optional[torch.Tensor] = None,
+    deterministic: tp.Optional[bool] = None,
 ):
     """Backward launch; `M` is the lse returned by the forward. Returns (dq, dk, dv) in the input
     dtype; dk and dv are already reduced over the query heads of each key/value head. With
     `bias_grad=True` a fourth result is the gradient of `bias` in float32 and in the bias's own
     shape (summed over the batch elements / query heads that share an entry); the reference has no
-    bias cotangent (flash_attention_triton/_flash_attention.py:88)."""
+    bias cotangent (flash_attention_triton/_flash_attention.py:88). `deterministic=True` makes dq
+    bit-reproducible from call to call like the reference's (its dq program adds the key tiles in a
+    loop, _backward_triton.py:438-516) at the price of a slower backward; the default (None) reads
+    the environment variable FA2_B200_DETERMINISTIC (unset or "0": off)."""
     _check_qkv(q, k, v)
     lib = _capi.load()
+    if deterministic is None:
+        deterministic = os.environ.get("FA2_B200_DETERMINISTIC", "0") not in ("", "0")
     q, k, v, o, dO = map(_unit_last, (q, k, v, o, dO))
     batch, sq, hq, d = q.shape
     sk = k.shape[1]
@@ -350,6 +357,7 @@ def bwd_attention_kernel_call(
     a.dropout_seed_dev, _keep_d = _seed_ptr(dropout_seed, q)
     a.offsets_dev, _keep_f = _offsets_ptr(offsets_dev, q)
     a.dropout_bits, a.dropout_bits_bytes = _dropout_bits_ptr(dropout_bits, q)
+    a.deterministic = int(bool(deterministic))
     _launch(lib.fa2_bwd, a, q.device)
     if bias_grad:
         return dq, dk, dv, dbias

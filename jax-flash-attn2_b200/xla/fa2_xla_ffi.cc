@@ -179,7 +179,7 @@ ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ff
                    ffi::AnyBuffer v, ffi::AnyBuffer bias, ffi::AnyBuffer mask, ffi::AnyBuffer o,
                    ffi::AnyBuffer lse, ffi::AnyBuffer seqlens, ffi::AnyBuffer seed, ffi::AnyBuffer offsets,
                    ffi::AnyBuffer dropout_bits, float softmax_scale, float dropout_p, bool causal, int64_t dropout_seed,
-                   int32_t batch_offset, int32_t head_offset, int32_t heads_q_global,
+                   int32_t batch_offset, int32_t head_offset, int32_t heads_q_global, bool deterministic,
                    ffi::Result<ffi::AnyBuffer> dq, ffi::Result<ffi::AnyBuffer> dk,
                    ffi::Result<ffi::AnyBuffer> dv, ffi::Result<ffi::AnyBuffer> dbias,
                    ffi::Result<ffi::AnyBuffer> workspace) {
@@ -223,6 +223,7 @@ ffi::Error BwdImpl(cudaStream_t stream, ffi::AnyBuffer d_o, ffi::AnyBuffer q, ff
     a.dropout_bits = static_cast<const uint32_t*>(dropout_bits.untyped_data());
     a.dropout_bits_bytes = static_cast<size_t>(dropout_bits.element_count()) * 4;
   }
+  a.deterministic = deterministic ? 1 : 0;
   if (fa2_bwd(&a, stream) != FA2_OK) return Failed("fa2_b200_bwd");
   return ffi::Error::Success();
 }
@@ -276,6 +277,7 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(
         .Attr<int32_t>("batch_offset")
         .Attr<int32_t>("head_offset")
         .Attr<int32_t>("heads_q_global")
+        .Attr<bool>("deterministic")
         .Ret<ffi::AnyBuffer>()    // dq
         .Ret<ffi::AnyBuffer>()    // dk
         .Ret<ffi::AnyBuffer>()    // dv

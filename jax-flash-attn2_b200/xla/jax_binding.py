@@ -23,7 +23,7 @@ import jax.numpy as jnp
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-FA2_ABI_VERSION = 2000      # of the include/fa2_b200.h this module was written against
+FA2_ABI_VERSION = 3000      # of the include/fa2_b200.h this module was written against
 _SCRATCH_SLACK = 128        # kScratchSlack of fa2_xla_ffi.cc: room to align a scratch result
 _core = ctypes.CDLL(os.path.join(_HERE, "..", "libfa2_b200.so"), mode=ctypes.RTLD_GLOBAL)
 _core.fa2_version.restype = ctypes.c_int
@@ -155,8 +155,10 @@ def _fwd_attention_kernel_call(q, k, v, attention_mask=None, bias=None, softmax_
 
 def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_prob, causal,
                                softmax_scale, dropout_seed, varlen_mode=True, *, offsets=None,
-                               heads_q_global=None, bias_grad=False, dropout_bits=None):
+                               heads_q_global=None, bias_grad=False, dropout_bits=None, deterministic=None):
     del varlen_mode
+    if deterministic is None:   # bit-reproducible dq at the price of a slower backward
+        deterministic = os.environ.get("FA2_B200_DETERMINISTIC", "0") not in ("", "0")
     bias_, mask_, seqlens = _operands(q, bias, attention_mask)
     seed_op, seed_attr = _seed_operand(q, dropout_seed)
     want_dbias = bias_grad and bias is not None
@@ -170,6 +172,7 @@ def _bwd_attention_kernel_call(dO, q, k, v, bias, attention_mask, o, M, dropout_
     dq, dk, dv, dbias, _ = jax.ffi.ffi_call("fa2_b200_bwd", out_types)(
         dO, q, k, v, bias_, mask_, o, M, seqlens, seed_op, _offsets_operand(q, offsets),
         jnp.zeros((1,), jnp.uint32) if dropout_bits is None else dropout_bits,
+        deterministic=bool(deterministic),
         **_attrs(q, softmax_scale, dropout_prob, causal, seed_attr, heads_q_global))
     return dq, dk, dv, (dbias.astype(bias.dtype) if want_dbias else None)
 

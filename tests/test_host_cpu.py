@@ -23,7 +23,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert set(_capi.EXPORTED_SYMBOLS) <= declared
-    assert lib.fa2_version() == _capi.FA2_ABI_VERSION == 2000
+    assert lib.fa2_version() == _capi.FA2_ABI_VERSION == 3000
     assert f"#define FA2_ABI_VERSION {_capi.FA2_ABI_VERSION}" in header
 
 
@@ -44,11 +44,11 @@ def test_validation_errors_come_before_any_launch():
         assert b"head_dim" in lib.fa2_last_error()
     a.p.head_dim = 96              # padded to 128 inside: the workspace is sized for 128 columns
     rows = 1 * 4 * 128
-    # statistics, fp32 dq accumulator, one word, and (head dim 128) 4 KiB of statistics in
-    # MMA operand form per 128 rows
-    assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 128 * 4 + 256 + rows // 128 * 4096
+    # statistics, fp32 dq accumulator, one word, (head dim 128) 4 KiB of statistics in MMA operand
+    # form per 128 rows, and a counter per 128-row tile (256-byte granules) for the ordered mode
+    assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 128 * 4 + 256 + rows // 128 * 4096 + 256
     a.p.head_dim = 64
-    assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 64 * 4 + 256
+    assert lib.fa2_bwd_workspace_bytes(C.byref(a.p)) == 2 * rows * 4 + rows * 64 * 4 + 256 + 256
     a.p.head_dim = 96
     a.p.head_dim = 128
     a.p.dropout_p = 1.0
@@ -62,7 +62,7 @@ def test_validation_errors_come_before_any_launch():
     # workspace size is pure arithmetic
     n = lib.fa2_bwd_workspace_bytes(C.byref(a.p))
     rows = 1 * 4 * 128
-    assert n == 2 * rows * 4 + rows * 128 * 4 + 256 + rows // 128 * 4096
+    assert n == 2 * rows * 4 + rows * 128 * 4 + 256 + rows // 128 * 4096 + 256
     b = _capi.BwdParams()
     b.p = a.p
     assert lib.fa2_bwd(C.byref(b), None) == _capi.FA2_ERR_INVALID_ARG
@@ -125,11 +125,11 @@ def test_problems_whose_item_counts_overflow_are_refused():
 def test_stale_library_version_is_refused(monkeypatch):
     """The binding refuses a library whose ABI version differs from the one it was written for."""
     monkeypatch.setattr(_capi, "_lib", None)
-    monkeypatch.setattr(_capi, "FA2_ABI_VERSION", 3000)
+    monkeypatch.setattr(_capi, "FA2_ABI_VERSION", 4000)
     with pytest.raises(ImportError, match="ABI version"):
         _capi.load()
-    monkeypatch.setattr(_capi, "FA2_ABI_VERSION", 2000)
-    assert _capi.load().fa2_version() == 2000
+    monkeypatch.setattr(_capi, "FA2_ABI_VERSION", 3000)
+    assert _capi.load().fa2_version() == 3000
 
 
 def test_forward_scratch_is_only_asked_for_low_occupancy_problems():
