@@ -172,7 +172,7 @@ typedef struct {
    * adds its part to a float32 accumulator, by default in whatever order the tiles get there). The
    * key tiles then add their parts in descending order of their index, each waiting for the one
    * above it, and are launched in that order; the backward takes longer. dk, dv and the forward are
-   * bit-reproducible either way. Head dims up to 128; FA2_ERR_UNSUPPORTED above. */
+   * bit-reproducible either way. */
   int32_t deterministic;
 } fa2_bwd_params;
 

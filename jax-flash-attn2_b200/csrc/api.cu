@@ -280,8 +280,9 @@ BwdWorkspace bwd_workspace(const fa2_problem& p) {
   // the row statistics once more as MMA operand tiles, 4 KiB per 128 rows (head dim 128)
   const bool fold = hd.padded == 128;
   w.order_off = w.xstats_off + (fold ? rows / 128 * 4096 : 0);
-  // one counter per 128-row dQ tile for the bit-reproducible mode (head dims up to 128)
-  w.total = w.order_off + (hd.padded <= 128 ? align_up(rows / 128 * sizeof(int), 256) : 0);
+  // counters for the bit-reproducible mode: one per 128-row dQ tile, at head dim 256 one per
+  // 64 rows and half of the head dim
+  w.total = w.order_off + align_up(rows / 128 * (hd.padded <= 128 ? 1 : 4) * sizeof(int), 256);
   return w;
 }
 
@@ -576,8 +577,6 @@ int fa2_bwd(const fa2_bwd_params* a, void* cuda_stream) {
     return fail(FA2_ERR_INVALID_ARG, "seqlens requires seqlen_q == seqlen_k");
   if (a->seqlens && (reinterpret_cast<uintptr_t>(a->seqlens) & 3))
     return fail(FA2_ERR_INVALID_ARG, "seqlens must be 4-byte aligned");
-  if (a->deterministic && D > 128)
-    return fail(FA2_ERR_UNSUPPORTED, "deterministic dq is implemented for head dims up to 128");
   kp.seqlens = a->seqlens;
   if ((rc = set_dropout_operands(&kp.drop, a->dropout_seed_dev, a->offsets_dev))) return rc;
   if ((rc = set_dropout_bits(&kp.drop, p, a->dropout_bits, a->dropout_bits_bytes))) return rc;

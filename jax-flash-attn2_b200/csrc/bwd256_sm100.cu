@@ -136,7 +136,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int half = blockIdx.x & 1;
   const int rest = blockIdx.x >> 1;
   int n, bhk;
-  bwd_work_item(rest, p.B * p.Hkv, p.n_kvblk, p.sched_groups, false, bhk, n);
+  bwd_work_item(rest, p.B * p.Hkv, p.n_kvblk, p.sched_groups, p.dq_order != nullptr, bhk, n);
   const int b = bhk / p.Hkv;
   const int hk = bhk - b * p.Hkv;
   const int nQ64 = (p.Sq + kBQ - 1) / kBQ;      // tiles in the accumulator layout
@@ -363,6 +363,10 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tdQ = tmem_base + lane_base + kColdQ;
     bool ok = true;
+    // Bit-reproducible dq (p.dq_order, as in bwd_sm100.cu): this key tile adds its part of a dQ
+    // tile (64 query rows, this CTA's half of the head dim) when the contributing key tiles above
+    // it have, and counts up once its reductions have been performed. Two more barriers per step.
+    const bool ordered = p.dq_order != nullptr;
     for (int it = 0; it < T; ++it) {
       int h, i;
       step_coords(it, h, i);
@@ -371,7 +375,7 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // No early exit: a thread that left alone would strand the other 127 at the (unbounded)
         // named barriers of the staging loop. Keep in step with them: eight barriers per step.
 #pragma unroll 1
-        for (int k = 0; k < 8; ++k) named_bar_sync(3, 128);
+        for (int k = 0; k < 8 + (ordered ? 2 : 0); ++k) named_bar_sync(3, 128);
         continue;
       }
       tc_fence_after();
@@ -383,6 +387,17 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_arrive(bar_dq_drained);
       float* dst_tile = p.dq_acc +
                         (((static_cast<long long>(b) * p.Hq + h) * nQ64 + i) * 2 + half) * (kBQ * 128);
+      // four counters per 128-row tile of the pre-pass: (64-row half, head-dim half)
+      int* turn = ordered ? p.dq_order + ((static_cast<long long>(b) * p.Hq + h) * nQ128 + (i >> 1)) * 4 +
+                                (i & 1) * 2 + half
+                          : nullptr;
+      if (ordered) {
+        if (r == 0) {
+          const int above = bwd_tile_contributors(kCausal, i, kBQ, sq_b, sk_b, p.n_kvblk, p.causal_off) - 1 - n;
+          if (!wait_for_turn(turn, above, abort_flag)) atomicOr(p.status, 256);
+        }
+        named_bar_sync(3, 128);
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int buf = c & 1;
@@ -401,6 +416,14 @@ bwd256_main_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           bulk_reduce_add_f32(dst_tile + c * (16 * 128), smem_base + L::kStageOff + buf * L::kChunkBytes,
                               L::kChunkBytes);
           tma_store_commit();
+        }
+      }
+      if (ordered) {
+        named_bar_sync(3, 128);
+        if (r == 0) {
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // performed, not only read
+          __threadfence();
+          atomicAdd(turn, 1);
         }
       }
     }
@@ -654,7 +677,7 @@ static cudaError_t launch256_all(const BwdLaunch& a, cudaStream_t stream) {
       static_cast<const uint16_t*>(a.o), static_cast<const uint16_t*>(a.d_o), a.o_strides[0],
       a.o_strides[1], a.o_strides[2], a.do_strides[0], a.do_strides[1], a.do_strides[2], kp.lse,
       kp.lse_sb, kp.lse_sh, a.delta, kp.dq_acc, kp.Sq, kp.Hq, nQ128, kBf16 ? nullptr : absmax,
-      a.head_dim_real, kp.seqlens, nullptr, 0.f, nullptr, 0);
+      a.head_dim_real, kp.seqlens, nullptr, 0.f, kp.dq_order, 4);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   mark(1);

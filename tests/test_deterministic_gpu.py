@@ -25,6 +25,8 @@ def rel_l2(a, b):
     dict(B=2, Sq=700, Sk=1000, Hq=4, Hkv=4, D=128, dtype=torch.bfloat16, causal=True),      # ragged, Sq != Sk
     dict(B=2, Sq=640, Sk=900, Hq=4, Hkv=2, D=64, dtype=torch.bfloat16, causal=False),
     dict(B=2, Sq=512, Sk=512, Hq=4, Hkv=2, D=64, dtype=torch.float16, causal=True, p=0.1, bias_heads=4),
+    dict(B=2, Sq=520, Sk=520, Hq=4, Hkv=2, D=256, dtype=torch.bfloat16, causal=True),       # head dim 256 kernel
+    dict(B=1, Sq=300, Sk=450, Hq=2, Hkv=2, D=192, dtype=torch.float16, causal=False, p=0.1),
     # per-batch lengths (one element empty): checked against the default path only
     dict(B=3, Sq=600, Sk=600, Hq=4, Hkv=2, D=96, dtype=torch.bfloat16, causal=True, lengths=(600, 130, 0),
          oracle=False),
@@ -58,15 +60,3 @@ def test_deterministic_backward_is_bit_reproducible(case):
         ref = BlockAttention().backward(do, q, k, v, out.cpu(), lse.cpu()[:, :, :Sq], out_dtype=torch.float32, **kw)
         for mine, want in zip(first, ref):
             assert rel_l2(mine.cpu(), want) <= GRAD_TOL
-
-
-def test_deterministic_is_refused_above_head_dim_128():
-    import jax_flash_attn2 as J
-    from jax_flash_attn2 import _capi
-    q, k, v, do = (x.cuda() for x in W.make_qkv(1, 128, 128, 2, 2, 256, torch.bfloat16, 0.25))
-    out, lse = J.fwd_attention_kernel_call(q, k, v, None, None, None, 0.0, True, None)
-    with pytest.raises(_capi.Fa2Error, match="deterministic"):
-        J.bwd_attention_kernel_call(do, q, k, v, None, None, out, lse, 0.0, True, None, None, deterministic=True)
-    # and the call that follows is not affected
-    J.bwd_attention_kernel_call(do, q, k, v, None, None, out, lse, 0.0, True, None, None)
-    assert J.device_status() == 0
